@@ -1,0 +1,164 @@
+/*
+ * libreef_cuda — C-ABI device layer of the REEF executor kernel path on NVIDIA B200 (sm_100a).
+ *
+ * This header is the drop-in boundary: it replaces the reference's GPU abstraction, i.e. the
+ * 19 GPU* macros over the HIP driver API (reference: src/reef/executor/hip/hip_impl.h:5-23),
+ * the GPUConfig device/kernel resource model (reference: src/reef/executor/hip/hip_impl.h:58-75,
+ * src/reef/executor/hip/hip_impl.cpp:9-74) and the handful of direct HIP calls that bypass the
+ * macros (reference: src/reef/executor/executor_base.cpp:78, src/reef/executor/hybrid_executor.cpp:99-100,
+ * src/reef/server/scheduler.cpp:45,48,353-356,458).
+ *
+ * Conventions: plain C types only; every function returns a reef_status (the reference's Status
+ * enum, reference: src/reef/util/common.h:46-52, plus Timeout); no exceptions cross the boundary;
+ * handles are opaque.  Functions are thread-compatible per handle and not internally locked — the
+ * reference issues all GPU calls for a device from one scheduler thread and so does the host here.
+ */
+#ifndef REEF_CUDA_H_
+#define REEF_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define REEF_API __attribute__((visibility("default")))
+
+typedef int reef_status;
+enum {
+    REEF_SUCC = 0,        /* Status::Succ        */
+    REEF_FAIL = 1,        /* Status::Fail        */
+    REEF_NOT_FOUND = 2,   /* Status::NotFound    */
+    REEF_OUT_OF_RANGE = 3,/* Status::OutOfRange  */
+    REEF_FULL = 4,        /* Status::Full        */
+    REEF_TIMEOUT = 5      /* new: a bounded wait ran out */
+};
+
+typedef struct reef_module_s* reef_module_t;   /* replaces GPUModule_t   */
+typedef struct reef_kernel_s* reef_kernel_t;   /* replaces GPUFunction_t */
+typedef void* reef_stream_t;                   /* replaces GPUStream_t (a cudaStream_t) */
+typedef void* reef_event_t;
+typedef void* reef_graph_t;
+typedef uint64_t reef_dptr_t;                  /* replaces GPUDevicePtr_t */
+
+/* Last error text of the calling thread (CUDA error string or a registry message). */
+REEF_API const char* reef_last_error(void);
+
+/* ---- device ------------------------------------------------------------------------------- */
+/* GPUInit + GPUDeviceGet (reference: executor_base.cpp:19-22): selects `device` for the calling
+ * thread.  One executor / scheduler thread per GPU calls this with its own ordinal. */
+REEF_API reef_status reef_gpu_init(int device);
+REEF_API reef_status reef_device_count(int* count);
+/* GPUConfig::get_num_cus (reference: hip_impl.cpp:9-12 hard-codes 60): queried, 148 on B200. */
+REEF_API reef_status reef_device_num_sms(int* num_sms);
+REEF_API reef_status reef_device_sync(void);                       /* GPUDeviceSynchronize */
+
+/* ---- memory ------------------------------------------------------------------------------- */
+REEF_API reef_status reef_malloc(reef_dptr_t* ptr, size_t bytes);  /* GPUMalloc */
+REEF_API reef_status reef_free(reef_dptr_t ptr);                   /* GPUFree   */
+REEF_API reef_status reef_memset(reef_dptr_t ptr, int value, size_t bytes);                 /* GPUMemset */
+REEF_API reef_status reef_memset_async(reef_dptr_t ptr, int value, size_t bytes, reef_stream_t s);
+REEF_API reef_status reef_memcpy_h2d(reef_dptr_t dst, const void* src, size_t bytes);       /* GPUMemcpyHtoD */
+REEF_API reef_status reef_memcpy_d2h(void* dst, reef_dptr_t src, size_t bytes);             /* GPUMemcpyDtoH */
+REEF_API reef_status reef_memcpy_h2d_async(reef_dptr_t dst, const void* src, size_t bytes, reef_stream_t s); /* hipMemcpyHtoDAsync, scheduler.cpp:353 */
+REEF_API reef_status reef_memcpy_d2h_async(void* dst, reef_dptr_t src, size_t bytes, reef_stream_t s);       /* hipMemcpyDtoHAsync, hybrid_executor.cpp:138 */
+REEF_API reef_status reef_host_alloc_pinned(void** ptr, size_t bytes);                      /* hipHostMalloc, hybrid_executor.cpp:99-100 */
+REEF_API reef_status reef_host_free_pinned(void* ptr);
+
+/* ---- streams, events, graphs -------------------------------------------------------------- */
+/* GPUStreamCreate / hipStreamCreateWithWindowSize (reference: scheduler.cpp:45,48).  CUDA cannot
+ * bound or clear a stream's device queue, so the "window" is a host-side in-flight limiter in the
+ * scheduler; `high_priority` != 0 gives the real-time stream the greatest CUDA stream priority. */
+REEF_API reef_status reef_stream_create(reef_stream_t* s, int high_priority);
+REEF_API reef_status reef_stream_destroy(reef_stream_t s);
+REEF_API reef_status reef_stream_sync(reef_stream_t s);            /* GPUStreamSynchronize */
+/* GPUStreamQuery / GPUStreamEmpty (reference: hip_impl.cpp:77-80): *busy = 0 when idle. */
+REEF_API reef_status reef_stream_query(reef_stream_t s, int* busy);
+/* GPUWriteValue32Async (reference: hip_impl.h:20): ordered 32-bit store to device memory. */
+REEF_API reef_status reef_write32_async(reef_stream_t s, reef_dptr_t ptr, uint32_t value);
+REEF_API reef_status reef_event_create(reef_event_t* e);
+REEF_API reef_status reef_event_destroy(reef_event_t e);
+REEF_API reef_status reef_event_record(reef_event_t e, reef_stream_t s);
+REEF_API reef_status reef_event_sync(reef_event_t e);
+REEF_API reef_status reef_event_query(reef_event_t e, int* pending);
+REEF_API reef_status reef_event_elapsed_ms(reef_event_t start, reef_event_t stop, float* ms);
+REEF_API reef_status reef_stream_wait_event(reef_stream_t s, reef_event_t e);
+/* CUDA-graph capture of a launch sequence (no reference counterpart: the reference pays one
+ * hipModuleLaunchKernel per layer, executor_base.cpp:196-223). */
+REEF_API reef_status reef_graph_begin(reef_stream_t s);
+REEF_API reef_status reef_graph_end(reef_stream_t s, reef_graph_t* g);
+REEF_API reef_status reef_graph_launch(reef_graph_t g, reef_stream_t s);
+REEF_API reef_status reef_graph_destroy(reef_graph_t g);
+
+/* ---- kernel registry ---------------------------------------------------------------------- */
+/* GPUModuleLoad (reference: executor_base.cpp:24, hybrid_executor.cpp:22-23).  The reference loads
+ * one code object per model; here every kernel is built into this library and a "module" is a
+ * view of the built-in registry (path may be NULL and is only recorded). */
+REEF_API reef_status reef_module_open(const char* path_or_null, reef_module_t* mod);
+REEF_API reef_status reef_module_close(reef_module_t mod);
+/* GPUModuleGetFunction (reference: executor_base.cpp:47-52): resolve a kernel by the name string
+ * in <model>.json.  The name is "<family>__<key><int>_<key><int>..." ; an unknown family or an
+ * unsupported shape returns REEF_NOT_FOUND. */
+REEF_API reef_status reef_module_get_kernel(reef_module_t mod, const char* name, reef_kernel_t* k);
+/* Launch geometry of a kernel name: dims = {grid x,y,z, block x,y,z} as stored in
+ * "launch_params" (reference: model.cpp:35-37) and the dynamic shared memory in bytes as stored in
+ * "shared_memory".  Needs no GPU; the resource generator calls it so json and registry agree. */
+REEF_API reef_status reef_kernel_plan(const char* name, uint32_t dims[6], uint32_t* dyn_smem, int* num_args);
+
+/* GPUConfig::KernelResource + calculate_occupancy (reference: hip_impl.h:62-74, hip_impl.cpp:34-74). */
+typedef struct {
+    int num_blocks;        /* logical thread blocks of one launch                           */
+    int threads;           /* threads per block                                             */
+    int regs_per_thread;   /* replaces vgprs/sgprs                                          */
+    int static_smem;       /* bytes                                                         */
+    int dyn_smem;          /* bytes                                                         */
+    int local_mem;         /* replaces stack_size                                           */
+    int max_blocks_per_sm; /* occupancy from the CUDA occupancy API at (threads, dyn_smem)  */
+    double flops;          /* algorithmic FLOPs of one launch                               */
+    double bytes;          /* algorithmic HBM bytes of one launch                           */
+    int tensor_core;       /* 1 when the kernel's contraction runs on tcgen05               */
+} reef_kernel_attrs_t;
+REEF_API reef_status reef_kernel_attrs(reef_kernel_t k, reef_kernel_attrs_t* out);
+
+/* GPUModuleLaunchKernel (reference: executor_base.cpp:211-223).  `args[i]` points at the i-th
+ * 8-byte device pointer, positional as in the json "args" list.  dims must equal the plan. */
+REEF_API reef_status reef_launch(reef_kernel_t k, const uint32_t dims[6], uint32_t dyn_smem,
+                                 reef_stream_t s, void** args);
+/* Best-effort flavour (reference: hybrid_executor.cpp:153-163 launches K(int* preempted,
+ * int* task_slot, ...), wrapper contract script/best_effort_kernel.py:22-33).  Every block reads
+ * *preempt_flag at entry and at its loop heads and leaves without side effects on the completion
+ * counter when it is set; a block that ran to the end adds 1 to *task_slot.  The kernel is
+ * idempotent, so a kernel whose counter is short of num_blocks is simply launched again. */
+REEF_API reef_status reef_launch_be(reef_kernel_t k, const uint32_t dims[6], uint32_t dyn_smem,
+                                    reef_stream_t s, reef_dptr_t preempt_flag, reef_dptr_t task_slot,
+                                    void** args);
+/* Dynamic kernel padding (reference: scheduler.cpp:613-649 launches merge_framework_N with
+ * {rt func, rt occupancy, rt blocks, rt offset, rt args, be func, be occupancy, be blocks,
+ * be offset, be args, cu_partition}; device side resource/mocked_kernel/mocked_kernel.trans.cu:112-186).
+ * One persistent grid of sms*occupancy blocks: blocks resident on SMs [0, sm_partition) take the
+ * real-time kernel's logical blocks from a ticket counter, the others run best-effort logical
+ * blocks [be_block_offset, be_block_offset+be_block_num) and then help with what is left of the
+ * real-time kernel.  be may be NULL (then be_block_num = 0).  `ctrl` is 16 bytes of zeroed device
+ * memory owned by the caller, reused across launches (the kernel re-zeroes it when it drains). */
+REEF_API reef_status reef_dispatch(reef_kernel_t rt, void** rt_args,
+                                   reef_kernel_t be, void** be_args,
+                                   int be_block_offset, int be_block_num,
+                                   int sm_partition, int occupancy,
+                                   reef_dptr_t preempt_flag, reef_dptr_t be_task_slot,
+                                   reef_dptr_t ctrl, reef_stream_t s);
+
+/* GPUClearHostQueue / GPUResetCU (reference: hip_impl.h:21-22) have no CUDA equivalent: queued
+ * launches are dropped by the host scheduler before they reach the stream and running blocks leave
+ * at their next flag poll.  This call is the bounded replacement for the reference's wait loop
+ * (reference: scheduler.cpp:336-345): waits until `s` is idle or `timeout_us` passed (REEF_TIMEOUT). */
+REEF_API reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us);
+
+/* Number of kernels this library launched since load (its own kernels only; graph replays count
+ * the kernels inside the graph). */
+REEF_API uint64_t reef_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* REEF_CUDA_H_ */

@@ -1,0 +1,123 @@
+/*
+ * libreef_host — C entry points over the C++ host side (model loader, executors, scheduler) so that
+ * tests, benchmarks and non-C++ front ends can drive it.  Each function wraps the C++ method of the
+ * same name; the C++ classes mirror the reference's (reference: src/reef/executor/executor_base.h,
+ * src/reef/executor/hybrid_executor.h, src/reef/server/scheduler.h:68-126).  Return values are the
+ * reference's Status enum (reference: src/reef/util/common.h:46-52) plus 5 = Timeout.
+ */
+#ifndef REEF_HOST_H_
+#define REEF_HOST_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define REEF_HOST_API __attribute__((visibility("default")))
+
+typedef struct reef_executor_s* reef_executor_t;     /* HybridExecutor */
+typedef struct reef_scheduler_s* reef_scheduler_t;   /* REEFScheduler  */
+
+/* ---- resource parsers (reference tests: src/reef/test/test.cpp:59-91) ---------------------- */
+/* Model::from_json: counts of storage entries, kernels and I/O args; NotFound on a bad file. */
+REEF_HOST_API int reef_model_parse(const char* json_path, size_t* num_storage, size_t* num_kernels, size_t* num_args);
+/* ModelParamParser::parse_from_file: element count of blob `key` (0 when absent) and blob count. */
+REEF_HOST_API int reef_param_parse(const char* param_path, const char* key, size_t* key_elems, size_t* num_blobs);
+/* ModelProfile::from_json: kernel count, model latency, and the smallest latency entry. */
+REEF_HOST_API int reef_profile_parse(const char* profile_path, size_t* num_kernels, int* model_latency, int* min_latency);
+
+/* ---- executor (ExecutorBase / HybridExecutor) ---------------------------------------------- */
+REEF_HOST_API int reef_executor_create(int device, reef_executor_t* e);
+REEF_HOST_API int reef_executor_destroy(reef_executor_t e);
+REEF_HOST_API const char* reef_executor_error(reef_executor_t e);
+/* load_hybrid_model_from_file; profile_path may be NULL/"" (no latency tables) */
+REEF_HOST_API int reef_executor_load(reef_executor_t e, const char* json_path, const char* profile_path);
+REEF_HOST_API int reef_executor_load_param(reef_executor_t e, const char* param_path);
+REEF_HOST_API int reef_executor_num_kernels(reef_executor_t e, size_t* n);
+REEF_HOST_API int reef_executor_num_storage(reef_executor_t e, size_t* n);
+REEF_HOST_API int reef_executor_get_data_size(reef_executor_t e, const char* name, size_t* bytes);
+REEF_HOST_API int reef_executor_set_input(reef_executor_t e, const char* name, const void* data, size_t len);
+REEF_HOST_API int reef_executor_get_output(reef_executor_t e, void* out, size_t len);
+REEF_HOST_API int reef_executor_get_data(reef_executor_t e, int idx, void* out, size_t len);
+REEF_HOST_API int reef_executor_execute(reef_executor_t e);                 /* raw kernels, then sync       */
+REEF_HOST_API int reef_executor_execute_to(reef_executor_t e, int idx);     /* kernels [0, idx)             */
+REEF_HOST_API int reef_executor_execute_kernel(reef_executor_t e, int idx);
+REEF_HOST_API int reef_executor_execute_preemptable(reef_executor_t e);     /* best-effort flavour           */
+REEF_HOST_API int reef_executor_execute_graph(reef_executor_t e);           /* CUDA-graph replay, then sync  */
+REEF_HOST_API int reef_executor_execute_dispatch(reef_executor_t e);        /* every kernel through the dispatcher, unpadded */
+/* Best-effort run with the preempt flag raised `delay_us` after the first launch (host timer), then
+ * resumed from the first kernel whose completion counter is short until the model is done.
+ * *restarts = number of resume rounds, *first_incomplete = restart kernel of the first round. */
+REEF_HOST_API int reef_executor_execute_preempt_resume(reef_executor_t e, int delay_us, int* restarts, int* first_incomplete);
+/* Completion counters (task slots) and logical block counts per kernel, n entries each. */
+REEF_HOST_API int reef_executor_task_slots(reef_executor_t e, int* slots, int* block_nums, size_t n);
+/* Average milliseconds of `iters` executions after `warmup` (mode: 0 raw launches, 1 graph, 2 best-effort). */
+REEF_HOST_API int reef_executor_time(reef_executor_t e, int mode, int warmup, int iters, float* avg_ms);
+/* Per-kernel device time in microseconds (CUDA events around each launch), n = num_kernels entries;
+ * also returns algorithmic flops/bytes and the tensor-core marker per kernel when the arrays are given. */
+REEF_HOST_API int reef_executor_profile_kernels(reef_executor_t e, int iters, float* us, double* flops, double* bytes,
+                                                int* tensor_core, int* blocks, int* max_blocks_per_sm, size_t n);
+/* One persistent wave of kernel idx at `occupancy` blocks per SM on every SM (latency[occupancy-1] of profile.json) */
+REEF_HOST_API int reef_executor_profile_wave(reef_executor_t e, int idx, int occupancy, int iters, float* us);
+
+/* ---- scheduler (REEFScheduler) ------------------------------------------------------------ */
+/* mode: 0 NoPreempt, 1 MultiStream, 2 WaitPreempt, 3 REEF, 4 Reset (reference: scheduler.h:22-28) */
+REEF_HOST_API int reef_sched_create(int mode, int device, reef_scheduler_t* s);
+REEF_HOST_API int reef_sched_destroy(reef_scheduler_t s);
+REEF_HOST_API const char* reef_sched_error(reef_scheduler_t s);
+REEF_HOST_API int reef_sched_load_model(reef_scheduler_t s, const char* model_dir, const char* model_name, uint32_t* mid);
+REEF_HOST_API int reef_sched_load_model_files(reef_scheduler_t s, const char* json_path, const char* profile_path,
+                                              const char* param_path, uint32_t* mid);
+/* type: 0 RealTimeQueue, 1 BestEffortQueue */
+REEF_HOST_API int reef_sched_create_queue(reef_scheduler_t s, int type, uint32_t* qid);
+REEF_HOST_API int reef_sched_bind_model_queue(reef_scheduler_t s, uint32_t qid, uint32_t mid);
+REEF_HOST_API int reef_sched_get_data_size(reef_scheduler_t s, uint32_t mid, const char* name, size_t* bytes);
+REEF_HOST_API int reef_sched_set_input(reef_scheduler_t s, uint32_t mid, const void* data, size_t len, const char* name);
+REEF_HOST_API int reef_sched_get_output(reef_scheduler_t s, uint32_t mid, void* data, size_t len, const char* name);
+REEF_HOST_API int reef_sched_new_task(reef_scheduler_t s, uint32_t mid, uint32_t* tid);
+REEF_HOST_API int reef_sched_wait_task(reef_scheduler_t s, uint32_t tid);
+typedef struct {
+    int state;                 /* 0 Init, 1 Waiting, 2 Executing, 3 Finish */
+    int preempted, padded, padded_to_complete;
+    int64_t submit_ns, start_ns, end_ns;   /* system_clock, ns since epoch */
+} reef_task_info_t;
+REEF_HOST_API int reef_sched_task_info(reef_scheduler_t s, uint32_t tid, reef_task_info_t* info);
+REEF_HOST_API int reef_sched_set_wait_sync(reef_scheduler_t s, int value);
+REEF_HOST_API int reef_sched_set_be_stream_cap(reef_scheduler_t s, int value);
+REEF_HOST_API int reef_sched_set_rt_graph(reef_scheduler_t s, int value);
+REEF_HOST_API int reef_sched_run(reef_scheduler_t s);
+REEF_HOST_API int reef_sched_shutdown(reef_scheduler_t s);
+REEF_HOST_API int64_t reef_sched_avg_preempt_latency(reef_scheduler_t s);
+REEF_HOST_API int64_t reef_sched_avg_kernel_sel_latency(reef_scheduler_t s);
+typedef struct {
+    uint64_t preempt_count, preempt_ns_sum, preempt_ns_max;
+    uint64_t rt_tasks, be_tasks, be_tasks_padded_to_finish, padded_kernels, padded_blocks;
+} reef_sched_stats_t;
+REEF_HOST_API int reef_sched_stats(reef_scheduler_t s, reef_sched_stats_t* out);
+
+/* ---- closed-loop clients (behaviour of the reference's reef_client_cont, src/example/rpc_client_cont.cpp:31-35):
+ * every client thread repeats { set_input from its host buffer; new_task; wait_task; get_output into its host
+ * buffer } and records the per-request wall-clock latency.  Clients whose max_requests is 0 run until all
+ * clients with max_requests > 0 are done (background load). */
+typedef struct {
+    uint32_t mid;
+    uint32_t max_requests;       /* 0 = run while the bounded clients run                       */
+    uint32_t warmup_requests;    /* not recorded                                                */
+    const void* input;           /* host buffer for set_input (may be NULL: skip the copy)      */
+    size_t input_len;
+    const char* input_name;      /* NULL = "data"                                               */
+    void* output;                /* host buffer for get_output (may be NULL: skip the copy)     */
+    size_t output_len;
+    float* latencies_ms;         /* out: max_requests entries (bounded clients only)            */
+    uint64_t completed;          /* out: recorded requests                                      */
+    double elapsed_s;            /* out: wall time of the recorded requests                     */
+    uint32_t think_us;           /* pause between requests                                      */
+} reef_client_t;
+REEF_HOST_API int reef_run_clients(reef_scheduler_t s, reef_client_t* clients, size_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* REEF_HOST_H_ */

@@ -1,0 +1,324 @@
+// C-ABI device layer (see include/reef_cuda.h for the reference symbols each entry point replaces).
+#include <chrono>
+#include <cstring>
+#include <new>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../kernels/registry.h"
+
+using namespace reef;
+
+struct reef_module_s {
+    std::string path;
+    std::vector<reef_kernel_s*> kernels;
+};
+struct reef_kernel_s {
+    KernelSpec spec;
+};
+struct reef_graph_s {
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+    unsigned long long kernels;
+};
+
+static int g_num_sms = 0;
+
+#define CK(call)                                                                 \
+    do {                                                                         \
+        cudaError_t _e = (call);                                                 \
+        if (_e != cudaSuccess) {                                                 \
+            set_error(std::string(#call) + ": " + cudaGetErrorString(_e));       \
+            return REEF_FAIL;                                                    \
+        }                                                                        \
+    } while (0)
+
+extern "C" {
+
+const char* reef_last_error(void) { return last_error(); }
+
+static thread_local int t_device = -1;
+
+reef_status reef_gpu_init(int device) {
+    if (t_device == device) return REEF_SUCC;   // this thread is already bound
+    CK(cudaSetDevice(device));
+    CK(cudaFree(0));
+    cudaDeviceProp prop;
+    CK(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        set_error("libreef_cuda is built for sm_100a only; device is sm_" + std::to_string(prop.major) +
+                  std::to_string(prop.minor));
+        return REEF_FAIL;
+    }
+    g_num_sms = prop.multiProcessorCount;
+    t_device = device;
+    return REEF_SUCC;
+}
+
+reef_status reef_device_count(int* count) {
+    CK(cudaGetDeviceCount(count));
+    return REEF_SUCC;
+}
+
+reef_status reef_device_num_sms(int* n) {
+    if (g_num_sms == 0) {
+        int dev;
+        CK(cudaGetDevice(&dev));
+        CK(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    *n = g_num_sms;
+    return REEF_SUCC;
+}
+
+reef_status reef_device_sync(void) {
+    CK(cudaDeviceSynchronize());
+    return REEF_SUCC;
+}
+
+reef_status reef_malloc(reef_dptr_t* ptr, size_t bytes) {
+    void* p = nullptr;
+    CK(cudaMalloc(&p, bytes ? bytes : 4));
+    *ptr = (reef_dptr_t)p;
+    return REEF_SUCC;
+}
+reef_status reef_free(reef_dptr_t ptr) {
+    CK(cudaFree((void*)ptr));
+    return REEF_SUCC;
+}
+reef_status reef_memset(reef_dptr_t ptr, int value, size_t bytes) {
+    CK(cudaMemset((void*)ptr, value, bytes));
+    return REEF_SUCC;
+}
+reef_status reef_memset_async(reef_dptr_t ptr, int value, size_t bytes, reef_stream_t s) {
+    CK(cudaMemsetAsync((void*)ptr, value, bytes, (cudaStream_t)s));
+    return REEF_SUCC;
+}
+reef_status reef_memcpy_h2d(reef_dptr_t dst, const void* src, size_t bytes) {
+    CK(cudaMemcpy((void*)dst, src, bytes, cudaMemcpyHostToDevice));
+    return REEF_SUCC;
+}
+reef_status reef_memcpy_d2h(void* dst, reef_dptr_t src, size_t bytes) {
+    CK(cudaMemcpy(dst, (const void*)src, bytes, cudaMemcpyDeviceToHost));
+    return REEF_SUCC;
+}
+reef_status reef_memcpy_h2d_async(reef_dptr_t dst, const void* src, size_t bytes, reef_stream_t s) {
+    CK(cudaMemcpyAsync((void*)dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)s));
+    return REEF_SUCC;
+}
+reef_status reef_memcpy_d2h_async(void* dst, reef_dptr_t src, size_t bytes, reef_stream_t s) {
+    CK(cudaMemcpyAsync(dst, (const void*)src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)s));
+    return REEF_SUCC;
+}
+reef_status reef_host_alloc_pinned(void** ptr, size_t bytes) {
+    CK(cudaHostAlloc(ptr, bytes ? bytes : 4, cudaHostAllocDefault));
+    return REEF_SUCC;
+}
+reef_status reef_host_free_pinned(void* ptr) {
+    CK(cudaFreeHost(ptr));
+    return REEF_SUCC;
+}
+
+reef_status reef_stream_create(reef_stream_t* s, int high_priority) {
+    int lo = 0, hi = 0;
+    CK(cudaDeviceGetStreamPriorityRange(&lo, &hi));   // hi is the numerically lowest = greatest priority
+    cudaStream_t st;
+    CK(cudaStreamCreateWithPriority(&st, cudaStreamNonBlocking, high_priority ? hi : lo));
+    *s = (reef_stream_t)st;
+    return REEF_SUCC;
+}
+reef_status reef_stream_destroy(reef_stream_t s) {
+    CK(cudaStreamDestroy((cudaStream_t)s));
+    return REEF_SUCC;
+}
+reef_status reef_stream_sync(reef_stream_t s) {
+    CK(cudaStreamSynchronize((cudaStream_t)s));
+    return REEF_SUCC;
+}
+reef_status reef_stream_query(reef_stream_t s, int* busy) {
+    cudaError_t e = cudaStreamQuery((cudaStream_t)s);
+    if (e == cudaSuccess) { *busy = 0; return REEF_SUCC; }
+    if (e == cudaErrorNotReady) { *busy = 1; return REEF_SUCC; }
+    set_error(std::string("cudaStreamQuery: ") + cudaGetErrorString(e));
+    return REEF_FAIL;
+}
+typedef int (*write_value32_fn)(cudaStream_t, unsigned long long, unsigned int, unsigned int);
+static write_value32_fn g_write32 = nullptr;
+static int g_write32_state = 0;   // 0 unknown, 1 driver entry point, 2 pinned-constant copy
+static uint32_t* g_flag_consts = nullptr;
+
+reef_status reef_write32_async(reef_stream_t s, reef_dptr_t ptr, uint32_t value) {
+    if (g_write32_state == 0) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuStreamWriteValue32", &fn, cudaEnableDefault, &q);
+        if (e == cudaSuccess && q == cudaDriverEntryPointSuccess && fn != nullptr) {
+            g_write32 = (write_value32_fn)fn;
+            g_write32_state = 1;
+        } else {
+            (void)cudaGetLastError();
+            CK(cudaHostAlloc((void**)&g_flag_consts, 256 * sizeof(uint32_t), cudaHostAllocDefault));
+            for (uint32_t i = 0; i < 256; i++) g_flag_consts[i] = i;
+            g_write32_state = 2;
+        }
+    }
+    if (g_write32_state == 1) {
+        int rc = g_write32((cudaStream_t)s, (unsigned long long)ptr, value, 0);
+        if (rc != 0) {
+            set_error("cuStreamWriteValue32 failed with CUresult " + std::to_string(rc));
+            return REEF_FAIL;
+        }
+        return REEF_SUCC;
+    }
+    if (value > 255) {
+        set_error("reef_write32_async: fallback path supports values 0..255");
+        return REEF_OUT_OF_RANGE;
+    }
+    CK(cudaMemcpyAsync((void*)ptr, &g_flag_consts[value], 4, cudaMemcpyHostToDevice, (cudaStream_t)s));
+    return REEF_SUCC;
+}
+
+reef_status reef_event_create(reef_event_t* e) {
+    cudaEvent_t ev;
+    CK(cudaEventCreate(&ev));
+    *e = (reef_event_t)ev;
+    return REEF_SUCC;
+}
+reef_status reef_event_destroy(reef_event_t e) {
+    CK(cudaEventDestroy((cudaEvent_t)e));
+    return REEF_SUCC;
+}
+reef_status reef_event_record(reef_event_t e, reef_stream_t s) {
+    CK(cudaEventRecord((cudaEvent_t)e, (cudaStream_t)s));
+    return REEF_SUCC;
+}
+reef_status reef_event_sync(reef_event_t e) {
+    CK(cudaEventSynchronize((cudaEvent_t)e));
+    return REEF_SUCC;
+}
+reef_status reef_event_query(reef_event_t e, int* pending) {
+    cudaError_t r = cudaEventQuery((cudaEvent_t)e);
+    if (r == cudaSuccess) { *pending = 0; return REEF_SUCC; }
+    if (r == cudaErrorNotReady) { *pending = 1; return REEF_SUCC; }
+    set_error(std::string("cudaEventQuery: ") + cudaGetErrorString(r));
+    return REEF_FAIL;
+}
+reef_status reef_event_elapsed_ms(reef_event_t a, reef_event_t b, float* ms) {
+    CK(cudaEventElapsedTime(ms, (cudaEvent_t)a, (cudaEvent_t)b));
+    return REEF_SUCC;
+}
+reef_status reef_stream_wait_event(reef_stream_t s, reef_event_t e) {
+    CK(cudaStreamWaitEvent((cudaStream_t)s, (cudaEvent_t)e, 0));
+    return REEF_SUCC;
+}
+
+static thread_local unsigned long long g_capture_start = 0;
+reef_status reef_graph_begin(reef_stream_t s) {
+    g_capture_start = launch_count();
+    CK(cudaStreamBeginCapture((cudaStream_t)s, cudaStreamCaptureModeThreadLocal));
+    return REEF_SUCC;
+}
+reef_status reef_graph_end(reef_stream_t s, reef_graph_t* g) {
+    cudaGraph_t graph;
+    CK(cudaStreamEndCapture((cudaStream_t)s, &graph));
+    cudaGraphExec_t exec;
+    CK(cudaGraphInstantiate(&exec, graph, 0));
+    reef_graph_s* h = new (std::nothrow) reef_graph_s{graph, exec, launch_count() - g_capture_start};
+    if (!h) return REEF_FAIL;
+    *g = (reef_graph_t)h;
+    return REEF_SUCC;
+}
+reef_status reef_graph_launch(reef_graph_t g, reef_stream_t s) {
+    reef_graph_s* h = (reef_graph_s*)g;
+    CK(cudaGraphLaunch(h->exec, (cudaStream_t)s));
+    add_launches(h->kernels);
+    return REEF_SUCC;
+}
+reef_status reef_graph_destroy(reef_graph_t g) {
+    reef_graph_s* h = (reef_graph_s*)g;
+    if (!h) return REEF_SUCC;
+    cudaGraphExecDestroy(h->exec);
+    cudaGraphDestroy(h->graph);
+    delete h;
+    return REEF_SUCC;
+}
+
+reef_status reef_module_open(const char* path, reef_module_t* mod) {
+    reef_module_s* m = new (std::nothrow) reef_module_s;
+    if (!m) return REEF_FAIL;
+    if (path) m->path = path;
+    *mod = m;
+    return REEF_SUCC;
+}
+reef_status reef_module_close(reef_module_t mod) {
+    if (!mod) return REEF_SUCC;
+    for (auto* k : mod->kernels) delete k;
+    delete mod;
+    return REEF_SUCC;
+}
+reef_status reef_module_get_kernel(reef_module_t mod, const char* name, reef_kernel_t* k) {
+    if (!mod || !name) return REEF_FAIL;
+    reef_kernel_s* h = new (std::nothrow) reef_kernel_s;
+    if (!h) return REEF_FAIL;
+    int rc = plan_kernel(name, &h->spec);
+    if (rc != REEF_SUCC) {
+        delete h;
+        return rc;
+    }
+    mod->kernels.push_back(h);
+    *k = h;
+    return REEF_SUCC;
+}
+reef_status reef_kernel_plan(const char* name, uint32_t dims[6], uint32_t* dyn_smem, int* num_args) {
+    KernelSpec s;
+    int rc = plan_kernel(name, &s);
+    if (rc != REEF_SUCC) return rc;
+    for (int i = 0; i < 3; i++) {
+        dims[i] = s.grid[i];
+        dims[3 + i] = s.block[i];
+    }
+    if (dyn_smem) *dyn_smem = s.dyn_smem;
+    if (num_args) *num_args = s.nargs;
+    return REEF_SUCC;
+}
+reef_status reef_kernel_attrs(reef_kernel_t k, reef_kernel_attrs_t* out) {
+    if (!k || !out) return REEF_FAIL;
+    return kernel_attrs(k->spec, out);
+}
+
+reef_status reef_launch(reef_kernel_t k, const uint32_t dims[6], uint32_t dyn_smem, reef_stream_t s, void** args) {
+    if (!k) return REEF_FAIL;
+    return launch_plain(k->spec, dims, dyn_smem, (cudaStream_t)s, args);
+}
+reef_status reef_launch_be(reef_kernel_t k, const uint32_t dims[6], uint32_t dyn_smem, reef_stream_t s,
+                           reef_dptr_t flag, reef_dptr_t slot, void** args) {
+    if (!k || !flag || !slot) return REEF_FAIL;
+    return launch_be(k->spec, dims, dyn_smem, (cudaStream_t)s, (const int*)flag, (int*)slot, args);
+}
+reef_status reef_dispatch(reef_kernel_t rt, void** rt_args, reef_kernel_t be, void** be_args, int be_off,
+                          int be_num, int sm_partition, int occupancy, reef_dptr_t flag, reef_dptr_t be_slot,
+                          reef_dptr_t ctrl, reef_stream_t s) {
+    (void)flag;
+    if ((!rt && !be) || !ctrl) return REEF_FAIL;
+    int sms = 0;
+    int rc = reef_device_num_sms(&sms);
+    if (rc != REEF_SUCC) return rc;
+    return launch_dispatch(rt ? &rt->spec : nullptr, rt_args, be ? &be->spec : nullptr, be_args, be_off, be_num, sm_partition,
+                           occupancy, sms, (int*)be_slot, (int*)ctrl, (cudaStream_t)s);
+}
+
+reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us) {
+    auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        int busy = 0;
+        int rc = reef_stream_query(s, &busy);
+        if (rc != REEF_SUCC) return rc;
+        if (!busy) return REEF_SUCC;
+        auto us = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+        if ((uint64_t)us > timeout_us) return REEF_TIMEOUT;
+    }
+}
+
+uint64_t reef_launch_count(void) { return launch_count(); }
+
+}  // extern "C"

@@ -1,0 +1,446 @@
+#include "executor.h"
+
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+
+namespace reef {
+namespace executor {
+
+static const size_t kAlign = 256;
+
+ExecutorBase::ExecutorBase() {}
+
+ExecutorBase::~ExecutorBase() {
+    if (arena) reef_free(arena);
+    if (own_module && base_mod) reef_module_close(base_mod);
+}
+
+Status ExecutorBase::load_model_from_file(const char* json_file_path, const char* co_file_path) {
+    GPUModule_t mod;
+    GPU_RETURN_STATUS(reef_module_open(co_file_path, &mod));
+    own_module = true;
+    return this->load_model_from_GPU_module(json_file_path, mod);
+}
+
+Status ExecutorBase::load_model_from_GPU_module(const char* json_file_path, GPUModule_t mod) {
+    return init_executor_base(json_file_path, mod);
+}
+
+size_t ExecutorBase::storage_bytes(size_t idx) const {
+    const StorageInfo& si = model->storage[idx];
+    return Model::get_stype_size(si.stype) * si.size;
+}
+
+Status ExecutorBase::init_executor_base(const char* json_file_path, GPUModule_t mod) {
+    base_mod = mod;
+    // 1. json
+    model.reset(Model::from_json(json_file_path, &err_));
+    if (model.get() == nullptr) RETURN_STATUS(Status::NotFound);
+
+    // 2. kernels, by name; launch geometry in the json must be the registry's plan
+    kernels.clear();
+    kernel_smem.clear();
+    for (KernelInfo& ki : model->kernels) {
+        GPUFunction_t k;
+        int rc = reef_module_get_kernel(mod, ki.name.c_str(), &k);
+        if (rc != REEF_SUCC) {
+            err_ = reef_last_error();
+            RETURN_STATUS(rc);
+        }
+        uint32_t dims[6], smem = 0;
+        int nargs = 0;
+        GPU_RETURN_STATUS(reef_kernel_plan(ki.name.c_str(), dims, &smem, &nargs));
+        if (memcmp(dims, ki.launch_params, sizeof(dims)) != 0 || (size_t)nargs != ki.args.size()) {
+            err_ = "launch_params or argument count of " + ki.name + " do not match the kernel registry";
+            RETURN_STATUS(Status::Fail);
+        }
+        auto it = model->shared_memory.find(ki.name);
+        if (it != model->shared_memory.end() && it->second != smem) {
+            err_ = "shared_memory of " + ki.name + " does not match the kernel registry";
+            RETURN_STATUS(Status::Fail);
+        }
+        kernels.push_back(k);
+        kernel_smem.push_back(smem);
+    }
+
+    // 3. device storage: one zero-filled arena, 256-byte aligned slices (the reference does one
+    //    hipMalloc + zero copy per entry, executor_base.cpp:54-63)
+    size_t total = 0;
+    std::vector<size_t> offs;
+    for (size_t i = 0; i < model->storage.size(); i++) {
+        offs.push_back(total);
+        total += align_up(std::max<size_t>(storage_bytes(i), 4), kAlign);
+    }
+    arena_bytes = total;
+    GPU_RETURN_STATUS(reef_malloc(&arena, total));
+    GPU_RETURN_STATUS(reef_memset(arena, 0, total));
+    storage.clear();
+    for (size_t i = 0; i < model->storage.size(); i++) storage.push_back(arena + offs[i]);
+
+    // 4. positional args -> pointers to the storage slots
+    raw_args.clear();
+    raw_args.reserve(model->kernels.size());
+    for (KernelInfo& ki : model->kernels) {
+        std::vector<void*> ka;
+        for (size_t idx : ki.args) ka.push_back(&storage[idx]);
+        raw_args.push_back(ka);
+    }
+    if (s == nullptr) GPU_RETURN_STATUS(reef_stream_create(&s, 0));
+    return Status::Succ;
+}
+
+Status ExecutorBase::load_param_from_file(const char* param_file_path) {
+    std::unique_ptr<ModelParam> params(ModelParamParser::parse_from_file(param_file_path, &err_));
+    if (!params) RETURN_STATUS(Status::NotFound);
+    for (size_t i = 0; i < storage.size(); i++) {
+        const ParamBlob* blob = params->find(model->storage[i].name);
+        if (!blob) continue;
+        size_t bytes = blob->count * sizeof(float);
+        if (bytes > storage_bytes(i)) {
+            err_ = "param " + model->storage[i].name + " is larger than its storage entry";
+            RETURN_STATUS(Status::OutOfRange);
+        }
+        GPU_RETURN_STATUS(reef_memcpy_h2d(storage[i], blob->data, bytes));
+    }
+    return Status::Succ;
+}
+
+Status ExecutorBase::get_data_size(const std::string& key, size_t& size) {
+    size_t idx;
+    if (find_storage_idx(key, idx) != Status::Succ) return Status::NotFound;
+    size = storage_bytes(idx);
+    return Status::Succ;
+}
+
+Status ExecutorBase::set_input(const std::string& key, const std::vector<float>& value) {
+    return set_input(key, (const void*)value.data(), value.size() * sizeof(float));
+}
+
+Status ExecutorBase::set_input(const std::string& key, const void* value, size_t len) {
+    size_t idx;
+    if (find_storage_idx(key, idx) != Status::Succ) return Status::NotFound;
+    return set_input((int)idx, value, len);
+}
+
+Status ExecutorBase::set_input(int idx, const void* value, size_t len) {
+    if (idx < 0 || (size_t)idx >= storage.size()) return Status::OutOfRange;
+    size_t bytes = storage_bytes(idx);
+    if (len < bytes) return Status::OutOfRange;
+    GPU_RETURN_STATUS(reef_memcpy_h2d(storage[idx], value, bytes));
+    return Status::Succ;
+}
+
+Status ExecutorBase::set_input_async(const std::string& key, const void* value, size_t len, GPUStream_t stream) {
+    size_t idx;
+    if (find_storage_idx(key, idx) != Status::Succ) return Status::NotFound;
+    size_t bytes = storage_bytes(idx);
+    if (len < bytes) return Status::OutOfRange;
+    GPU_RETURN_STATUS(reef_memcpy_h2d_async(storage[idx], value, bytes, stream));
+    return Status::Succ;
+}
+
+Status ExecutorBase::get_output(std::vector<float>& out) {
+    size_t idx;
+    if (find_storage_idx("output", idx) != Status::Succ) return Status::NotFound;
+    if (Model::get_stype_size(model->storage[idx].stype) != sizeof(float)) return Status::Fail;
+    out.resize(model->storage[idx].size);
+    return get_data((int)idx, (void*)out.data(), out.size() * sizeof(float));
+}
+
+Status ExecutorBase::get_output(void* out, size_t len) {
+    size_t idx;
+    if (find_storage_idx("output", idx) != Status::Succ) return Status::NotFound;
+    if (len < storage_bytes(idx)) return Status::Fail;
+    return get_data((int)idx, out, len);
+}
+
+Status ExecutorBase::get_output_async(void* out, size_t len, GPUStream_t stream) {
+    size_t idx;
+    if (find_storage_idx("output", idx) != Status::Succ) return Status::NotFound;
+    size_t bytes = storage_bytes(idx);
+    if (len < bytes) return Status::Fail;
+    GPU_RETURN_STATUS(reef_memcpy_d2h_async(out, storage[idx], bytes, stream));
+    return Status::Succ;
+}
+
+Status ExecutorBase::get_data(int idx, void* out, size_t len) {
+    if (idx < 0 || (size_t)idx >= storage.size()) return Status::OutOfRange;
+    size_t bytes = storage_bytes(idx);
+    if (len < bytes) return Status::Fail;
+    GPU_RETURN_STATUS(reef_memcpy_d2h(out, storage[idx], bytes));
+    return Status::Succ;
+}
+
+Status ExecutorBase::find_storage_idx(const std::string& name, size_t& idx) {
+    for (size_t i = 0; i < storage.size(); i++)
+        if (model->storage[i].name == name) {
+            idx = i;
+            return Status::Succ;
+        }
+    return Status::NotFound;
+}
+
+size_t ExecutorBase::num_kernels() const { return model ? model->kernels.size() : 0; }
+void ExecutorBase::set_stream(GPUStream_t stream) { s = stream; }
+GPUStream_t ExecutorBase::stream() const { return s; }
+
+Status ExecutorBase::execute(GPUStream_t stream) { return execute_to((int)num_kernels(), stream); }
+
+Status ExecutorBase::execute_to(int idx, GPUStream_t stream) {
+    if (stream == nullptr) stream = s;
+    if (idx < 0 || (size_t)idx > num_kernels()) return Status::OutOfRange;
+    for (int i = 0; i < idx; i++) RETURN_STATUS(launch_kernel(i, stream));
+    GPU_RETURN_STATUS(reef_stream_sync(stream));
+    return Status::Succ;
+}
+
+Status ExecutorBase::execute_kernel(int idx, GPUStream_t stream) {
+    if (stream == nullptr) stream = s;
+    if (idx < 0 || (size_t)idx >= num_kernels()) return Status::OutOfRange;
+    RETURN_STATUS(launch_kernel(idx, stream));
+    GPU_RETURN_STATUS(reef_stream_sync(stream));
+    return Status::Succ;
+}
+
+Status ExecutorBase::launch_kernel(int i, GPUStream_t stream) {
+    int rc = reef_launch(kernels[i], model->kernels[i].launch_params, kernel_smem[i], stream, raw_args[i].data());
+    if (rc != REEF_SUCC) err_ = reef_last_error();
+    GPU_RETURN_STATUS(rc);
+    return Status::Succ;
+}
+
+// ------------------------------------------------------------------------------------------------
+
+HybridExecutor::HybridExecutor() {}
+
+HybridExecutor::~HybridExecutor() {
+    if (graph) reef_graph_destroy(graph);
+    if (own_flag && preempt_flag) reef_free(preempt_flag);
+    if (task_slot_base) reef_free(task_slot_base);
+    if (dispatch_ctrl) reef_free(dispatch_ctrl);
+    if (task_slots_host) reef_host_free_pinned(task_slots_host);
+}
+
+Status HybridExecutor::load_hybrid_model_from_file(const char* json_file_path, const char* profile_file_path,
+                                                   const char*, const char*) {
+    RETURN_STATUS(load_model_from_file(json_file_path, nullptr));
+    return init_hybrid_executor(profile_file_path);
+}
+
+Status HybridExecutor::init_hybrid_executor(const char* profile_file_path) {
+    const size_t n = model->kernels.size();
+    int num_sms = 0;
+    GPU_RETURN_STATUS(reef_device_num_sms(&num_sms));
+
+    // 1. preempt flag (replaced by the scheduler-wide flag later) and completion counters
+    GPU_RETURN_STATUS(reef_malloc(&preempt_flag, 4));
+    GPU_RETURN_STATUS(reef_memset(preempt_flag, 0, 4));
+    own_flag = true;
+    GPU_RETURN_STATUS(reef_malloc(&task_slot_base, n * 4));
+    GPU_RETURN_STATUS(reef_memset(task_slot_base, 0, n * 4));
+    GPU_RETURN_STATUS(reef_malloc(&dispatch_ctrl, 16));
+    GPU_RETURN_STATUS(reef_memset(dispatch_ctrl, 0, 16));
+    GPU_RETURN_STATUS(reef_host_alloc_pinned((void**)&task_slots_host, n * sizeof(int)));
+    memset(task_slots_host, 0, n * sizeof(int));
+
+    // 2. per-kernel scheduling metadata (reference: trans_executor.cpp:84-99)
+    trans_args.assign(n, KernelArg());
+    for (size_t i = 0; i < n; i++) {
+        KernelArg& ka = trans_args[i];
+        GPU_RETURN_STATUS(reef_kernel_attrs(kernels[i], &ka.resource));
+        ka.block_num = ka.resource.num_blocks;
+        ka.threads = ka.resource.threads;
+        int max_layers = std::max(1, ka.resource.max_blocks_per_sm);
+        int layers = align_up(ka.block_num, num_sms) / num_sms;
+        ka.min_occupancy = std::max(1, std::min(layers, max_layers));
+    }
+
+    // 3. latency profile
+    if (profile_file_path != nullptr && profile_file_path[0] != 0) {
+        model_profile.reset(ModelProfile::from_json(profile_file_path, &err_));
+        if (!model_profile) RETURN_STATUS(Status::NotFound);
+        for (size_t i = 0; i < n; i++) {
+            auto it = model_profile->kernel_latency.find(model->kernels[i].name);
+            if (it != model_profile->kernel_latency.end()) trans_args[i].profile = it->second;
+        }
+    }
+    return Status::Succ;
+}
+
+Status HybridExecutor::set_preempt_flag(GPUDevicePtr_t flag) {
+    if (own_flag && preempt_flag) GPU_RETURN_STATUS(reef_free(preempt_flag));
+    own_flag = false;
+    preempt_flag = flag;
+    return Status::Succ;
+}
+
+Status HybridExecutor::execute_preemptale(GPUStream_t stream) {
+    if (stream == nullptr) stream = s;
+    for (size_t i = 0; i < num_kernels(); i++) RETURN_STATUS(launch_preempt_kernel((int)i, stream));
+    GPU_RETURN_STATUS(reef_stream_sync(stream));
+    return Status::Succ;
+}
+
+Status HybridExecutor::reset_task_slot_async(int kernel_offset, GPUStream_t stream) {
+    GPU_RETURN_STATUS(reef_memset_async(task_slot_base + (size_t)kernel_offset * 4, 0, 4, stream));
+    return Status::Succ;
+}
+
+void HybridExecutor::reset_task_slots(GPUStream_t stream, int from_kernel) {
+    size_t n = num_kernels();
+    if ((size_t)from_kernel >= n) return;
+    reef_memset_async(task_slot_base + (size_t)from_kernel * 4, 0, (n - from_kernel) * 4, stream);
+}
+
+void HybridExecutor::copy_be_kernel_offset(GPUStream_t stream) {
+    reef_memcpy_d2h_async(task_slots_host, task_slot_base, 4 * num_kernels(), stream);
+}
+
+int HybridExecutor::get_be_kernel_offset(int begin) {
+    // first kernel whose completion counter is short of its logical block count
+    for (size_t i = begin; i < num_kernels(); i++)
+        if (task_slots_host[i] < trans_args[i].block_num) return (int)i;
+    return (int)num_kernels();
+}
+
+Status HybridExecutor::launch_preempt_kernel(int i, GPUStream_t stream) {
+    int rc = reef_launch_be(kernels[i], model->kernels[i].launch_params, kernel_smem[i], stream, preempt_flag,
+                            task_slot_base + (size_t)i * 4, raw_args[i].data());
+    if (rc != REEF_SUCC) err_ = reef_last_error();
+    GPU_RETURN_STATUS(rc);
+    return Status::Succ;
+}
+
+Status HybridExecutor::launch_dispatch(int rt_idx, HybridExecutor* be, int be_idx, int be_block_offset,
+                                       int be_block_num, int sm_partition, int occupancy, GPUStream_t stream) {
+    int rc = reef_dispatch(kernels[rt_idx], raw_args[rt_idx].data(), be ? be->kernels[be_idx] : nullptr,
+                           be ? be->raw_args[be_idx].data() : nullptr, be_block_offset, be_block_num, sm_partition,
+                           occupancy, preempt_flag, be ? be->task_slot_base + (size_t)be_idx * 4 : 0, dispatch_ctrl,
+                           stream);
+    if (rc != REEF_SUCC) err_ = reef_last_error();
+    GPU_RETURN_STATUS(rc);
+    return Status::Succ;
+}
+
+Status HybridExecutor::execute_graph(GPUStream_t stream) {
+    if (graph == nullptr || graph_stream != stream) {
+        if (graph) reef_graph_destroy(graph);
+        graph = nullptr;
+        GPU_RETURN_STATUS(reef_graph_begin(stream));
+        Status st = Status::Succ;
+        for (size_t i = 0; i < num_kernels() && st == Status::Succ; i++) st = ExecutorBase::launch_kernel((int)i, stream);
+        int rc = reef_graph_end(stream, &graph);
+        if (st != Status::Succ) return st;
+        GPU_RETURN_STATUS(rc);
+        graph_stream = stream;
+    }
+    GPU_RETURN_STATUS(reef_graph_launch(graph, stream));
+    return Status::Succ;
+}
+
+Status HybridExecutor::execute_dispatch(GPUStream_t stream) {
+    if (stream == nullptr) stream = s;
+    int num_sms = 0;
+    GPU_RETURN_STATUS(reef_device_num_sms(&num_sms));
+    for (size_t i = 0; i < num_kernels(); i++)
+        RETURN_STATUS(launch_dispatch((int)i, nullptr, 0, 0, 0, num_sms, trans_args[i].min_occupancy, stream));
+    GPU_RETURN_STATUS(reef_stream_sync(stream));
+    return Status::Succ;
+}
+
+static void busy_wait_us(int us) {
+    auto t0 = std::chrono::steady_clock::now();
+    while (std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count() < us) {
+    }
+}
+
+Status HybridExecutor::execute_preempt_resume(int delay_us, int* restarts, int* first_incomplete) {
+    GPUStream_t flag_stream;
+    GPU_RETURN_STATUS(reef_stream_create(&flag_stream, 1));
+    const int n = (int)num_kernels();
+    int from = 0, rounds = 0;
+    if (first_incomplete) *first_incomplete = -1;
+    GPU_RETURN_STATUS(reef_write32_async(flag_stream, preempt_flag, 0));
+    GPU_RETURN_STATUS(reef_stream_sync(flag_stream));
+    reset_task_slots(s, 0);
+    Status st = Status::Succ;
+    while (from < n) {
+        for (int i = from; i < n && st == Status::Succ; i++) st = launch_preempt_kernel(i, s);
+        if (st != Status::Succ) break;
+        const bool preempt = rounds < 8;
+        if (preempt) {
+            busy_wait_us(delay_us << std::min(rounds, 6));
+            reef_write32_async(flag_stream, preempt_flag, 1);
+            reef_stream_sync(flag_stream);
+        }
+        if (reef_preempt_wait(s, 5000000) != REEF_SUCC) { st = Status::Timeout; break; }
+        copy_be_kernel_offset(s);
+        GPU_RETURN_STATUS(reef_stream_sync(s));
+        int k = get_be_kernel_offset(from);
+        if (preempt) {
+            reef_write32_async(flag_stream, preempt_flag, 0);
+            reef_stream_sync(flag_stream);
+        }
+        if (k >= n) break;
+        if (rounds == 0 && first_incomplete) *first_incomplete = k;
+        reset_task_slots(s, k);
+        from = k;
+        rounds++;
+    }
+    if (restarts) *restarts = rounds;
+    reef_stream_destroy(flag_stream);
+    return st;
+}
+
+Status HybridExecutor::profile_kernels(int iters, float* us) {
+    reef_event_t a, b;
+    GPU_RETURN_STATUS(reef_event_create(&a));
+    GPU_RETURN_STATUS(reef_event_create(&b));
+    Status st = Status::Succ;
+    for (size_t i = 0; i < num_kernels() && st == Status::Succ; i++) {
+        st = ExecutorBase::launch_kernel((int)i, s);   // warm
+        reef_event_record(a, s);
+        for (int r = 0; r < iters && st == Status::Succ; r++) st = ExecutorBase::launch_kernel((int)i, s);
+        reef_event_record(b, s);
+        reef_event_sync(b);
+        float ms = 0;
+        reef_event_elapsed_ms(a, b, &ms);
+        us[i] = ms * 1000.f / (float)std::max(1, iters);
+    }
+    reef_event_destroy(a);
+    reef_event_destroy(b);
+    return st;
+}
+
+Status HybridExecutor::profile_wave(int idx, int occupancy, int iters, float* us) {
+    if (idx < 0 || (size_t)idx >= num_kernels() || occupancy < 1) return Status::OutOfRange;
+    int num_sms = 0;
+    GPU_RETURN_STATUS(reef_device_num_sms(&num_sms));
+    int blocks = std::min(trans_args[idx].block_num, num_sms * occupancy);
+    reef_event_t a, b;
+    GPU_RETURN_STATUS(reef_event_create(&a));
+    GPU_RETURN_STATUS(reef_event_create(&b));
+    Status st = Status::Succ;
+    auto once = [&]() {
+        int rc = reef_dispatch(nullptr, nullptr, kernels[idx], raw_args[idx].data(), 0, blocks, 0, occupancy,
+                               preempt_flag, task_slot_base + (size_t)idx * 4, dispatch_ctrl, s);
+        if (rc != REEF_SUCC) { err_ = reef_last_error(); st = (Status)rc; }
+    };
+    once();
+    reef_event_record(a, s);
+    for (int r = 0; r < iters && st == Status::Succ; r++) once();
+    reef_event_record(b, s);
+    reef_event_sync(b);
+    float ms = 0;
+    reef_event_elapsed_ms(a, b, &ms);
+    *us = ms * 1000.f / (float)std::max(1, iters);
+    reset_task_slots(s, 0);
+    reef_stream_sync(s);
+    reef_event_destroy(a);
+    reef_event_destroy(b);
+    return st;
+}
+
+}  // namespace executor
+}  // namespace reef

@@ -1,0 +1,143 @@
+// Executors: own a model's device storage and launch its kernels through the C-ABI device layer.
+//
+//   ExecutorBase   raw kernels in json order                 (reference: src/reef/executor/executor_base.{h,cpp})
+//   HybridExecutor + per-kernel scheduling metadata (KernelArg: logical blocks, minimal occupancy,
+//                  resources, latency profile), the best-effort flavour with preempt flag and
+//                  completion counters, the dispatcher launch, and a CUDA-graph fast path
+//                  (reference: src/reef/executor/trans_executor.{h,cpp}, hybrid_executor.{h,cpp})
+#pragma once
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../../include/reef_cuda.h"
+#include "common.h"
+#include "model.h"
+
+namespace reef {
+namespace server {
+class REEFScheduler;
+}
+namespace executor {
+
+typedef reef_dptr_t GPUDevicePtr_t;
+typedef reef_kernel_t GPUFunction_t;
+typedef reef_module_t GPUModule_t;
+typedef reef_stream_t GPUStream_t;
+
+class ExecutorBase {
+public:
+    ExecutorBase();
+    virtual ~ExecutorBase();
+
+    // co_file_path is accepted for signature parity; kernels come from the built-in registry.
+    Status load_model_from_file(const char* json_file_path, const char* co_file_path = nullptr);
+    virtual Status load_model_from_GPU_module(const char* json_file_path, GPUModule_t module);
+    Status load_param_from_file(const char* param_file_path);
+
+    Status set_input(const std::string& key, const std::vector<float>& value);
+    Status set_input(int idx, const void* value, size_t len);
+    Status set_input(const std::string& key, const void* value, size_t len);
+    Status get_data_size(const std::string& key, size_t& size);
+    Status get_output(std::vector<float>& out);
+    Status get_output(void* out, size_t len);
+    Status get_data(int idx, void* out, size_t len);
+    // asynchronous I/O on a stream from/to pinned host memory (no reference counterpart: the
+    // reference copies synchronously on the default stream, executor_base.cpp:112-116)
+    Status set_input_async(const std::string& key, const void* value, size_t len, GPUStream_t stream);
+    Status get_output_async(void* out, size_t len, GPUStream_t stream);
+
+    Status execute(GPUStream_t stream = nullptr);
+    Status execute_to(int idx, GPUStream_t stream = nullptr);
+    Status execute_kernel(int idx, GPUStream_t stream = nullptr);
+    Status execute_kernel_async(int idx) { return launch_kernel(idx, s); }   // no sync
+    size_t num_kernels() const;
+
+    void set_stream(GPUStream_t stream);
+    GPUStream_t stream() const;
+    const std::string& error() const { return err_; }
+
+    std::unique_ptr<Model> model;
+
+protected:
+    Status init_executor_base(const char* json_file_path, GPUModule_t module);
+    virtual Status launch_kernel(int kernel_offset, GPUStream_t stream);
+    Status find_storage_idx(const std::string& name, size_t& idx);
+    size_t storage_bytes(size_t idx) const;
+
+    std::vector<GPUDevicePtr_t> storage;            // one device pointer per storage entry (views into one arena)
+    std::vector<GPUFunction_t> kernels;             // per kernel call
+    std::vector<uint32_t> kernel_smem;              // per kernel call, from "shared_memory"
+    std::vector<std::vector<void*>> raw_args;       // raw_args[k][j] = &storage[idx]
+    GPUDevicePtr_t arena = 0;
+    size_t arena_bytes = 0;
+    GPUModule_t base_mod = nullptr;
+    bool own_module = false;
+    GPUStream_t s = nullptr;
+    std::string err_;
+};
+
+class HybridExecutor : public ExecutorBase {
+    friend class server::REEFScheduler;
+
+public:
+    // reference: trans_executor.h:47-63
+    class KernelArg {
+    public:
+        int block_num = 0;        // logical thread blocks of the kernel
+        int block_offset = 0;
+        int threads = 0;
+        int min_occupancy = 1;    // minimal blocks/SM the real-time kernel needs to finish in one wave
+        reef_kernel_attrs_t resource{};
+        KernelProfile profile;
+    };
+
+    HybridExecutor();
+    virtual ~HybridExecutor();
+
+    // The three code-object paths of the reference signature are accepted and ignored.
+    Status load_hybrid_model_from_file(const char* json_file_path, const char* profile_file_path,
+                                       const char* trans_co_file_path = nullptr,
+                                       const char* preempt_co_file_path = nullptr);
+
+    Status execute_preemptale(GPUStream_t stream = nullptr);     // (sic) reference spelling
+    Status set_preempt_flag(GPUDevicePtr_t flag);
+    Status reset_task_slot_async(int kernel_offset, GPUStream_t stream);
+    void reset_task_slots(GPUStream_t stream, int from_kernel = 0);
+    void copy_be_kernel_offset(GPUStream_t stream);
+    int get_be_kernel_offset(int begin);
+
+    Status launch_preempt_kernel(int kernel_offset, GPUStream_t stream);
+    // dispatcher launch of kernel `rt_idx`, padded with logical blocks of `be`'s kernel `be_idx`
+    Status launch_dispatch(int rt_idx, HybridExecutor* be, int be_idx, int be_block_offset, int be_block_num,
+                           int sm_partition, int occupancy, GPUStream_t stream);
+    // CUDA graph of the whole kernel list on `stream` (captured lazily on first use)
+    Status execute_graph(GPUStream_t stream);
+    // every kernel through the dispatcher without a best-effort partner, then sync
+    Status execute_dispatch(GPUStream_t stream = nullptr);
+    // best-effort run, flag raised after delay_us, resumed from the first incomplete kernel until done
+    Status execute_preempt_resume(int delay_us, int* restarts, int* first_incomplete);
+    // device time of each kernel (us, CUDA events, average of iters)
+    Status profile_kernels(int iters, float* us);
+    // one persistent wave of kernel idx: sms*occupancy logical blocks through the dispatcher (us)
+    Status profile_wave(int idx, int occupancy, int iters, float* us);
+    const int* host_task_slots() const { return task_slots_host; }
+
+    std::vector<KernelArg> trans_args;
+    const ModelProfile* profile() const { return model_profile.get(); }
+
+protected:
+    Status init_hybrid_executor(const char* profile_file_path);
+
+    GPUDevicePtr_t preempt_flag = 0;
+    bool own_flag = false;
+    GPUDevicePtr_t task_slot_base = 0;
+    GPUDevicePtr_t dispatch_ctrl = 0;
+    int* task_slots_host = nullptr;
+    std::shared_ptr<ModelProfile> model_profile;
+    reef_graph_t graph = nullptr;
+    GPUStream_t graph_stream = nullptr;
+};
+
+}  // namespace executor
+}  // namespace reef

@@ -1,0 +1,176 @@
+// REEFScheduler: model pool, one real-time queue and up to 32 best-effort queues, one scheduler
+// thread per GPU, reset-style preemption and dynamic kernel padding
+// (reference: src/reef/server/scheduler.{h,cpp}; public surface scheduler.h:68-126).
+//
+// What changes on CUDA:
+//  * hipStreamCreateWithWindowSize / hipStreamClearQueue (reference: scheduler.cpp:45-50,316):
+//    CUDA cannot bound or clear a stream's queue, so each best-effort queue keeps at most
+//    `be_stream_device_queue_cap` kernels in flight (tracked with events) and the rest of the
+//    task stays on the host, where "clearing" is free.
+//  * hipResetWavefronts (reference: scheduler.cpp:332-333): running best-effort blocks cannot be
+//    killed; they leave at their next preempt-flag poll (block entry and loop heads).
+//  * merge_framework_N proxy kernels (reference: scheduler.cpp:613-649): one persistent dispatcher
+//    kernel (reef_dispatch).
+#pragma once
+#include <atomic>
+#include <chrono>
+#include <condition_variable>
+#include <deque>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+#include "common.h"
+#include "executor.h"
+#include "threadsafe_queue.h"
+
+namespace reef {
+namespace server {
+
+class REEFScheduler {
+    struct Model;
+
+public:
+    typedef uint32_t ModelID;
+    typedef uint32_t QueueID;
+    typedef uint32_t TaskID;
+
+    enum ScheduleMode {
+        NoPreempt,    // real-time waits for running best-effort kernels
+        MultiStream,  // plain concurrent streams
+        WaitPreempt,  // flag + wait for the device to drain, progress from completion counters
+        REEF,         // flag preemption + dynamic kernel padding
+        Reset         // flag preemption without padding
+    };
+    enum TaskQueueType { RealTimeQueue, BestEffortQueue };
+    enum TaskState { Init, Waiting, Executing, Finish };
+
+    struct Task {
+        friend class REEFScheduler;
+
+    private:
+        std::shared_ptr<Model> model;
+        QueueID qid;
+        TaskID id;
+        std::atomic<int> state;
+        int launch_offset;   // next kernel to hand to the stream
+        int kernel_offset;   // first kernel not known to be complete
+        int block_offset;    // logical blocks of kernel_offset already done by padding
+        std::mutex mtx;
+        std::condition_variable cv;
+        std::chrono::system_clock::time_point submit, start, end;
+        bool preempted;
+        bool padding;
+        bool padding_to_finish;
+        bool needs_recover;
+
+    public:
+        bool is_preempted() const { return preempted; }
+        bool is_padded() const { return padding; }
+        bool is_padded_to_complete() const { return padding_to_finish; }
+        TaskState get_state() const { return (TaskState)state.load(); }
+        std::vector<std::chrono::system_clock::time_point> get_timestamp() const { return {submit, start, end}; }
+    };
+
+    explicit REEFScheduler(ScheduleMode _mode = ScheduleMode::REEF, int device = 0);
+    ~REEFScheduler();
+
+    Status load_model(const std::string& model_dir, const std::string& model_name, ModelID& mid);
+    Status load_model(const std::string& rt_co_path, const std::string& be_co_path, const std::string& json_path,
+                      const std::string& profile_path, const std::string& param_path, ModelID& mid);
+    Status create_queue(const TaskQueueType& qtp, QueueID& qid);
+    Status bind_model_queue(const QueueID& qid, const ModelID& mid);
+    Status get_data_size(ModelID mid, const std::string& name, size_t& size);
+    Status set_input(ModelID mid, const void* data, size_t len, const std::string& name = "data");
+    Status get_output(ModelID mid, void* data, size_t len, const std::string& name = "output");
+    Status new_task(const ModelID& mid, TaskID& tid);
+    Status wait_task(TaskID tid);
+    Status get_task(TaskID tid, std::shared_ptr<Task>& t);
+    ScheduleMode sche_mode() const { return mode; }
+    void set_wait_sync(bool value) { wait_sync = value; }
+    void set_be_stream_cap(int value) { be_stream_device_queue_cap = value < 1 ? 1 : value; }
+    // real-time tasks that find no best-effort work replay a CUDA graph of the model (default on)
+    void set_rt_graph(bool value) { rt_graph = value; }
+    Status run();
+    Status shutdown();
+
+    int64_t avg_preempt_latency() const;       // microseconds, as in the reference
+    int64_t avg_kernel_sel_latency() const;    // nanoseconds per real-time kernel
+    // finer-grained statistics (no reference counterpart)
+    struct Stats {
+        uint64_t preempt_count, preempt_ns_sum, preempt_ns_max;
+        uint64_t rt_tasks, be_tasks, be_tasks_padded_to_finish, padded_kernels, padded_blocks;
+    };
+    Stats stats() const;
+    const std::string& error() const { return err_; }
+
+private:
+    struct Model {
+        executor::HybridExecutor executor;
+        QueueID qid;
+    };
+    struct InFlight {
+        reef_event_t ev;
+        int kernel;
+    };
+    struct TaskQueue {
+        ThreadSafeQueue<std::shared_ptr<Task>> task_queue;
+        executor::GPUStream_t stream = nullptr;
+        std::deque<InFlight> inflight;
+        std::vector<reef_event_t> free_events;
+    };
+
+    Status create_task_queue(std::shared_ptr<TaskQueue>& ret, bool rt);
+    void loop_body();
+    void execute_be_task(std::shared_ptr<Task>& task, std::shared_ptr<TaskQueue>& tqueue);
+    void execute_rt_task(std::shared_ptr<Task>& task);
+    void preempt_be_tasks();
+    void reset_preempt_flag_async();
+    void preempt_reset();
+    void preempt_wait();
+    void dynamic_kernel_padding(std::shared_ptr<Task>& rt_task);
+    void retire(TaskQueue& q, Task& t);
+    void finish_task(std::shared_ptr<Task>& t);
+    bool any_be_waiting();
+
+    ScheduleMode mode;
+    int device;
+    int num_sms = 0;
+    static const size_t model_pool_capacity = 1024;
+    std::atomic_uint32_t model_pool_size;
+    std::vector<std::shared_ptr<Model>> model_pool;
+
+    std::atomic_uint32_t task_idx_pool;
+    std::unordered_map<TaskID, std::shared_ptr<Task>> task_pool;
+    std::mutex task_pool_mtx;
+
+    static const size_t max_num_be_queues = 32;
+    static const QueueID rt_queue_id = 32;
+    std::mutex be_queues_mtx;
+    std::vector<std::shared_ptr<TaskQueue>> be_queues;
+    std::atomic_uint32_t be_queue_cnt;
+    std::shared_ptr<TaskQueue> rt_queue;
+    std::mutex task_cnt_mtx;
+    std::condition_variable task_cnt_cv;
+    bool wait_sync;
+    bool rt_graph;
+
+    std::unique_ptr<std::thread> scheduler;
+    executor::GPUStream_t preempt_stream = nullptr;
+    executor::GPUDevicePtr_t preempt_flag = 0;
+    bool preempted;
+    int be_stream_device_queue_cap;
+    std::atomic_bool _shutdown;
+    std::atomic<uint64_t> pending_tasks;
+
+    uint64_t preempt_count, preempt_latency_sum, preempt_latency_max;
+    uint64_t kernel_sel_count, kernel_sel_latency_sum;
+    uint64_t n_rt_tasks, n_be_tasks, n_be_padded_finish, n_padded_kernels, n_padded_blocks;
+    std::string err_;
+};
+
+}  // namespace server
+}  // namespace reef

@@ -1,0 +1,485 @@
+// Kernel registry: resolves "<family>__<key><int>_..." names from <model>.json to hand-written
+// sm_100a kernels, plans their launch geometry, and launches them in the three flavours
+// (plain, best-effort, dispatcher).  Replaces GPUModuleGetFunction / GPUModuleLaunchKernel on a
+// per-model code object (reference: src/reef/executor/executor_base.cpp:47-52,211-223,
+// src/reef/executor/hybrid_executor.cpp:153-163, src/reef/server/scheduler.cpp:613-649).
+#include "registry.h"
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+
+#include "conv_simt.cuh"
+#include "simple.cuh"
+
+namespace reef {
+
+static thread_local std::string g_err;
+void set_error(const std::string& s) { g_err = s; }
+const char* last_error() { return g_err.c_str(); }
+
+// ------------------------------------------------------------------------------------------
+// name grammar
+// ------------------------------------------------------------------------------------------
+struct Attrs {
+    std::map<std::string, long long> kv;
+    bool has(const char* k) const { return kv.count(k) != 0; }
+    long long get(const char* k, long long dflt) const {
+        auto it = kv.find(k);
+        return it == kv.end() ? dflt : it->second;
+    }
+    bool need(const char* k, int* out) const {
+        auto it = kv.find(k);
+        if (it == kv.end()) return false;
+        *out = (int)it->second;
+        return true;
+    }
+};
+
+static bool parse_name(const std::string& name, std::string* op, Attrs* attrs) {
+    size_t pos = name.find("__");
+    if (pos == std::string::npos) {
+        *op = name;
+        return true;
+    }
+    *op = name.substr(0, pos);
+    std::string tail = name.substr(pos + 2);
+    size_t i = 0;
+    while (i < tail.size()) {
+        size_t j = tail.find('_', i);
+        if (j == std::string::npos) j = tail.size();
+        std::string tok = tail.substr(i, j - i);
+        size_t d = 0;
+        while (d < tok.size() && !(tok[d] >= '0' && tok[d] <= '9')) d++;
+        if (d == 0 || d == tok.size()) return false;
+        attrs->kv[tok.substr(0, d)] = atoll(tok.c_str() + d);
+        i = j + 1;
+    }
+    return true;
+}
+
+static int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Build the device task + launch plan for a name.  Returns REEF_SUCC / REEF_NOT_FOUND.
+static int build_spec(const std::string& name, KernelSpec* s) {
+    std::string op;
+    Attrs a;
+    if (!parse_name(name, &op, &a)) {
+        set_error("malformed kernel name: " + name);
+        return REEF_NOT_FOUND;
+    }
+    memset(&s->task, 0, sizeof(KTask));
+    s->name = name;
+    s->block[0] = kThreads; s->block[1] = 1; s->block[2] = 1;
+    s->dyn_smem = 0;
+    s->flops = 0;
+    s->bytes = 0;
+    s->tensor_core = 0;
+    KTask& t = s->task;
+
+    if (op == "add" || op == "multiply") {
+        // reference: resource/mocked_kernel/mocked_kernel.json launch_params [64,1,1,4,8,4]
+        t.family = op == "add" ? F_MOCK_ADD : F_MOCK_MUL;
+        t.nblocks = 64;
+        s->block[0] = 4; s->block[1] = 8; s->block[2] = 4;
+        s->nargs = 3;
+        s->bytes = 4.0 * (128 + 2 * 8192);
+        return REEF_SUCC;
+    }
+    if (op == "fused_add") {
+        EltP& p = t.p.elt;
+        if (!a.need("c", &p.c) || !a.need("hw", &p.n)) goto bad;
+        t.family = F_FUSED_ADD_NCHW;
+        t.nblocks = ceil_div(p.c * p.n, kEltPerBlock);
+        s->nargs = 3;
+        s->bytes = 4.0 * (2.0 * p.c * p.n + p.c);
+        return REEF_SUCC;
+    }
+    if (op == "fused_add_nn_relu") {
+        EltP& p = t.p.elt;
+        if (!a.need("c", &p.c) || !a.need("n", &p.n)) goto bad;
+        p.ics = (int)a.get("ics", p.c);
+        p.ioff = (int)a.get("ioff", 0);
+        if ((p.c | p.ics | p.ioff) & 3) goto bad;
+        t.family = F_BIAS_RELU;
+        t.nblocks = ceil_div(p.c * p.n, kEltPerBlock);
+        s->nargs = 3;
+        s->bytes = 4.0 * (2.0 * p.c * p.n + p.c);
+        return REEF_SUCC;
+    }
+    if (op == "fused_nn_batch_flatten") {
+        EltP& p = t.p.elt;
+        if (!a.need("n", &p.n)) goto bad;
+        t.family = F_COPY;
+        t.nblocks = ceil_div(p.n, kEltPerBlock);
+        s->nargs = 2;
+        s->bytes = 8.0 * p.n;
+        return REEF_SUCC;
+    }
+    if (op == "fused_nn_global_avg_pool2d") {
+        EltP& p = t.p.elt;
+        if (!a.need("c", &p.c) || !a.need("hw", &p.n)) goto bad;
+        t.family = F_GLOBAL_AVG_POOL;
+        t.nblocks = ceil_div(p.c, 32);
+        s->dyn_smem = 8 * 32 * 4;
+        s->nargs = 2;
+        s->bytes = 4.0 * ((double)p.c * p.n + p.c);
+        return REEF_SUCC;
+    }
+    if (op == "fused_nn_max_pool2d" || op == "fused_nn_max_pool2d_add_nn_relu" || op == "fused_nn_avg_pool2d") {
+        PoolP& p = t.p.pool;
+        if (!a.need("c", &p.c) || !a.need("hi", &p.hi) || !a.need("wi", &p.wi) || !a.need("k", &p.k) ||
+            !a.need("s", &p.s) || !a.need("p", &p.p) || !a.need("ho", &p.ho) || !a.need("wo", &p.wo))
+            goto bad;
+        p.ics = (int)a.get("ics", p.c); p.ioff = (int)a.get("ioff", 0);
+        p.ocs = (int)a.get("ocs", p.c); p.ooff = (int)a.get("ooff", 0);
+        p.cip = (int)a.get("cip", 1);
+        p.has_bias = op == "fused_nn_max_pool2d_add_nn_relu";
+        if ((p.c | p.ics | p.ioff | p.ocs | p.ooff) & 3) goto bad;
+        t.family = op == "fused_nn_avg_pool2d" ? F_AVG_POOL : F_MAX_POOL;
+        t.nblocks = ceil_div(p.ho * p.wo * (p.c / 4), kPoolItemsPerBlock);
+        s->nargs = p.has_bias ? 3 : 2;
+        s->bytes = 4.0 * ((double)p.c * p.hi * p.wi + (double)p.c * p.ho * p.wo + (p.has_bias ? p.c : 0));
+        return REEF_SUCC;
+    }
+    if (op == "fused_nn_dense_add" || op == "fused_nn_dense_add_nn_relu") {
+        DenseP& p = t.p.dense;
+        if (!a.need("k", &p.k) || !a.need("n", &p.n)) goto bad;
+        p.relu = op == "fused_nn_dense_add_nn_relu";
+        t.family = F_DENSE;
+        t.nblocks = ceil_div(p.n, kDenseRowsPerBlock);
+        s->nargs = 4;
+        s->flops = 2.0 * p.k * p.n;
+        s->bytes = 4.0 * ((double)p.k * p.n + p.k + 2.0 * p.n);
+        return REEF_SUCC;
+    }
+    if (op == "fused_nn_softmax") {
+        SoftmaxP& p = t.p.softmax;
+        if (!a.need("n", &p.n)) goto bad;
+        p.rows = (int)a.get("rows", 1);
+        t.family = F_SOFTMAX;
+        t.nblocks = p.rows;
+        s->dyn_smem = 16 * 4;
+        s->nargs = 2;
+        s->bytes = 8.0 * p.rows * p.n;
+        return REEF_SUCC;
+    }
+    if (op.rfind("fused_nn_conv2d", 0) == 0) {
+        ConvP& p = t.p.conv;
+        std::string tail = op.substr(strlen("fused_nn_conv2d"));
+        p.ep = 0;
+        p.i_res = p.i_bias = p.i_gamma = p.i_beta = -1;
+        bool relu = false;
+        const std::string r = "_nn_relu";
+        if (tail.size() >= r.size() && tail.compare(tail.size() - r.size(), r.size(), r) == 0) {
+            relu = true;
+            tail = tail.substr(0, tail.size() - r.size());
+        }
+        int nargs = 3;
+        if (tail == "") {
+        } else if (tail == "_add") {
+            if (relu) { p.ep |= EP_BIAS; p.i_bias = 3; } else { p.ep |= EP_RES; p.i_res = 3; }
+            nargs = 4;
+        } else if (tail == "_add_add") {
+            p.ep |= EP_RES | EP_BIAS; p.i_res = 3; p.i_bias = 4;
+            nargs = 5;
+        } else if (tail == "_add_multiply_add") {
+            p.ep |= EP_RES | EP_GB; p.i_res = 3; p.i_gamma = 4; p.i_beta = 5;
+            nargs = 6;
+        } else {
+            set_error("unknown conv2d family: " + op);
+            return REEF_NOT_FOUND;
+        }
+        if (relu) p.ep |= EP_RELU;
+        if (!a.need("ci", &p.ci) || !a.need("hi", &p.hi) || !a.need("wi", &p.wi) || !a.need("co", &p.co) ||
+            !a.need("kh", &p.kh) || !a.need("kw", &p.kw) || !a.need("sh", &p.sh) || !a.need("sw", &p.sw) ||
+            !a.need("ph", &p.ph) || !a.need("pw", &p.pw))
+            goto bad;
+        p.nchw = (int)a.get("nchw", 0);
+        p.ics = (int)a.get("ics", p.ci); p.ioff = (int)a.get("ioff", 0);
+        p.ocs = (int)a.get("ocs", p.co); p.ooff = (int)a.get("ooff", 0);
+        p.ho = (p.hi + 2 * p.ph - p.kh) / p.sh + 1;
+        p.wo = (p.wi + 2 * p.pw - p.kw) / p.sw + 1;
+        p.ktot = p.kh * p.kw * p.ci;
+        p.ptot = p.ho * p.wo;
+        if (p.ho <= 0 || p.wo <= 0) goto bad;
+        if ((p.co | p.ocs | p.ooff) & 3) goto bad;
+        if (!p.nchw && (p.ci % CBK) == 0 && ((p.ics | p.ioff) & 3)) goto bad;
+        s->nargs = nargs;
+        s->flops = 2.0 * p.co * (double)p.ktot * p.ptot;
+        s->bytes = 4.0 * ((double)p.ci * p.hi * p.wi + (double)p.co * p.ktot + (double)p.co * p.ptot *
+                          ((p.ep & EP_RES) ? 2.0 : 1.0) + p.co * ((p.ep & EP_GB) ? 2.0 : ((p.ep & EP_BIAS) ? 1.0 : 0.0)));
+        int impl = (int)a.get("v", 0);
+        if (impl == 0) {
+            t.family = F_CONV_SIMT;
+            p.tiles_p = ceil_div(p.ptot, CBM);
+            p.tiles_c = ceil_div(p.co, CBN);
+            t.nblocks = p.tiles_p * p.tiles_c;
+            s->dyn_smem = kConvSimtSmem;
+            return REEF_SUCC;
+        }
+        set_error("unknown conv2d variant in: " + name);
+        return REEF_NOT_FOUND;
+    }
+    set_error("unknown kernel family: " + op);
+    return REEF_NOT_FOUND;
+bad:
+    set_error("unsupported shape or missing attribute in kernel name: " + name);
+    return REEF_NOT_FOUND;
+}
+
+int plan_kernel(const char* name, KernelSpec* s) {
+    int rc = build_spec(name, s);
+    if (rc != REEF_SUCC) return rc;
+    s->grid[0] = (uint32_t)s->task.nblocks;
+    s->grid[1] = 1;
+    s->grid[2] = 1;
+    return REEF_SUCC;
+}
+
+// ------------------------------------------------------------------------------------------
+// device flavours
+// ------------------------------------------------------------------------------------------
+template <int F>
+__device__ __forceinline__ bool run_body(const KTask& t, int vb, unsigned char* smem, const int* flag) {
+    if (F == F_MOCK_ADD) return body_mock<false>(t, vb, smem, flag);
+    if (F == F_MOCK_MUL) return body_mock<true>(t, vb, smem, flag);
+    if (F == F_FUSED_ADD_NCHW) return body_fused_add_nchw(t, vb, smem, flag);
+    if (F == F_BIAS_RELU) return body_bias_relu(t, vb, smem, flag);
+    if (F == F_CONV_SIMT) return body_conv_simt(t, vb, smem, flag);
+    if (F == F_MAX_POOL) return body_pool<true>(t, vb, smem, flag);
+    if (F == F_AVG_POOL) return body_pool<false>(t, vb, smem, flag);
+    if (F == F_GLOBAL_AVG_POOL) return body_gap(t, vb, smem, flag);
+    if (F == F_COPY) return body_copy(t, vb, smem, flag);
+    if (F == F_DENSE) return body_dense(t, vb, smem, flag);
+    if (F == F_SOFTMAX) return body_softmax(t, vb, smem, flag);
+    return true;
+}
+
+__device__ __forceinline__ bool run_any(const KTask& t, int vb, unsigned char* smem, const int* flag) {
+    switch (t.family) {
+        case F_MOCK_ADD: return run_body<F_MOCK_ADD>(t, vb, smem, flag);
+        case F_MOCK_MUL: return run_body<F_MOCK_MUL>(t, vb, smem, flag);
+        case F_FUSED_ADD_NCHW: return run_body<F_FUSED_ADD_NCHW>(t, vb, smem, flag);
+        case F_BIAS_RELU: return run_body<F_BIAS_RELU>(t, vb, smem, flag);
+        case F_CONV_SIMT: return run_body<F_CONV_SIMT>(t, vb, smem, flag);
+        case F_MAX_POOL: return run_body<F_MAX_POOL>(t, vb, smem, flag);
+        case F_AVG_POOL: return run_body<F_AVG_POOL>(t, vb, smem, flag);
+        case F_GLOBAL_AVG_POOL: return run_body<F_GLOBAL_AVG_POOL>(t, vb, smem, flag);
+        case F_COPY: return run_body<F_COPY>(t, vb, smem, flag);
+        case F_DENSE: return run_body<F_DENSE>(t, vb, smem, flag);
+        case F_SOFTMAX: return run_body<F_SOFTMAX>(t, vb, smem, flag);
+        default: return true;
+    }
+}
+
+extern __shared__ __align__(16) unsigned char reef_dyn_smem[];
+
+template <int F>
+__global__ void __launch_bounds__(kThreads) k_plain(const __grid_constant__ KTask t) {
+    run_body<F>(t, blockIdx.x, reef_dyn_smem, nullptr);
+}
+
+// Best-effort flavour (reference wrapper: script/best_effort_kernel.py:22-33): leave at once when
+// the preempt flag is up; bodies poll it again at their loop heads; a block that ran to the end
+// (all of its stores issued, fenced) adds one to the kernel's completion counter.
+template <int F>
+__global__ void __launch_bounds__(kThreads) k_be(const __grid_constant__ KTask t, const int* __restrict__ flag,
+                                                 int* __restrict__ task_slot) {
+    if (ld_flag(flag)) return;
+    const bool done = run_body<F>(t, blockIdx.x, reef_dyn_smem, flag);
+    __syncthreads();
+    if (done && threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
+        __threadfence();
+        atomicAdd(task_slot, 1);
+    }
+}
+
+// Persistent dispatcher (dynamic kernel padding).  ctrl[0] = real-time ticket, ctrl[1] =
+// best-effort ticket, ctrl[2] = drained blocks.  The role of a block comes from the SM it is
+// resident on, not from its index: the reference assumes round-robin block placement over CUs
+// (reference: resource/mocked_kernel/mocked_kernel.trans.cu:112-186, blockIdx.x % 60), which
+// CUDA does not promise; tickets make the result independent of placement.
+__device__ __forceinline__ int next_ticket(int* counter, int* s_slot) {
+    __syncthreads();
+    if (threadIdx.x == 0) *s_slot = atomicAdd(counter, 1);
+    __syncthreads();
+    return *s_slot;
+}
+
+__global__ void __launch_bounds__(kThreads) k_dispatch(const __grid_constant__ KTask rt, const __grid_constant__ KTask be,
+                                                       int be_off, int be_num, int sm_partition,
+                                                       int* __restrict__ be_slot, int* __restrict__ ctrl) {
+    __shared__ int s_ticket;
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    const bool rt_first = (int)smid < sm_partition;
+
+#pragma unroll 1
+    for (int phase = 0; phase < 2; phase++) {
+        const bool do_rt = (phase == 0) == rt_first;
+        if (do_rt) {
+            for (;;) {
+                int v = next_ticket(&ctrl[0], &s_ticket);
+                if (v >= rt.nblocks) break;
+                run_any(rt, v, reef_dyn_smem, nullptr);
+            }
+        } else {
+            for (;;) {
+                int v = next_ticket(&ctrl[1], &s_ticket);
+                if (v >= be_num) break;
+                run_any(be, be_off + v, reef_dyn_smem, nullptr);
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    __threadfence();
+                    atomicAdd(be_slot, 1);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        int d = atomicAdd(&ctrl[2], 1);
+        if (d == (int)gridDim.x - 1) {
+            ctrl[0] = 0;
+            ctrl[1] = 0;
+            __threadfence();
+            ctrl[2] = 0;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// host launchers
+// ------------------------------------------------------------------------------------------
+static unsigned long long g_launches = 0;
+unsigned long long launch_count() { return g_launches; }
+void add_launches(unsigned long long n) { g_launches += n; }
+
+#define FOR_EACH_FAMILY(X)                                                                      \
+    X(F_MOCK_ADD) X(F_MOCK_MUL) X(F_FUSED_ADD_NCHW) X(F_BIAS_RELU) X(F_CONV_SIMT) X(F_MAX_POOL) \
+    X(F_AVG_POOL) X(F_GLOBAL_AVG_POOL) X(F_COPY) X(F_DENSE) X(F_SOFTMAX)
+
+static const void* plain_fn(int family) {
+    switch (family) {
+#define X(F) case F: return (const void*)k_plain<F>;
+        FOR_EACH_FAMILY(X)
+#undef X
+        default: return nullptr;
+    }
+}
+static const void* be_fn(int family) {
+    switch (family) {
+#define X(F) case F: return (const void*)k_be<F>;
+        FOR_EACH_FAMILY(X)
+#undef X
+        default: return nullptr;
+    }
+}
+
+static int check_cuda(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return REEF_SUCC;
+    set_error(std::string(what) + ": " + cudaGetErrorString(e));
+    return REEF_FAIL;
+}
+
+static void fill_args(const KernelSpec& s, void** args, KTask* t) {
+    *t = s.task;
+    for (int i = 0; i < s.nargs; i++) t->a[i] = *reinterpret_cast<void**>(args[i]);
+}
+
+static bool dims_match(const KernelSpec& s, const uint32_t dims[6], uint32_t smem) {
+    return dims[0] == s.grid[0] && dims[1] == s.grid[1] && dims[2] == s.grid[2] && dims[3] == s.block[0] &&
+           dims[4] == s.block[1] && dims[5] == s.block[2] && smem == s.dyn_smem;
+}
+
+int launch_plain(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cudaStream_t st, void** args) {
+    if (!dims_match(s, dims, smem)) {
+        set_error("launch_params / shared_memory do not match the kernel plan of " + s.name);
+        return REEF_OUT_OF_RANGE;
+    }
+    KTask t;
+    fill_args(s, args, &t);
+    void* kargs[] = {&t};
+    cudaError_t e = cudaLaunchKernel(plain_fn(t.family), dim3(dims[0], dims[1], dims[2]),
+                                     dim3(dims[3], dims[4], dims[5]), kargs, smem, st);
+    g_launches++;
+    return check_cuda(e, "cudaLaunchKernel");
+}
+
+int launch_be(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cudaStream_t st, const int* flag,
+              int* slot, void** args) {
+    if (!dims_match(s, dims, smem)) {
+        set_error("launch_params / shared_memory do not match the kernel plan of " + s.name);
+        return REEF_OUT_OF_RANGE;
+    }
+    KTask t;
+    fill_args(s, args, &t);
+    void* kargs[] = {&t, (void*)&flag, (void*)&slot};
+    cudaError_t e = cudaLaunchKernel(be_fn(t.family), dim3(dims[0], dims[1], dims[2]),
+                                     dim3(dims[3], dims[4], dims[5]), kargs, smem, st);
+    g_launches++;
+    return check_cuda(e, "cudaLaunchKernel(be)");
+}
+
+int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, void** be_args, int be_off,
+                    int be_num, int sm_partition, int occupancy, int num_sms, int* be_slot, int* ctrl,
+                    cudaStream_t st) {
+    KTask trt, tbe;
+    uint32_t smem = 0;
+    if (rt != nullptr) {
+        fill_args(*rt, rt_args, &trt);
+        smem = rt->dyn_smem;
+    } else {
+        memset(&trt, 0, sizeof(trt));   // nblocks = 0: the real-time phase ends at once
+    }
+    if (be != nullptr && be_num > 0) {
+        fill_args(*be, be_args, &tbe);
+        if (be->dyn_smem > smem) smem = be->dyn_smem;
+        if (be_off < 0 || be_off + be_num > tbe.nblocks) {
+            set_error("best-effort block range outside the kernel");
+            return REEF_OUT_OF_RANGE;
+        }
+    } else {
+        memset(&tbe, 0, sizeof(tbe));
+        be_num = 0;
+    }
+    if (occupancy < 1) occupancy = 1;
+    int grid = num_sms * occupancy;
+    void* kargs[] = {&trt, &tbe, &be_off, &be_num, &sm_partition, (void*)&be_slot, (void*)&ctrl};
+    cudaError_t e = cudaLaunchKernel((const void*)k_dispatch, dim3(grid), dim3(kThreads), kargs, smem, st);
+    g_launches++;
+    return check_cuda(e, "cudaLaunchKernel(dispatch)");
+}
+
+int kernel_attrs(const KernelSpec& s, reef_kernel_attrs_t* out) {
+    cudaFuncAttributes fa;
+    const void* fn = plain_fn(s.task.family);
+    int rc = check_cuda(cudaFuncGetAttributes(&fa, fn), "cudaFuncGetAttributes");
+    if (rc != REEF_SUCC) return rc;
+    int threads = s.block[0] * s.block[1] * s.block[2];
+    int occ = 0;
+    rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, threads, s.dyn_smem),
+                    "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
+    if (rc != REEF_SUCC) return rc;
+    out->num_blocks = s.task.nblocks;
+    out->threads = threads;
+    out->regs_per_thread = fa.numRegs;
+    out->static_smem = (int)fa.sharedSizeBytes;
+    out->dyn_smem = (int)s.dyn_smem;
+    out->local_mem = (int)fa.localSizeBytes;
+    out->max_blocks_per_sm = occ;
+    out->flops = s.flops;
+    out->bytes = s.bytes;
+    out->tensor_core = s.tensor_core;
+    return REEF_SUCC;
+}
+
+int dispatch_occupancy(uint32_t smem, int* occ) {
+    return check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, (const void*)k_dispatch, kThreads, smem),
+                      "cudaOccupancyMaxActiveBlocksPerMultiprocessor(dispatch)");
+}
+
+}  // namespace reef

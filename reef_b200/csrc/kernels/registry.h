@@ -1,0 +1,39 @@
+// Host-side view of the kernel registry (internal to libreef_cuda).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../../include/reef_cuda.h"
+#include "task.cuh"
+
+namespace reef {
+
+struct KernelSpec {
+    std::string name;
+    KTask task;            // family + shape parameters; pointer slots are filled per launch
+    uint32_t grid[3];
+    uint32_t block[3];
+    uint32_t dyn_smem;
+    int nargs;
+    double flops, bytes;   // algorithmic work of one launch
+    int tensor_core;
+};
+
+void set_error(const std::string& s);
+const char* last_error();
+
+int plan_kernel(const char* name, KernelSpec* out);
+int launch_plain(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cudaStream_t st, void** args);
+int launch_be(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cudaStream_t st, const int* flag,
+              int* slot, void** args);
+int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, void** be_args, int be_off,
+                    int be_num, int sm_partition, int occupancy, int num_sms, int* be_slot, int* ctrl,
+                    cudaStream_t st);
+int kernel_attrs(const KernelSpec& s, reef_kernel_attrs_t* out);
+int dispatch_occupancy(uint32_t smem, int* occ);
+unsigned long long launch_count();
+void add_launches(unsigned long long n);
+
+}  // namespace reef

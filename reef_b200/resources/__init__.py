@@ -1,0 +1,59 @@
+"""Generator of REEF model resources (``<model>.json`` + ``.param`` + ``.profile.json``).
+
+Replaces the reference's TVM export + schedule merge (reference: script/tvm_generate_model.py,
+script/generate_final_schedule.py) for the synthetic benchmark configs: the architectures are
+authored here, the kernel list is chosen here, and launch geometry comes from the kernel registry
+through the C-ABI (``reef_kernel_plan``), so the json cannot disagree with the library.
+"""
+from __future__ import annotations
+
+import os
+
+from .graph import Graph, kname, parse_kname, read_param_file, write_param_file  # noqa: F401
+from .mocked import build_mocked_kernel
+from .resnet import build_resnet
+
+DEFAULT_DIR = os.environ.get("REEF_RESOURCE_DIR", "/tmp/reef_b200_resources")
+
+# seeds: 1000 * (index of the benchmark config the model first appears in) + model ordinal
+_BUILDERS = {
+    "resnet18": lambda **kw: build_resnet(18, seed=1000, **kw),
+    "resnet50": lambda **kw: build_resnet(50, seed=5001, **kw),
+    "resnet152": lambda **kw: build_resnet(152, seed=2000, **kw),
+    # small variants for fast parity tests (same builders, 64x64 input like the reference's shipped resnet152)
+    "resnet18_64": lambda **kw: build_resnet(18, name="resnet18_64", image=64, seed=1064, **kw),
+    "resnet50_64": lambda **kw: build_resnet(50, name="resnet50_64", image=64, seed=5064, **kw),
+}
+
+
+def available():
+    return ["mocked_kernel"] + sorted(_BUILDERS)
+
+
+def generate(model: str, out_root: str | None = None, *, force: bool = False, variant: str = "", **kw) -> str:
+    """Write the resources of `model` under <out_root>/<model><variant>/ and return that directory."""
+    from .. import capi
+    out_root = out_root or DEFAULT_DIR
+    name = model + variant
+    out_dir = os.path.join(out_root, name)
+    base = os.path.join(out_dir, name)
+    exts = (".json", ".profile.json") if model == "mocked_kernel" else (".json", ".param", ".profile.json")
+    if not force and all(os.path.exists(base + ext) for ext in exts):
+        return out_dir
+    if model == "mocked_kernel":
+        g = build_mocked_kernel()
+        g.name = name
+        # mocked_kernel has no parameters; the reference ships no .param for it
+        os.makedirs(out_dir, exist_ok=True)
+        import json
+        j = g.finalize(capi.plan_fn)
+        with open(base + ".json", "w") as f:
+            json.dump(j, f, indent=1)
+        from .graph import default_profile
+        with open(base + ".profile.json", "w") as f:
+            json.dump(default_profile(j), f)
+        return out_dir
+    b = _BUILDERS[model](**kw)
+    b.g.name = name
+    b.g.write(out_dir, capi.plan_fn)
+    return out_dir

@@ -1,0 +1,219 @@
+"""Layer-level helpers on top of :class:`Graph`: each call appends one fused kernel.
+
+The fused-op families and their positional argument order are the ones the
+reference's TVM build produced (reference: resource/resnet18/resnet18.json,
+resource/resnet152/resnet152.cu:315-374,771-841,4390-4474):
+
+=====================================  ==========================================
+family                                 args (storage indices, in order)
+=====================================  ==========================================
+fused_add                              out, in, bias            (NCHW, model input)
+fused_add_nn_relu                      out, in, bias            (NHWC)
+fused_nn_conv2d                        in, W, out
+fused_nn_conv2d_nn_relu                in, W, out
+fused_nn_conv2d_add                    in, W, out, residual
+fused_nn_conv2d_add_nn_relu            in, W, out, bias
+fused_nn_conv2d_add_add_nn_relu        in, W, out, residual, bias
+fused_nn_conv2d_add_multiply_add_nn_relu  in, W, out, residual, gamma, beta
+fused_nn_max_pool2d[_add_nn_relu]      in, out[, bias]
+fused_nn_avg_pool2d                    in, out
+fused_nn_global_avg_pool2d             in, out
+fused_nn_batch_flatten                 out, in
+fused_nn_dense_add[_nn_relu]           x, W, out, bias
+fused_nn_softmax                       in, out
+=====================================  ==========================================
+
+Synthetic parameters follow the benchmark configs: He-normal conv weights,
+BatchNorm (gamma~U(0.5,1.5), beta,mean~N(0,0.1), var~U(0.5,1.5), eps 2e-5)
+folded offline into a per-channel scale (absorbed by the adjacent conv weights)
+and a bias, exactly the form the reference graphs carry (bias-only
+``fused_add_nn_relu`` / ``max_pool2d_add_nn_relu`` ops, reference:
+resource/resnet18/resnet18.json kernels 0-2,10).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from .graph import Graph, Tensor, kname
+
+BN_EPS = 2e-5
+
+
+class Builder:
+    def __init__(self, name: str, seed: int, conv_impl: str = "auto"):
+        self.g = Graph(name)
+        self.seed = int(seed)
+        self._n = 0
+        self.conv_impl = conv_impl
+
+    # ---- randomness ----------------------------------------------------
+    def rng(self) -> np.random.Generator:
+        self._n += 1
+        return np.random.default_rng([self.seed, self._n])
+
+    def bn(self, c: int):
+        """Folded BatchNorm: returns (scale s > 0, shift t) with y = s*x + t."""
+        r = self.rng()
+        gamma = r.uniform(0.5, 1.5, c)
+        beta = r.normal(0.0, 0.1, c)
+        mean = r.normal(0.0, 0.1, c)
+        var = r.uniform(0.5, 1.5, c)
+        s = gamma / np.sqrt(var + BN_EPS)
+        t = beta - mean * s
+        return s.astype(np.float32), t.astype(np.float32)
+
+    def he_conv(self, co, kh, kw, ci):
+        """He-normal weights, OHWI."""
+        std = np.sqrt(2.0 / (ci * kh * kw))
+        return self.rng().normal(0.0, std, (co, kh, kw, ci)).astype(np.float32)
+
+    # ---- tensors -------------------------------------------------------
+    def new_act(self, h, w, c) -> Tensor:
+        return Tensor(self.g.temp(h * w * c), h, w, c)
+
+    def slice_of(self, buf: Tensor, coff: int, c: int) -> Tensor:
+        return Tensor(buf.idx, buf.h, buf.w, c, buf.cstride, buf.coff + coff)
+
+    # ---- ops -----------------------------------------------------------
+    def input_bias_nchw(self, data_idx: int, c: int, h: int, w: int, bias) -> Tensor:
+        out = Tensor(self.g.temp(c * h * w), h, w, c)
+        b = self.g.param(bias)
+        self.g.kernel(kname("fused_add", c=c, hw=h * w), [out.idx, data_idx, b])
+        return out
+
+    def conv(self, x: Tensor, co: int, k, stride=1, pad=0, *, weight=None,
+             out_scale=None, in_scale=None, bias=None, relu=False,
+             residual: Tensor | None = None, gamma_beta=None,
+             out: Tensor | None = None, nchw_in=False, w_gain: float = 1.0) -> Tensor:
+        kh, kw = (k, k) if isinstance(k, int) else k
+        sh, sw = (stride, stride) if isinstance(stride, int) else stride
+        ph, pw = (pad, pad) if isinstance(pad, int) else pad
+        ci = x.c
+        ho = (x.h + 2 * ph - kh) // sh + 1
+        wo = (x.w + 2 * pw - kw) // sw + 1
+        wgt = self.he_conv(co, kh, kw, ci) if weight is None else weight
+        if w_gain != 1.0:
+            wgt = wgt * np.float32(w_gain)
+        if out_scale is not None:
+            wgt = wgt * np.asarray(out_scale, np.float32)[:, None, None, None]
+        if in_scale is not None:
+            wgt = wgt * np.asarray(in_scale, np.float32)[None, None, None, :]
+        if out is None:
+            out = self.new_act(ho, wo, co)
+        assert (out.h, out.w, out.c) == (ho, wo, co)
+        w_idx = self.g.param(wgt)
+        op = "fused_nn_conv2d"
+        args = [x.idx, w_idx, out.idx]
+        if residual is not None:
+            assert (residual.h, residual.w, residual.c) == (ho, wo, co) and residual.cstride == co
+            op += "_add"
+            args.append(residual.idx)
+        if gamma_beta is not None:
+            assert bias is None and relu
+            op += "_multiply_add"
+            args += [self.g.param(gamma_beta[0]), self.g.param(gamma_beta[1])]
+        elif bias is not None:
+            assert relu, "bias without ReLU is not a family the reference graphs contain"
+            op += "_add"
+            args.append(self.g.param(bias))
+        if relu:
+            op += "_nn_relu"
+        attrs = dict(ci=ci, hi=x.h, wi=x.w, co=co, kh=kh, kw=kw, sh=sh, sw=sw, ph=ph, pw=pw)
+        if nchw_in:
+            attrs["nchw"] = 1
+        if x.cstride != ci or x.coff:
+            attrs["ics"] = x.cstride
+            attrs["ioff"] = x.coff
+        if out.cstride != co or out.coff:
+            attrs["ocs"] = out.cstride
+            attrs["ooff"] = out.coff
+        impl = self.pick_conv_impl(attrs)
+        if impl:
+            attrs["v"] = impl
+        self.g.kernel(kname(op, **attrs), args)
+        return out
+
+    def pick_conv_impl(self, attrs) -> int:
+        """0 = fp32 SIMT implicit GEMM (default).  Other variants are chosen by
+        the model builders through ``conv_impl``."""
+        if self.conv_impl in ("auto", "simt"):
+            return 0
+        return int(self.conv_impl)
+
+    def pool(self, x: Tensor, kind: str, k: int, stride: int, pad: int, *,
+             bias=None, out: Tensor | None = None, count_include_pad=True, ceil_mode=False) -> Tensor:
+        if ceil_mode:
+            ho = -(-(x.h + 2 * pad - k) // stride) + 1
+            wo = -(-(x.w + 2 * pad - k) // stride) + 1
+        else:
+            ho = (x.h + 2 * pad - k) // stride + 1
+            wo = (x.w + 2 * pad - k) // stride + 1
+        if out is None:
+            out = self.new_act(ho, wo, x.c)
+        attrs = dict(c=x.c, hi=x.h, wi=x.w, k=k, s=stride, p=pad, ho=ho, wo=wo)
+        if x.cstride != x.c or x.coff:
+            attrs["ics"] = x.cstride
+            attrs["ioff"] = x.coff
+        if out.cstride != x.c or out.coff:
+            attrs["ocs"] = out.cstride
+            attrs["ooff"] = out.coff
+        if kind == "max":
+            op = "fused_nn_max_pool2d"
+            args = [x.idx, out.idx]
+            if bias is not None:
+                op += "_add_nn_relu"
+                args.append(self.g.param(bias))
+        else:
+            op = "fused_nn_avg_pool2d"
+            attrs["cip"] = 1 if count_include_pad else 0
+            args = [x.idx, out.idx]
+        self.g.kernel(kname(op, **attrs), args)
+        return out
+
+    def bias_relu(self, x: Tensor, bias) -> Tensor:
+        assert x.cstride == x.c and x.coff == 0
+        out = self.new_act(x.h, x.w, x.c)
+        self.g.kernel(kname("fused_add_nn_relu", c=x.c, n=x.h * x.w),
+                      [out.idx, x.idx, self.g.param(bias)])
+        return out
+
+    def bias_relu_slice(self, x: Tensor, bias) -> Tensor:
+        """relu(x + bias) on a channel slice view (DenseNet pre-activation)."""
+        out = self.new_act(x.h, x.w, x.c)
+        attrs = dict(c=x.c, n=x.h * x.w)
+        if x.cstride != x.c or x.coff:
+            attrs["ics"] = x.cstride
+            attrs["ioff"] = x.coff
+        self.g.kernel(kname("fused_add_nn_relu", **attrs), [out.idx, x.idx, self.g.param(bias)])
+        return out
+
+    def global_avg_pool(self, x: Tensor) -> Tensor:
+        assert x.cstride == x.c and x.coff == 0
+        out = Tensor(self.g.temp(x.c), 1, 1, x.c)
+        self.g.kernel(kname("fused_nn_global_avg_pool2d", c=x.c, hw=x.h * x.w), [x.idx, out.idx])
+        return out
+
+    def flatten(self, x: Tensor) -> Tensor:
+        n = x.h * x.w * x.c
+        out = Tensor(self.g.temp(n), 1, 1, n)
+        self.g.kernel(kname("fused_nn_batch_flatten", n=n), [out.idx, x.idx])
+        return out
+
+    def dense(self, x: Tensor, n: int, *, relu=False, w_std=None, weight=None, bias=None,
+              out_idx=None) -> Tensor:
+        k = x.h * x.w * x.c
+        if weight is None:
+            std = np.sqrt(2.0 / k) if w_std is None else w_std
+            weight = self.rng().normal(0.0, std, (n, k)).astype(np.float32)
+        if bias is None:
+            bias = self.rng().normal(0.0, 0.1, n).astype(np.float32)
+        out = Tensor(self.g.temp(n) if out_idx is None else out_idx, 1, 1, n)
+        op = "fused_nn_dense_add" + ("_nn_relu" if relu else "")
+        self.g.kernel(kname(op, k=k, n=n), [x.idx, self.g.param(weight), out.idx, self.g.param(bias)])
+        return out
+
+    def softmax_output(self, x: Tensor) -> int:
+        n = x.h * x.w * x.c
+        out = self.g.add_storage("output", n)   # not in "args": the reference lists inputs and params only
+        self.g.kernel(kname("fused_nn_softmax", n=n), [x.idx, out])
+        return out

@@ -1,0 +1,175 @@
+"""GPU parity tests of the executor layers, through the C-ABI (libreef_host -> libreef_cuda).
+Pyramid as in the reference's test.cpp: raw executor -> dispatcher (rt_executor) -> best-effort flavour
+(hybrid_executor), same fixtures at every level; plus per-layer parity against the CPU oracle."""
+import json
+
+import numpy as np
+import pytest
+
+from conftest import rel_err, seeded_input
+from gpu_util import FP32_TOL, all_storage, compare_layers, load_executor, single_kernel_model
+from oracle import oracle
+from reef_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+
+def _mocked(e):
+    three = np.full(8192, 3.0, np.float32)
+    for n in ("a", "b", "c"):
+        e.set_input(n, three)
+
+
+@pytest.mark.parametrize("flavour", ["execute", "execute_dispatch", "execute_preemptable", "execute_graph"])
+def test_mocked_kernel_all_flavours(gen, flavour):
+    # reference: test.cpp:102-116 (executor_base), :246-261 (rt_executor), :296-311 (hybrid_executor)
+    e = load_executor(gen("mocked_kernel"))
+    _mocked(e)
+    getattr(e, flavour)()
+    out = e.get_output()
+    assert out.shape == (8192,) and np.all(out == 18.0)
+
+
+def test_set_input_errors(gen):
+    e = load_executor(gen("mocked_kernel"))
+    with pytest.raises(capi.ReefError) as ex:
+        e.set_input("a", np.zeros(16, np.float32))          # shorter than the storage entry
+    assert ex.value.status == capi.OUT_OF_RANGE
+    with pytest.raises(capi.ReefError) as ex:
+        e.set_input("nope", np.zeros(8192, np.float32))
+    assert ex.value.status == capi.NOT_FOUND
+    with pytest.raises(capi.ReefError) as ex:
+        e.execute_kernel(5)
+    assert ex.value.status == capi.OUT_OF_RANGE
+
+
+def test_unknown_kernel_name_is_not_found(tmp_path):
+    bad = tmp_path / "bad.json"
+    bad.write_text(json.dumps({"storage": [{"name": "a", "size": 4, "stype": "float32"}],
+                               "kernels": [{"name": "no_such_kernel", "launch_params": [1, 1, 1, 1, 1, 1], "args": [0]}],
+                               "args": [0], "shared_memory": {}}))
+    e = capi.HybridExecutor(0)
+    with pytest.raises(capi.ReefError) as ex:
+        e.load_model_from_file(str(bad))
+    assert ex.value.status == capi.NOT_FOUND
+
+
+CONV_CASES = [
+    # (family, ci, hi, wi, co, kh, kw, s, ph, pw)   ragged pixel/out-channel tiles, strides, asymmetric taps
+    ("fused_nn_conv2d", 16, 9, 11, 8, 3, 3, 1, 1, 1),
+    ("fused_nn_conv2d_add", 64, 14, 14, 100, 1, 1, 1, 0, 0),
+    ("fused_nn_conv2d_add_nn_relu", 32, 15, 15, 72, 3, 3, 2, 1, 1),
+    ("fused_nn_conv2d_add_add_nn_relu", 48, 7, 7, 64, 1, 1, 2, 0, 0),
+    ("fused_nn_conv2d_add_multiply_add_nn_relu", 128, 7, 7, 256, 3, 3, 1, 1, 1),
+    ("fused_nn_conv2d_nn_relu", 80, 8, 8, 32, 1, 7, 1, 0, 3),
+    ("fused_nn_conv2d_add_nn_relu", 20, 10, 10, 12, 5, 5, 1, 2, 2),    # ci not a multiple of 16: generic gather
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES, ids=[c[0][9:] + f"_{c[1]}x{c[4]}k{c[5]}{c[6]}s{c[7]}" for c in CONV_CASES])
+def test_conv_kernel_parity(tmp_path, case):
+    fam, ci, hi, wi, co, kh, kw, s, ph, pw = case
+    ho, wo = (hi + 2 * ph - kh) // s + 1, (wi + 2 * pw - kw) // s + 1
+    name = f"{fam}__ci{ci}_hi{hi}_wi{wi}_co{co}_kh{kh}_kw{kw}_sh{s}_sw{s}_ph{ph}_pw{pw}"
+    specs = [("in", ci * hi * wi), ("param", co * kh * kw * ci), ("out", ho * wo * co)]
+    tail = fam[len("fused_nn_conv2d"):].replace("_nn_relu", "")
+    if tail == "_add":
+        specs.append(("param", co) if fam.endswith("_nn_relu") else ("in", ho * wo * co))
+    elif tail == "_add_add":
+        specs += [("in", ho * wo * co), ("param", co)]
+    elif tail == "_add_multiply_add":
+        specs += [("in", ho * wo * co), ("param", co), ("param", co)]
+    base, inputs = single_kernel_model(tmp_path, "one", name, specs)
+    e = load_executor(base)
+    o = oracle.OracleExecutor(base + ".json", base + ".param")
+    for k, v in inputs.items():
+        e.set_input(k, v)
+        o.set_input(k, v)
+    e.execute()
+    o.execute()
+    assert rel_err(e.get_output(), o.get_output()) < FP32_TOL
+    # the best-effort flavour and the dispatcher run the same body: bit-identical to the raw launch
+    raw = e.get_output()
+    e.execute_preemptable()
+    assert np.array_equal(e.get_output(), raw)
+    e.execute_dispatch()
+    assert np.array_equal(e.get_output(), raw)
+
+
+@pytest.mark.parametrize("model", ["resnet18_64", "resnet50_64"])
+def test_small_resnet_layer_by_layer(gen, model):
+    base = gen(model)
+    j = json.load(open(base + ".json"))
+    x = seeded_input(3 * 64 * 64)
+    e = load_executor(base)
+    o = oracle.OracleExecutor(base + ".json", base + ".param")
+    e.set_input("data", x)
+    o.set_input("data", x)
+    e.execute()
+    o.execute()
+    worst = compare_layers(e, o, j)
+    print(model, "worst layer rel err", worst)
+    assert abs(float(e.get_output().sum()) - 1.0) < 1e-4
+
+
+def test_resnet18_golden_const10(gen):
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "resnet18_64_const10.npz"))
+    base = gen("resnet18_64")
+    j = json.load(open(base + ".json"))
+    e = load_executor(base)
+    e.set_input("data", np.full(3 * 64 * 64, 10.0, np.float32))
+    e.execute()
+    li = j["kernels"][-1]["args"][0]
+    assert rel_err(e.get_data(li, 4000), g["logits"]) < FP32_TOL
+    assert rel_err(e.get_output(), g["probs"]) < FP32_TOL
+
+
+@pytest.mark.parametrize("model,tol", [("resnet18", FP32_TOL), ("resnet152", FP32_TOL)])
+def test_full_size_resnet_logits_and_probs(gen, model, tol):
+    base = gen(model)
+    j = json.load(open(base + ".json"))
+    x = seeded_input(3 * 224 * 224, seed=11)
+    e = load_executor(base)
+    o = oracle.OracleExecutor(base + ".json", base + ".param")
+    e.set_input("data", x)
+    o.set_input("data", x)
+    e.execute()
+    o.execute()
+    li = j["kernels"][-1]["args"][0]
+    err_logits = rel_err(e.get_data(li, 4000), o.storage[li])
+    err_probs = rel_err(e.get_output(), o.get_output())
+    print(model, "logits rel err", err_logits, "probs rel err", err_probs)
+    assert err_logits < tol and err_probs < tol
+    # graph replay, dispatcher and best-effort flavour give the same bytes as the raw launches
+    raw = e.get_output()
+    for f in ("execute_graph", "execute_dispatch", "execute_preemptable"):
+        getattr(e, f)()
+        assert np.array_equal(e.get_output(), raw), f
+
+
+@pytest.mark.parametrize("model,delays", [("resnet50_64", [20, 60, 150]), ("resnet152", [100, 400, 1500])])
+def test_preempted_and_rerun_is_bit_identical(gen, model, delays):
+    """A best-effort run that is preempted (flag raised mid-flight) and resumed from the first kernel whose
+    completion counter is short must leave every buffer bit-identical to an uninterrupted GPU run."""
+    base = gen(model)
+    j = json.load(open(base + ".json"))
+    n_in = j["storage"][0]["size"]
+    x = seeded_input(n_in, seed=5)
+    ref = load_executor(base)
+    ref.set_input("data", x)
+    ref.execute_preemptable()
+    want = all_storage(ref, j)
+    slots, blocks = ref.task_slots()
+    assert slots == blocks                      # every kernel's counter reached its block count
+    hit = 0
+    for d in delays:
+        e = load_executor(base)
+        e.set_input("data", x)
+        restarts, first = e.execute_preempt_resume(d)
+        hit += restarts > 0
+        got = all_storage(e, j)
+        for i, (a, b) in enumerate(zip(got, want)):
+            assert np.array_equal(a, b), f"delay {d}us: storage {i} differs after {restarts} restarts (first {first})"
+        print(model, "delay", d, "us -> restarts", restarts, "first incomplete kernel", first)
+    assert hit > 0, "no delay landed inside the run; preemption was not exercised"
