@@ -1,0 +1,359 @@
+#!/usr/bin/env python
+"""Benchmark of the REEF executor kernel path on B200.
+
+Workload (BASELINE.json configs[2], the configuration the headline metric is quoted on): one
+real-time (RT) client issuing back-to-back ResNet-152 batch-1 requests while 4 best-effort (BE)
+clients run ResNet-152 batch-1 closed-loop, all on one GPU through REEFScheduler in REEF mode
+(flag preemption + dynamic kernel padding).  Synthetic, seeded weights and inputs.
+
+A "step" is one RT request.  `value` is whole-job inferences/s (RT + BE) with inputs resident in
+HBM; `e2e` is the same measured through the scheduler's public request calls with pinned HOST
+buffers (set_input H2D + new_task + wait_task + get_output D2H inside the timed region).  RT
+p50/p99, RT-alone p99, BE inf/s, BE-alone inf/s and preemption latency ride along in `rt_be`.
+
+N > 1 (torchrun, one rank per GPU): one scheduler + full weight replica per GPU, requests are
+independent, no data-path collective ("scaling": "weak").
+
+`--impl reference` times the CPU arm: the reference's own kernels cannot run here (HIP/gfx906,
+TVM-generated), so the arm is the plain-C oracle port of the same schedule graph on all host cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "resnet152_b1_inferences_per_s_rt_plus_4be"
+UNIT = "inf/s"
+WORKLOAD = "configs[2]: ResNet-152 b1 RT client back-to-back + 4 BE ResNet-152 b1 closed-loop clients, REEF mode"
+MODEL = "resnet152"
+N_BE = 4
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu):
+        self.gpu, self.proc, self.lines = gpu, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def pct(a, q):
+    return float(np.percentile(a, q)) if len(a) else None
+
+
+def pinned_array(capi, nbytes, dtype=np.float32):
+    import ctypes as C
+    p = C.c_void_p()
+    rc = capi.cuda_lib().reef_host_alloc_pinned(C.byref(p), C.c_size_t(nbytes))
+    if rc != 0:
+        raise RuntimeError("reef_host_alloc_pinned failed: " + capi.last_error())
+    buf = (C.c_char * nbytes).from_address(p.value)
+    return np.frombuffer(buf, dtype=dtype)
+
+
+def run_reference_arm(args, rank, world):
+    """CPU arm: the oracle port of the ResNet-152 schedule on all host cores; a step = one inference."""
+    if rank != 0:
+        return
+    from oracle import oracle
+    from reef_b200 import resources
+    d = resources.generate(MODEL)
+    base = os.path.join(d, MODEL)
+    x = np.random.default_rng(2001).normal(0, 1, 3 * 224 * 224).astype(np.float32)
+    o = oracle.OracleExecutor(base + ".json", base + ".param")
+    o.set_input("data", x)
+    cores = oracle.num_threads()
+    for _ in range(max(1, min(args.warmup, 3))):
+        o.execute()
+    steps = max(1, min(args.steps, 20))   # bounded sample: about 10-30 s of CPU work
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        o.execute()
+    dt = time.perf_counter() - t0
+    v = steps / dt
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": args.warmup, "ms_per_step": 1000.0 * dt / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD + " (CPU arm: the same ResNet-152 schedule, one client, sequential)"},
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                             "sample": f"{steps} ResNet-152 b1 inferences, OpenMP on {cores} threads"},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=100)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--be-cap", type=int, default=int(os.environ.get("REEF_BE_CAP", "4")))
+    ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--profile-out", default="")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: no CUDA device is visible and there is no CPU fallback")
+    from reef_b200 import build, capi, resources
+    if rank == 0:
+        build.build_all()
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist.barrier()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if rank == 0:
+        d = resources.generate(MODEL)
+    barrier()
+    d = resources.generate(MODEL)
+    base = os.path.join(d, MODEL)
+    S = capi.REEFScheduler
+    x = np.random.default_rng(2001 + rank).normal(0, 1, 3 * 224 * 224).astype(np.float32)
+
+    def make_sched(n_be, rt=True):
+        s = S(S.REEF, local_rank)
+        s.set_be_stream_cap(args.be_cap)
+        s.run()
+        ids = {"rt": None, "be": []}
+        if rt:
+            ids["rt"] = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
+            s.bind_model_queue(s.create_queue(S.RealTimeQueue), ids["rt"])
+            s.set_input(ids["rt"], x)
+        for _ in range(n_be):
+            m = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
+            s.bind_model_queue(s.create_queue(S.BestEffortQueue), m)
+            s.set_input(m, x)
+            ids["be"].append(m)
+        return s, ids
+
+    extra = {}
+    # ---- phase A: RT alone (closed loop, inputs resident) -------------------------------------
+    s, ids = make_sched(0)
+    r = s.run_clients([dict(mid=ids["rt"], max_requests=args.steps, warmup=args.warmup, want_output=False)])[0]
+    extra["rt_alone_p50_ms"] = pct(r["latencies_ms"], 50)
+    extra["rt_alone_p99_ms"] = pct(r["latencies_ms"], 99)
+    extra["rt_alone_inf_s"] = r["completed"] / r["elapsed_s"]
+    s.shutdown(); s.close()
+
+    # ---- phase B: BE alone ---------------------------------------------------------------------
+    s, ids = make_sched(N_BE, rt=False)
+    be_req = max(20, args.steps // 8)
+    rs = s.run_clients([dict(mid=m, max_requests=be_req, warmup=max(3, args.warmup // 8), want_output=False)
+                        for m in ids["be"]])
+    extra["be_alone_inf_s"] = sum(r["completed"] / r["elapsed_s"] for r in rs)
+    s.shutdown(); s.close()
+
+    # ---- phase C (timed region of `value`): RT + 4 BE, inputs resident in HBM --------------------
+    s, ids = make_sched(N_BE)
+    clients = [dict(mid=ids["rt"], max_requests=args.steps, warmup=args.warmup, want_output=False)] + \
+              [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
+    sampler = ClockSampler(local_rank)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    launches0 = capi.launch_count()
+    ev0.record()
+    rs = s.run_clients(clients)
+    torch.cuda.synchronize()
+    ev1.record()
+    torch.cuda.synchronize()
+    launches = capi.launch_count() - launches0
+    clocks = sampler.stop()
+    barrier()
+    rt_r, be_r = rs[0], rs[1:]
+    # the timed region of the K steps is the RT client's recorded window; BE throughput over the same window
+    region_s = rt_r["elapsed_s"]
+    total_inf = rt_r["completed"] + sum(r["completed"] for r in be_r)
+    be_inf_s = sum(r["completed"] / r["elapsed_s"] for r in be_r if r["elapsed_s"] > 0)
+    st = s.stats()
+    extra.update({"rt_p50_ms": pct(rt_r["latencies_ms"], 50), "rt_p99_ms": pct(rt_r["latencies_ms"], 99),
+                  "be_inf_s": be_inf_s, "rt_inf_s": rt_r["completed"] / region_s,
+                  "preempt_avg_us": st["preempt_ns_sum"] / max(1, st["preempt_count"]) / 1e3,
+                  "preempt_max_us": st["preempt_ns_max"] / 1e3, "preempt_count": st["preempt_count"],
+                  "padded_kernels": st["padded_kernels"], "be_tasks_padded_to_finish": st["be_tasks_padded_to_finish"],
+                  "device_event_ms_incl_warmup": ev0.elapsed_time(ev1), "be_stream_cap": args.be_cap})
+    s.shutdown(); s.close()
+
+    # ---- phase D: preemption latency with drain (flag set -> BE streams idle -> counters read) ----
+    s, ids = make_sched(N_BE)
+    s.set_wait_sync(True)
+    clients = [dict(mid=ids["rt"], max_requests=max(50, args.steps // 10), warmup=5, want_output=False, think_us=2000)] + \
+              [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
+    s.run_clients(clients)
+    st = s.stats()
+    extra["preempt_drain_avg_us"] = st["preempt_ns_sum"] / max(1, st["preempt_count"]) / 1e3
+    extra["preempt_drain_max_us"] = st["preempt_ns_max"] / 1e3
+    extra["preempt_drain_count"] = st["preempt_count"]
+    s.shutdown(); s.close()
+
+    # ---- phase E (e2e): same workload through the request calls with pinned host buffers ---------
+    s, ids = make_sched(N_BE)
+    in_bytes = x.nbytes
+    pins = []
+    clients = []
+    for i, m in enumerate([ids["rt"]] + ids["be"]):
+        pin = pinned_array(capi, in_bytes)
+        pin[:] = x
+        pins.append(pin)
+        clients.append(dict(mid=m, max_requests=args.steps if i == 0 else 0, warmup=args.warmup if i == 0 else 0,
+                            input=pin, want_output=True))
+    barrier()
+    rs = s.run_clients(clients)
+    barrier()
+    e2e_region = rs[0]["elapsed_s"]
+    e2e_total = rs[0]["completed"] / e2e_region + sum(r["completed"] / r["elapsed_s"] for r in rs[1:] if r["elapsed_s"] > 0)
+    out_bytes = 4000
+    extra["e2e_rt_p50_ms"] = pct(rs[0]["latencies_ms"], 50)
+    extra["e2e_rt_p99_ms"] = pct(rs[0]["latencies_ms"], 99)
+    s.shutdown(); s.close()
+
+    # ---- kernel profile -> roofline of the dominant kernel family (conv2d) ------------------------
+    e = capi.HybridExecutor(local_rank)
+    e.load_model_from_file(base + ".json", base + ".profile.json")
+    e.load_param_from_file(base + ".param")
+    e.set_input("data", x)
+    prof = e.profile_kernels(20)
+    names = [k["name"] for k in json.load(open(base + ".json"))["kernels"]]
+    conv = [(n, p) for n, p in zip(names, prof) if n.startswith("fused_nn_conv2d")]
+    conv_us = sum(p["us"] for _, p in conv)
+    conv_bytes = sum(p["bytes"] for _, p in conv)
+    conv_flops = sum(p["flops"] for _, p in conv)
+    all_us = sum(p["us"] for p in prof)
+    peak, peak_kind = measured_peaks()
+    achieved = conv_bytes / (conv_us * 1e-6) / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "conv_traffic.json")
+    if os.path.exists(tpath):
+        traffic = json.load(open(tpath)).get("traffic_bytes_per_launch")
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": traffic, "peak_kind": peak_kind,
+                "kernel": "conv2d family (%d launches of one ResNet-152 pass, timed in context with CUDA events)" % len(conv),
+                "algorithmic_bytes_per_pass": conv_bytes, "avg_launch_us": conv_us / max(1, len(conv)),
+                "conv_tflops": conv_flops / (conv_us * 1e-6) / 1e12, "conv_share_of_kernel_time": conv_us / all_us,
+                "model_kernel_time_us": all_us}
+    graph_ms = e.time(1, 5, 50)
+    extra["rt_graph_device_ms"] = graph_ms
+    if args.profile_out and rank == 0:
+        with open(args.profile_out, "w") as f:
+            json.dump([dict(name=n, **p) for n, p in zip(names, prof)], f, indent=1)
+    e.close()
+
+    # ---- aggregate over ranks --------------------------------------------------------------------
+    value = total_inf / region_s
+    ms_per_step = 1000.0 * region_s / max(1, rt_r["completed"])
+    e2e_value = e2e_total
+    if dist is not None:
+        t = torch.tensor([value, e2e_value, ms_per_step, float(launches)], dtype=torch.float64, device="cuda")
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        value, e2e_value, launches = float(tsum[0]), float(tsum[1]), int(tsum[3])
+        ms_per_step = float(tmax[2])
+        p99 = torch.tensor([extra["rt_p99_ms"], extra["rt_alone_p99_ms"]], dtype=torch.float64, device="cuda")
+        dist.all_reduce(p99, op=dist.ReduceOp.MAX)
+        extra["rt_p99_ms_max_over_ranks"], extra["rt_alone_p99_ms_max_over_ranks"] = float(p99[0]), float(p99[1])
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        from oracle import oracle
+        o = oracle.OracleExecutor(base + ".json", base + ".param")
+        o.set_input("data", x)
+        o.execute()
+        n_cpu = 0
+        t0 = time.perf_counter()
+        while n_cpu < 3 or (time.perf_counter() - t0 < 10.0 and n_cpu < 40):
+            o.execute()
+            n_cpu += 1
+        dt = time.perf_counter() - t0
+        cpu = {"value": n_cpu / dt, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+               "sample": f"{n_cpu} sequential ResNet-152 b1 inferences of the same schedule (plain-C oracle, OpenMP)"}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": WORKLOAD, "inputs": "1x3x224x224 N(0,1)", "clients": "1 RT + 4 BE per GPU",
+                           "l2": "weights of one pass (240 MB per model, 5 replicas) exceed the 126 MB L2"},
+                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+                "rt_be": extra}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -154,6 +154,10 @@ REEF_API reef_status reef_dispatch(reef_kernel_t rt, void** rt_args,
  * (reference: scheduler.cpp:336-345): waits until `s` is idle or `timeout_us` passed (REEF_TIMEOUT). */
 REEF_API reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us);
 
+/* Profiling aid (no reference counterpart): occupies `s` with a one-thread kernel for `ns` nanoseconds
+ * (clamped to 20 ms, bounded loop) so that launches queued behind it run back to back. */
+REEF_API reef_status reef_stream_delay(reef_stream_t s, uint64_t ns);
+
 /* Number of kernels this library launched since load (its own kernels only; graph replays count
  * the kernels inside the graph). */
 REEF_API uint64_t reef_launch_count(void);

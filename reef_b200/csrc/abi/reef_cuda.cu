@@ -321,4 +321,6 @@ reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us) {
 
 uint64_t reef_launch_count(void) { return launch_count(); }
 
+reef_status reef_stream_delay(reef_stream_t s, uint64_t ns) { return launch_delay((cudaStream_t)s, ns); }
+
 }  // extern "C"

@@ -394,22 +394,31 @@ Status HybridExecutor::execute_preempt_resume(int delay_us, int* restarts, int* 
 }
 
 Status HybridExecutor::profile_kernels(int iters, float* us) {
-    reef_event_t a, b;
-    GPU_RETURN_STATUS(reef_event_create(&a));
-    GPU_RETURN_STATUS(reef_event_create(&b));
+    // Whole-model passes with an event between consecutive kernels: every kernel is timed in context
+    // (weights of the other layers have cycled through L2 since its last run).  The stream is held by
+    // a short delay kernel while the host queues the pass, so event gaps hold no launch latency.
+    const size_t n = num_kernels();
+    std::vector<reef_event_t> ev(n + 1);
+    for (auto& e : ev) GPU_RETURN_STATUS(reef_event_create(&e));
+    std::vector<double> sum(n, 0.0);
     Status st = Status::Succ;
-    for (size_t i = 0; i < num_kernels() && st == Status::Succ; i++) {
-        st = ExecutorBase::launch_kernel((int)i, s);   // warm
-        reef_event_record(a, s);
-        for (int r = 0; r < iters && st == Status::Succ; r++) st = ExecutorBase::launch_kernel((int)i, s);
-        reef_event_record(b, s);
-        reef_event_sync(b);
-        float ms = 0;
-        reef_event_elapsed_ms(a, b, &ms);
-        us[i] = ms * 1000.f / (float)std::max(1, iters);
+    for (int it = 0; it <= iters && st == Status::Succ; it++) {
+        GPU_RETURN_STATUS(reef_stream_delay(s, 1000ull * (400 + 8 * n)));
+        reef_event_record(ev[0], s);
+        for (size_t i = 0; i < n && st == Status::Succ; i++) {
+            st = ExecutorBase::launch_kernel((int)i, s);
+            reef_event_record(ev[i + 1], s);
+        }
+        GPU_RETURN_STATUS(reef_stream_sync(s));
+        if (it == 0) continue;   // warm-up pass
+        for (size_t i = 0; i < n; i++) {
+            float ms = 0;
+            reef_event_elapsed_ms(ev[i], ev[i + 1], &ms);
+            sum[i] += ms;
+        }
     }
-    reef_event_destroy(a);
-    reef_event_destroy(b);
+    for (size_t i = 0; i < n; i++) us[i] = (float)(sum[i] * 1000.0 / std::max(1, iters));
+    for (auto& e : ev) reef_event_destroy(e);
     return st;
 }
 

@@ -160,8 +160,10 @@ __device__ __forceinline__ bool body_conv_simt(const KTask& t, int vb, unsigned 
                 v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
             }
             if (p.ep & EP_GB) {
-                v.x = v.x * sc.x + sh.x; v.y = v.y * sc.y + sh.y;
-                v.z = v.z * sc.z + sh.z; v.w = v.w * sc.w + sh.w;
+                // explicit fused multiply-add: the three flavours of this body are compiled in different
+                // kernels and must round identically
+                v.x = fmaf(v.x, sc.x, sh.x); v.y = fmaf(v.y, sc.y, sh.y);
+                v.z = fmaf(v.z, sc.z, sh.z); v.w = fmaf(v.w, sc.w, sh.w);
             } else {
                 v.x += sh.x; v.y += sh.y; v.z += sh.z; v.w += sh.w;
             }

@@ -351,6 +351,28 @@ __global__ void __launch_bounds__(kThreads) k_dispatch(const __grid_constant__ K
     }
 }
 
+// Bounded busy-wait of one thread (profiling aid: holds a stream while the host queues launches behind it).
+__global__ void k_delay(unsigned long long ns) {
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    if (ns > 20000000ull) ns = 20000000ull;   // never more than 20 ms
+    for (int i = 0; i < (1 << 24); i++) {
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 >= ns) break;
+        __nanosleep(200);
+    }
+}
+
+int launch_delay(cudaStream_t st, unsigned long long ns) {
+    k_delay<<<1, 1, 0, st>>>(ns);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error(std::string("k_delay: ") + cudaGetErrorString(e));
+        return REEF_FAIL;
+    }
+    return REEF_SUCC;
+}
+
 // ------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------

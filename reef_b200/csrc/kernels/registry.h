@@ -33,6 +33,7 @@ int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, 
                     cudaStream_t st);
 int kernel_attrs(const KernelSpec& s, reef_kernel_attrs_t* out);
 int dispatch_occupancy(uint32_t smem, int* occ);
+int launch_delay(cudaStream_t st, unsigned long long ns);
 unsigned long long launch_count();
 void add_launches(unsigned long long n);
 
