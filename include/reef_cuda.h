@@ -118,6 +118,8 @@ typedef struct {
     double flops;          /* algorithmic FLOPs of one launch                               */
     double bytes;          /* algorithmic HBM bytes of one launch                           */
     int tensor_core;       /* 1 when the kernel's contraction runs on tcgen05               */
+    int cluster;           /* thread blocks per cluster (1 = no cluster); block ranges handed to
+                              reef_dispatch for this kernel must be multiples of it           */
 } reef_kernel_attrs_t;
 REEF_API reef_status reef_kernel_attrs(reef_kernel_t k, reef_kernel_attrs_t* out);
 
@@ -136,23 +138,38 @@ REEF_API reef_status reef_launch_be(reef_kernel_t k, const uint32_t dims[6], uin
 /* Dynamic kernel padding (reference: scheduler.cpp:613-649 launches merge_framework_N with
  * {rt func, rt occupancy, rt blocks, rt offset, rt args, be func, be occupancy, be blocks,
  * be offset, be args, cu_partition}; device side resource/mocked_kernel/mocked_kernel.trans.cu:112-186).
- * One persistent grid of sms*occupancy blocks: blocks resident on SMs [0, sm_partition) take the
- * real-time kernel's logical blocks from a ticket counter, the others run best-effort logical
- * blocks [be_block_offset, be_block_offset+be_block_num) and then help with what is left of the
- * real-time kernel.  be may be NULL (then be_block_num = 0).  `ctrl` is 16 bytes of zeroed device
- * memory owned by the caller, reused across launches (the kernel re-zeroes it when it drains). */
+ * Runs the real-time kernel `rt` and, beside it, best-effort logical blocks
+ * [be_block_offset, be_block_offset+be_block_num) of `be` (be may be NULL, rt may be NULL).
+ *  - Both kernels are logical-block families and be_stream is NULL: ONE persistent grid of
+ *    sms*occupancy blocks on `s`; blocks resident on SMs [0, sm_partition) take real-time blocks
+ *    from a ticket counter, the others run the best-effort blocks and then help with what is left
+ *    of the real-time kernel (so the result does not depend on block placement).
+ *  - A tensor-core (cluster) kernel is involved, or be_stream is given: the real-time kernel is its
+ *    own launch on `s` and the best-effort blocks are launched beside it on be_stream, to be placed by
+ *    the hardware on the SMs the real-time kernel leaves free (`s` should have the greater priority).
+ *    For a cluster kernel the block range must be a multiple of its cluster size.
+ * Best-effort blocks run here do not poll the preempt flag; each one that completes adds 1 to
+ * *be_task_slot.  rt_ctrl / be_ctrl: 16 bytes of zeroed device memory each, owned by the caller and
+ * reused across launches (a grid re-zeroes its block when it drains); be_ctrl is only used by a
+ * separate best-effort launch and must not be shared by launches that can overlap. */
 REEF_API reef_status reef_dispatch(reef_kernel_t rt, void** rt_args,
                                    reef_kernel_t be, void** be_args,
                                    int be_block_offset, int be_block_num,
                                    int sm_partition, int occupancy,
-                                   reef_dptr_t preempt_flag, reef_dptr_t be_task_slot,
-                                   reef_dptr_t ctrl, reef_stream_t s);
+                                   reef_dptr_t be_task_slot,
+                                   reef_dptr_t rt_ctrl, reef_dptr_t be_ctrl,
+                                   reef_stream_t s, reef_stream_t be_stream);
 
 /* GPUClearHostQueue / GPUResetCU (reference: hip_impl.h:21-22) have no CUDA equivalent: queued
  * launches are dropped by the host scheduler before they reach the stream and running blocks leave
  * at their next flag poll.  This call is the bounded replacement for the reference's wait loop
  * (reference: scheduler.cpp:336-345): waits until `s` is idle or `timeout_us` passed (REEF_TIMEOUT). */
 REEF_API reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us);
+
+/* Device-side error word: kernels with bounded waits (mbarrier waits of the tensor-core convolution) set it
+ * instead of hanging or trapping.  Reads the word of the current device (after the caller synchronised the
+ * stream of interest) and clears it; *value != 0 means some wait expired and the outputs are not valid. */
+REEF_API reef_status reef_device_error(int* value);
 
 /* Profiling aid (no reference counterpart): occupies `s` with a one-thread kernel for `ns` nanoseconds
  * (clamped to 20 ms, bounded loop) so that launches queued behind it run back to back. */

@@ -29,7 +29,7 @@ class KernelAttrs(C.Structure):
     _fields_ = [("num_blocks", C.c_int), ("threads", C.c_int), ("regs_per_thread", C.c_int),
                 ("static_smem", C.c_int), ("dyn_smem", C.c_int), ("local_mem", C.c_int),
                 ("max_blocks_per_sm", C.c_int), ("flops", C.c_double), ("bytes", C.c_double),
-                ("tensor_core", C.c_int)]
+                ("tensor_core", C.c_int), ("cluster", C.c_int)]
 
 
 class TaskInfo(C.Structure):
@@ -104,6 +104,13 @@ def device_count() -> int:
     n = C.c_int()
     _check(cuda_lib().reef_device_count(C.byref(n)), "reef_device_count")
     return n.value
+
+
+def device_error() -> int:
+    """Reads and clears the device error word (non-zero: a bounded device-side wait expired)."""
+    v = C.c_int()
+    _check(cuda_lib().reef_device_error(C.byref(v)), "reef_device_error")
+    return v.value
 
 
 def launch_count() -> int:

@@ -296,15 +296,15 @@ reef_status reef_launch_be(reef_kernel_t k, const uint32_t dims[6], uint32_t dyn
     return launch_be(k->spec, dims, dyn_smem, (cudaStream_t)s, (const int*)flag, (int*)slot, args);
 }
 reef_status reef_dispatch(reef_kernel_t rt, void** rt_args, reef_kernel_t be, void** be_args, int be_off,
-                          int be_num, int sm_partition, int occupancy, reef_dptr_t flag, reef_dptr_t be_slot,
-                          reef_dptr_t ctrl, reef_stream_t s) {
-    (void)flag;
-    if ((!rt && !be) || !ctrl) return REEF_FAIL;
+                          int be_num, int sm_partition, int occupancy, reef_dptr_t be_slot, reef_dptr_t rt_ctrl,
+                          reef_dptr_t be_ctrl, reef_stream_t s, reef_stream_t be_stream) {
+    if ((!rt && !be) || !rt_ctrl) return REEF_FAIL;
     int sms = 0;
     int rc = reef_device_num_sms(&sms);
     if (rc != REEF_SUCC) return rc;
-    return launch_dispatch(rt ? &rt->spec : nullptr, rt_args, be ? &be->spec : nullptr, be_args, be_off, be_num, sm_partition,
-                           occupancy, sms, (int*)be_slot, (int*)ctrl, (cudaStream_t)s);
+    return launch_dispatch(rt ? &rt->spec : nullptr, rt_args, be ? &be->spec : nullptr, be_args, be_off, be_num,
+                           sm_partition, occupancy, sms, (int*)be_slot, (int*)rt_ctrl, (int*)be_ctrl, (cudaStream_t)s,
+                           (cudaStream_t)be_stream);
 }
 
 reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us) {
@@ -320,6 +320,15 @@ reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us) {
 }
 
 uint64_t reef_launch_count(void) { return launch_count(); }
+
+reef_status reef_device_error(int* value) {
+    int* w = nullptr;
+    int rc = tc_error_word(&w);
+    if (rc != REEF_SUCC) return rc;
+    CK(cudaMemcpy(value, w, 4, cudaMemcpyDeviceToHost));
+    if (*value != 0) CK(cudaMemset(w, 0, 4));
+    return REEF_SUCC;
+}
 
 reef_status reef_stream_delay(reef_stream_t s, uint64_t ns) { return launch_delay((cudaStream_t)s, ns); }
 

@@ -251,6 +251,8 @@ Status HybridExecutor::init_hybrid_executor(const char* profile_file_path) {
         GPU_RETURN_STATUS(reef_kernel_attrs(kernels[i], &ka.resource));
         ka.block_num = ka.resource.num_blocks;
         ka.threads = ka.resource.threads;
+        ka.granularity = std::max(1, ka.resource.cluster);
+        if (ka.resource.tensor_core) has_tc = true;
         int max_layers = std::max(1, ka.resource.max_blocks_per_sm);
         int layers = align_up(ka.block_num, num_sms) / num_sms;
         ka.min_occupancy = std::max(1, std::min(layers, max_layers));
@@ -313,11 +315,12 @@ Status HybridExecutor::launch_preempt_kernel(int i, GPUStream_t stream) {
 }
 
 Status HybridExecutor::launch_dispatch(int rt_idx, HybridExecutor* be, int be_idx, int be_block_offset,
-                                       int be_block_num, int sm_partition, int occupancy, GPUStream_t stream) {
+                                       int be_block_num, int sm_partition, int occupancy, GPUStream_t stream,
+                                       GPUStream_t be_stream) {
     int rc = reef_dispatch(kernels[rt_idx], raw_args[rt_idx].data(), be ? be->kernels[be_idx] : nullptr,
                            be ? be->raw_args[be_idx].data() : nullptr, be_block_offset, be_block_num, sm_partition,
-                           occupancy, preempt_flag, be ? be->task_slot_base + (size_t)be_idx * 4 : 0, dispatch_ctrl,
-                           stream);
+                           occupancy, be ? be->task_slot_base + (size_t)be_idx * 4 : 0, dispatch_ctrl,
+                           be ? be->dispatch_ctrl : 0, stream, be_stream);
     if (rc != REEF_SUCC) err_ = reef_last_error();
     GPU_RETURN_STATUS(rc);
     return Status::Succ;
@@ -427,13 +430,15 @@ Status HybridExecutor::profile_wave(int idx, int occupancy, int iters, float* us
     int num_sms = 0;
     GPU_RETURN_STATUS(reef_device_num_sms(&num_sms));
     int blocks = std::min(trans_args[idx].block_num, num_sms * occupancy);
+    blocks -= blocks % trans_args[idx].granularity;
+    if (blocks <= 0) blocks = std::min(trans_args[idx].block_num, trans_args[idx].granularity);
     reef_event_t a, b;
     GPU_RETURN_STATUS(reef_event_create(&a));
     GPU_RETURN_STATUS(reef_event_create(&b));
     Status st = Status::Succ;
     auto once = [&]() {
         int rc = reef_dispatch(nullptr, nullptr, kernels[idx], raw_args[idx].data(), 0, blocks, 0, occupancy,
-                               preempt_flag, task_slot_base + (size_t)idx * 4, dispatch_ctrl, s);
+                               task_slot_base + (size_t)idx * 4, dispatch_ctrl, dispatch_ctrl, s, nullptr);
         if (rc != REEF_SUCC) { err_ = reef_last_error(); st = (Status)rc; }
     };
     once();

@@ -88,6 +88,7 @@ public:
         int block_offset = 0;
         int threads = 0;
         int min_occupancy = 1;    // minimal blocks/SM the real-time kernel needs to finish in one wave
+        int granularity = 1;      // block ranges handed to the dispatcher are multiples of this (cluster size)
         reef_kernel_attrs_t resource{};
         KernelProfile profile;
     };
@@ -109,8 +110,11 @@ public:
 
     Status launch_preempt_kernel(int kernel_offset, GPUStream_t stream);
     // dispatcher launch of kernel `rt_idx`, padded with logical blocks of `be`'s kernel `be_idx`
+    // `be_stream` non-null (or a tensor-core kernel on either side): the best-effort blocks are launched
+    // beside the real-time kernel on be_stream instead of inside one grid
     Status launch_dispatch(int rt_idx, HybridExecutor* be, int be_idx, int be_block_offset, int be_block_num,
-                           int sm_partition, int occupancy, GPUStream_t stream);
+                           int sm_partition, int occupancy, GPUStream_t stream, GPUStream_t be_stream = nullptr);
+    bool has_tensor_core_kernels() const { return has_tc; }
     // CUDA graph of the whole kernel list on `stream` (captured lazily on first use)
     Status execute_graph(GPUStream_t stream);
     // every kernel through the dispatcher without a best-effort partner, then sync
@@ -134,6 +138,7 @@ protected:
     GPUDevicePtr_t task_slot_base = 0;
     GPUDevicePtr_t dispatch_ctrl = 0;
     int* task_slots_host = nullptr;
+    bool has_tc = false;
     std::shared_ptr<ModelProfile> model_profile;
     reef_graph_t graph = nullptr;
     GPUStream_t graph_stream = nullptr;

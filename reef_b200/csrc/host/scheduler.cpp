@@ -159,6 +159,7 @@ Status REEFScheduler::new_task(const ModelID& mid, TaskID& tid) {
     task->padding = false;
     task->padding_to_finish = false;
     task->needs_recover = false;
+    task->all_issued_by_padding = false;
     tid = task->id;
     {
         std::unique_lock<std::mutex> lock(task_pool_mtx);
@@ -335,6 +336,7 @@ void REEFScheduler::preempt_reset() {
         auto& q = *be_queues[i];
         if (q.task_queue.empty()) continue;
         auto task = q.task_queue.front();
+        if (task->get_state() == TaskState::Executing && task->all_issued_by_padding) continue;   // nothing to abort
         if (task->get_state() == TaskState::Executing) {
             hit.push_back(task);
             // An event that fires after the flag went up may belong to a kernel that left early, so the
@@ -376,7 +378,7 @@ void REEFScheduler::preempt_wait() {
         auto& q = *be_queues[i];
         if (q.task_queue.empty()) continue;
         auto task = q.task_queue.front();
-        if (task->get_state() != TaskState::Executing) continue;
+        if (task->get_state() != TaskState::Executing || task->all_issued_by_padding) continue;
         for (auto& f : q.inflight) q.free_events.push_back(f.ev);
         q.inflight.clear();
         auto& exe = task->model->executor;
@@ -461,37 +463,42 @@ void REEFScheduler::execute_rt_task(std::shared_ptr<Task>& task) {
     finish_task(task);
 }
 
-// reference: scheduler.cpp:477-683.  Per real-time kernel: pick the first best-effort queue whose head
-// kernel can share the grid (occupancy) and whose one-wave latency fits inside the real-time kernel
-// (profile), size its block count from the SMs the real-time kernel leaves free, launch the dispatcher,
-// and advance the best-effort task's (kernel_offset, block_offset).
+// reference: scheduler.cpp:477-683.  Per real-time kernel: pick a best-effort queue whose head kernel can
+// share the GPU (occupancy) and whose one-wave latency fits inside the real-time kernel (profile), size its
+// block count from the SMs the real-time kernel leaves free, launch both through reef_dispatch, and advance
+// the best-effort task's (kernel_offset, block_offset).  Queues are tried round-robin (the reference always
+// starts at queue 0, scheduler.cpp:533, which starves the later clients under a busy real-time client).
+// When both models consist of logical-block kernels only, the two kernels share ONE persistent dispatcher
+// grid on the real-time stream; as soon as a tensor-core cluster kernel is involved the best-effort blocks
+// are launched beside the real-time kernel on the best-effort queue's own stream.
 void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
     auto& rt_exe = rt_task->model->executor;
     std::vector<std::shared_ptr<Task>> complete_be_tasks;
     auto current_time_point = std::chrono::system_clock::now();
+    const uint32_t nq = be_queue_cnt.load();
 
     for (size_t i = 0; i < rt_exe.num_kernels(); i++) {
         auto sel_start = sclock::now();
         HybridExecutor::KernelArg& rt_args = rt_exe.trans_args[i];
         const int required_occupancy = rt_args.min_occupancy;
         const int rt_latency = std::max(1, rt_args.profile.total_latency);
-        const int logical_layers = align_up<int>(rt_args.block_num, num_sms) / num_sms;
+        const int logical_layers = std::max(1, align_up<int>(rt_args.block_num, num_sms) / num_sms);
 
         Task* final_be_task = nullptr;
         HybridExecutor::KernelArg* final_be_args = nullptr;
+        TaskQueue* final_queue = nullptr;
         int final_occupancy = required_occupancy, final_be_block_num = 0, sm_partition = num_sms;
 
-        uint32_t nq = be_queue_cnt.load();
-        for (uint32_t qi = 0; qi < nq; qi++) {
+        for (uint32_t n = 0; n < nq; n++) {
+            const uint32_t qi = (dkp_next_queue + n) % nq;
             auto& be_queue = be_queues[qi]->task_queue;
             if (be_queue.empty()) continue;
             auto be_task = be_queue.front();
             auto& be_exe = be_task->model->executor;
-            if (be_task->kernel_offset >= (int)be_exe.num_kernels()) continue;
+            if (be_task->kernel_offset >= (int)be_exe.num_kernels()) continue;   // fully issued already
             HybridExecutor::KernelArg& be_args = be_exe.trans_args[be_task->kernel_offset];
 
-            // 1. occupancy of the shared grid: both kernels run 256-thread blocks; the limit is the larger
-            //    dynamic shared memory and the dispatcher's registers
+            // 1. occupancy both kernels can run at
             int merged_occupancy = std::min(rt_args.resource.max_blocks_per_sm, be_args.resource.max_blocks_per_sm);
             if (merged_occupancy < required_occupancy) continue;
 
@@ -513,6 +520,7 @@ void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
             int be_iters = std::max(1, rt_latency / be_latency_per_iter);
             int blocks = (num_sms - part) * be_iters * be_occupancy;
             blocks = std::min(blocks, be_args.block_num - be_task->block_offset);
+            blocks -= blocks % be_args.granularity;   // cluster kernels advance by whole clusters
             if (blocks <= 0) continue;
 
             sm_partition = part;
@@ -520,18 +528,23 @@ void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
             final_be_block_num = blocks;
             final_be_args = &be_args;
             final_be_task = be_task.get();
+            final_queue = be_queues[qi].get();
+            dkp_next_queue = (qi + 1) % nq;
             break;
         }
         kernel_sel_count++;
         kernel_sel_latency_sum += ns_since(sel_start);
 
+        bool side_launch = false;
         if (final_be_task == nullptr) {
             rt_exe.launch_dispatch((int)i, nullptr, 0, 0, 0, num_sms, required_occupancy, rt_queue->stream);
         } else {
+            auto& be_exe = final_be_task->model->executor;
+            side_launch = rt_exe.has_tensor_core_kernels() || be_exe.has_tensor_core_kernels();
             if (final_be_task->start.time_since_epoch().count() == 0) final_be_task->start = current_time_point;
-            rt_exe.launch_dispatch((int)i, &final_be_task->model->executor, final_be_task->kernel_offset,
-                                   final_be_task->block_offset, final_be_block_num, sm_partition, final_occupancy,
-                                   rt_queue->stream);
+            rt_exe.launch_dispatch((int)i, &be_exe, final_be_task->kernel_offset, final_be_task->block_offset,
+                                   final_be_block_num, sm_partition, final_occupancy, rt_queue->stream,
+                                   side_launch ? final_queue->stream : nullptr);
             n_padded_kernels++;
             n_padded_blocks += final_be_block_num;
         }
@@ -547,18 +560,35 @@ void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
                 final_be_task->block_offset = 0;
                 final_be_task->kernel_offset++;
                 final_be_task->launch_offset = final_be_task->kernel_offset;
-                if (final_be_task->kernel_offset >= (int)final_be_task->model->executor.num_kernels()) {
-                    final_be_task->end = current_time_point;
-                    final_be_task->kernel_offset = 0;
+                const int n_be = (int)final_be_task->model->executor.num_kernels();
+                if (final_be_task->kernel_offset >= n_be) {
                     final_be_task->padding_to_finish = true;
-                    complete_be_tasks.push_back(be_queues[final_be_task->qid]->task_queue.front());
-                    be_queues[final_be_task->qid]->task_queue.pop();
+                    if (side_launch) {
+                        // its last blocks are on the best-effort stream: the task completes when that stream
+                        // has drained, which the best-effort branch of the loop sees through the window
+                        reef_event_t ev;
+                        if (!final_queue->free_events.empty()) {
+                            ev = final_queue->free_events.back();
+                            final_queue->free_events.pop_back();
+                        } else {
+                            reef_event_create(&ev);
+                        }
+                        reef_event_record(ev, final_queue->stream);
+                        final_queue->inflight.push_back(InFlight{ev, n_be - 1});
+                        final_be_task->all_issued_by_padding = true;
+                        final_be_task->state.store(TaskState::Executing);
+                    } else {
+                        final_be_task->end = current_time_point;
+                        final_be_task->kernel_offset = 0;
+                        complete_be_tasks.push_back(be_queues[final_be_task->qid]->task_queue.front());
+                        be_queues[final_be_task->qid]->task_queue.pop();
+                    }
                 }
             }
         }
     }
     if (!complete_be_tasks.empty()) {
-        // their last blocks ran inside the dispatcher launches above: complete once the stream drained
+        // their last blocks ran inside the dispatcher grids above: complete once the stream drained
         reef_stream_sync(rt_queue->stream);
         for (auto& t : complete_be_tasks) {
             n_be_tasks++;
@@ -605,6 +635,7 @@ void REEFScheduler::execute_be_task(std::shared_ptr<Task>& task, std::shared_ptr
         retire(*tqueue, *task);
         if (task->launch_offset >= num_kernels && tqueue->inflight.empty()) {
             task->end = std::chrono::system_clock::now();
+            if (task->all_issued_by_padding) n_be_padded_finish++;
             task->state.store(TaskState::Finish);
             task->kernel_offset = 0;
             task->block_offset = 0;

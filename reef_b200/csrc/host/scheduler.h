@@ -66,6 +66,7 @@ public:
         bool padding;
         bool padding_to_finish;
         bool needs_recover;
+        bool all_issued_by_padding;   // every kernel went out as padding; the stream only has to drain
 
     public:
         bool is_preempted() const { return preempted; }
@@ -166,6 +167,7 @@ private:
     std::atomic_bool _shutdown;
     std::atomic<uint64_t> pending_tasks;
 
+    uint32_t dkp_next_queue = 0;
     uint64_t preempt_count, preempt_latency_sum, preempt_latency_max;
     uint64_t kernel_sel_count, kernel_sel_latency_sum;
     uint64_t n_rt_tasks, n_be_tasks, n_be_padded_finish, n_padded_kernels, n_padded_blocks;

@@ -1,0 +1,236 @@
+// Host side of the tcgen05 convolution: tile/split planning, TMA tensor maps, cluster launch.
+#include "conv_tc.cuh"
+
+#include <cstdlib>
+#include <cstring>
+#include <string>
+
+#include "registry.h"
+
+namespace reef {
+
+static int ceil_div_i(int a, int b) { return (a + b - 1) / b; }
+
+// ---- planning (needs no GPU) --------------------------------------------------------------------
+int tc_plan(const ConvP& p, TcPlan* pl) {
+    memset(pl, 0, sizeof(*pl));
+    if (p.nchw || (p.ci % TC_BK) != 0 || p.sh != p.sw || (p.sh != 1 && p.sh != 2)) return REEF_NOT_FOUND;
+    if ((p.ics & 3) || (p.ioff & 3) || (p.ocs & 3) || (p.ooff & 3)) return REEF_NOT_FOUND;
+    if (p.kh * p.kw > 64 || p.ph >= p.kh || p.pw >= p.kw) return REEF_NOT_FOUND;
+    pl->spatial = (p.kh * p.kw > 1 || p.sh > 1 || p.ph || p.pw) ? 1 : 0;
+    if (pl->spatial) {
+        if (p.wo > 224) return REEF_NOT_FOUND;
+        int best = 1;
+        const int rmax = 224 / p.wo;
+        for (int r = 1; r <= rmax && r <= p.ho; r++)
+            if (p.ho % r == 0) best = r;               // largest divisor of Ho that fits the tile
+        if (best * 2 <= (rmax < p.ho ? rmax : p.ho)) best = rmax < p.ho ? rmax : p.ho;   // no useful divisor: ragged last tile
+        pl->rows = best;
+        pl->n_valid = best * p.wo;
+        pl->n_tiles = ceil_div_i(p.ho, best);
+    } else {
+        int t = ceil_div_i(p.ptot, 224);
+        pl->n_valid = ceil_div_i(p.ptot, t);
+        pl->rows = 0;
+        pl->n_tiles = ceil_div_i(p.ptot, pl->n_valid);
+    }
+    pl->n_mma = ceil_div_i(pl->n_valid, 16) * 16;
+    if (pl->n_mma < 16) pl->n_mma = 16;
+    pl->tmem_cols = 32;
+    while (pl->tmem_cols < pl->n_mma) pl->tmem_cols *= 2;
+    pl->m_tiles = ceil_div_i(p.co, TC_BM);
+    pl->cblocks = p.ci / TC_BK;
+    pl->kb_total = p.kh * p.kw * pl->cblocks;
+    // split K over a cluster until about 128 CTAs are in flight, keeping >= 2 K blocks per CTA
+    const int base = pl->m_tiles * pl->n_tiles;
+    int s = 1;
+    while (s < TC_MAX_SPLITS && base * s * 2 <= 128 && pl->kb_total >= 2 * (s * 2)) s *= 2;
+    // every rank must own at least one K block and the cluster size stays a power of two
+    for (;; s /= 2) {
+        pl->kb_per_split = ceil_div_i(pl->kb_total, s);
+        pl->splits = ceil_div_i(pl->kb_total, pl->kb_per_split);
+        if (pl->splits == s || s == 1) break;
+    }
+    pl->b_bytes = pl->n_valid * 128;
+    pl->smem = 1024 + TC_STAGES * (TC_A_BYTES + pl->n_mma * 128) + 128;
+    return REEF_SUCC;
+}
+
+// ---- tensor maps ---------------------------------------------------------------------------------
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static encode_tiled_fn g_encode = nullptr;
+
+static int get_encode() {
+    if (g_encode) return REEF_SUCC;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+        set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return REEF_FAIL;
+    }
+    g_encode = (encode_tiled_fn)fn;
+    return REEF_SUCC;
+}
+
+static int encode(CUtensorMap* tm, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
+                  const cuuint32_t* box) {
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base), dims,
+                          strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+        return REEF_FAIL;
+    }
+    return REEF_SUCC;
+}
+
+static int* g_error_word[16] = {nullptr};
+
+int tc_error_word(int** out) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 16) return REEF_FAIL;
+    if (!g_error_word[dev]) {
+        if (cudaMalloc(&g_error_word[dev], 4) != cudaSuccess || cudaMemset(g_error_word[dev], 0, 4) != cudaSuccess) {
+            set_error("cannot allocate the device error word");
+            return REEF_FAIL;
+        }
+    }
+    *out = g_error_word[dev];
+    return REEF_SUCC;
+}
+
+int tc_build_params(const ConvP& p, const TcPlan& pl, void* const* a, TcParams* P) {
+    int rc = get_encode();
+    if (rc != REEF_SUCC) return rc;
+    memset(P, 0, sizeof(*P));
+    const float* in = (const float*)a[0];
+    const float* wgt = (const float*)a[1];
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)p.ktot, (cuuint64_t)p.co};
+        cuuint64_t strides[1] = {(cuuint64_t)p.ktot * 4};
+        cuuint32_t box[2] = {TC_BK, TC_BM};
+        rc = encode(&P->tm_w, wgt, 2, dims, strides, box);
+        if (rc != REEF_SUCC) return rc;
+    }
+    if (pl.spatial) {
+        const int s = p.sh;
+        for (int ry = 0; ry < s; ry++)
+            for (int rx = 0; rx < s; rx++) {
+                const int nx = (p.wi - rx + s - 1) / s, ny = (p.hi - ry + s - 1) / s;
+                if (nx <= 0 || ny <= 0) continue;
+                const float* base = in + p.ioff + ((size_t)ry * p.wi + rx) * p.ics;
+                cuuint64_t dims[3] = {(cuuint64_t)p.ci, (cuuint64_t)nx, (cuuint64_t)ny};
+                cuuint64_t strides[2] = {(cuuint64_t)s * p.ics * 4, (cuuint64_t)s * p.wi * p.ics * 4};
+                cuuint32_t box[3] = {TC_BK, (cuuint32_t)p.wo, (cuuint32_t)pl.rows};
+                rc = encode(&P->tm_x[ry * s + rx], base, 3, dims, strides, box);
+                if (rc != REEF_SUCC) return rc;
+            }
+    } else {
+        cuuint64_t dims[2] = {(cuuint64_t)p.ci, (cuuint64_t)p.ptot};
+        cuuint64_t strides[1] = {(cuuint64_t)p.ics * 4};
+        cuuint32_t box[2] = {TC_BK, (cuuint32_t)pl.n_valid};
+        rc = encode(&P->tm_x[0], in + p.ioff, 2, dims, strides, box);
+        if (rc != REEF_SUCC) return rc;
+    }
+    P->out = (float*)a[2];
+    P->res = (p.ep & EP_RES) ? (const float*)a[p.i_res] : nullptr;
+    P->bias = (p.ep & EP_BIAS) ? (const float*)a[p.i_bias] : nullptr;
+    P->gamma = (p.ep & EP_GB) ? (const float*)a[p.i_gamma] : nullptr;
+    P->beta = (p.ep & EP_GB) ? (const float*)a[p.i_beta] : nullptr;
+    rc = tc_error_word(&P->error_word);
+    if (rc != REEF_SUCC) return rc;
+    P->co = p.co; P->ptot = p.ptot; P->ocs = p.ocs; P->ooff = p.ooff;
+    P->spatial = pl.spatial; P->wo = p.wo; P->rows = pl.rows;
+    P->n_valid = pl.n_valid; P->n_mma = pl.n_mma; P->tmem_cols = pl.tmem_cols;
+    P->kh = p.kh; P->kw = p.kw; P->stride = p.sh; P->ph = p.ph; P->pw = p.pw;
+    P->cblocks = pl.cblocks; P->kb_total = pl.kb_total; P->kb_per_split = pl.kb_per_split; P->splits = pl.splits;
+    P->ep = 0;
+    if (p.ep & EP_RES) P->ep |= TC_EP_RES;
+    if (p.ep & EP_BIAS) P->ep |= TC_EP_BIAS;
+    if (p.ep & EP_GB) P->ep |= TC_EP_GB;
+    if (p.ep & EP_RELU) P->ep |= TC_EP_RELU;
+    if (p.round_tf32) P->ep |= TC_EP_ROUND;
+    P->b_bytes = pl.b_bytes;
+    P->n_tiles = pl.n_tiles;
+    P->tile_begin = 0;
+    P->pdl = 1;
+    return REEF_SUCC;
+}
+
+static bool g_attr_set[16] = {false};
+static int g_use_pdl = -1;
+
+int tc_launch(const TcParams& P0, const TcPlan& pl, cudaStream_t st, const int* flag, int* slot, int tile_begin,
+              int tile_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 16 && !g_attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute((const void*)reef_conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             200 * 1024);
+        if (e != cudaSuccess) {
+            set_error(std::string("cudaFuncSetAttribute(conv_tc): ") + cudaGetErrorString(e));
+            return REEF_FAIL;
+        }
+        g_attr_set[dev] = true;
+    }
+    if (g_use_pdl < 0) {
+        const char* v = getenv("REEF_PDL");
+        g_use_pdl = (v && v[0] == '0') ? 0 : 1;
+    }
+    TcParams P = P0;
+    P.preempt_flag = flag;
+    P.task_slot = slot;
+    const int tiles = pl.n_tiles * pl.m_tiles;
+    if (tile_count < 0) tile_count = tiles - tile_begin;
+    if (tile_begin < 0 || tile_count <= 0 || tile_begin + tile_count > tiles) {
+        set_error("tensor-core convolution: tile range outside the kernel");
+        return REEF_OUT_OF_RANGE;
+    }
+    P.tile_begin = tile_begin;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(pl.splits, tile_count, 1);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attrs[2];
+    int na = 0;
+    if (pl.splits > 1) {
+        attrs[na].id = cudaLaunchAttributeClusterDimension;
+        attrs[na].val.clusterDim.x = pl.splits;
+        attrs[na].val.clusterDim.y = 1;
+        attrs[na].val.clusterDim.z = 1;
+        na++;
+    }
+    if (g_use_pdl) {
+        attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, reef_conv_tc_kernel, P);
+    if (e != cudaSuccess) {
+        set_error(std::string("cudaLaunchKernelEx(conv_tc): ") + cudaGetErrorString(e));
+        return REEF_FAIL;
+    }
+    return REEF_SUCC;
+}
+
+int tc_func_attrs(const TcPlan& pl, cudaFuncAttributes* fa, int* occ) {
+    cudaError_t e = cudaFuncGetAttributes(fa, (const void*)reef_conv_tc_kernel);
+    if (e != cudaSuccess) {
+        set_error(std::string("cudaFuncGetAttributes(conv_tc): ") + cudaGetErrorString(e));
+        return REEF_FAIL;
+    }
+    *occ = 1;   // 180 KB of shared memory: one CTA per SM
+    (void)pl;
+    return REEF_SUCC;
+}
+
+}  // namespace reef

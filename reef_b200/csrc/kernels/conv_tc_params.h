@@ -1,0 +1,44 @@
+// Parameters of the tcgen05 convolution kernel shared by its host planner and the registry
+// (the kernel itself lives in conv_tc.cuh and is compiled once, in conv_tc.cu).
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+namespace reef {
+
+constexpr int TC_STAGES = 4;
+constexpr int TC_BM = 128;            // output channels per tile (TMEM lanes)
+constexpr int TC_BK = 32;             // fp32 elements per K block = 128 bytes
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 4;
+constexpr int TC_THREADS = 128;
+constexpr int TC_MAX_SPLITS = 8;
+
+struct TcParams {
+    CUtensorMap tm_w;        // weights  dims (K, Cout), box (32, 128)
+    CUtensorMap tm_x[4];     // activations, one per stride sub-lattice (ry*s + rx)
+    float* out;
+    const float* res;
+    const float* bias;
+    const float* gamma;
+    const float* beta;
+    const int* preempt_flag; // best-effort flavour, else nullptr
+    int* task_slot;
+    int* error_word;         // device word set non-zero when a bounded wait expired
+    int co, ptot;
+    int ocs, ooff;
+    int spatial;             // 0: flat [P][C] view, tile = n_valid consecutive pixels; 1: tile = rows x Wo
+    int wo, rows;            // spatial: output width, rows per tile
+    int n_valid;             // pixels per tile
+    int n_mma;               // UMMA N (multiple of 16, >= n_valid)
+    int tmem_cols;           // power of two >= n_mma
+    int kh, kw, stride, ph, pw;
+    int cblocks;             // Cin / 32
+    int kb_total, kb_per_split, splits;
+    int ep;                  // EP_* bits
+    int b_bytes;             // bytes TMA delivers per B stage (box size)
+    int n_tiles;             // pixel tiles; linear tile index = tile_m * n_tiles + tile_n
+    int tile_begin;          // first tile of this launch (dynamic kernel padding launches sub-ranges)
+    int pdl;                 // programmatic dependent launch: weights are fetched before the grid dependency wait
+};
+
+}  // namespace reef

@@ -11,9 +11,18 @@
 #include <string>
 
 #include "conv_simt.cuh"
+#include "conv_tc_params.h"
 #include "simple.cuh"
 
 namespace reef {
+
+static unsigned long long g_launches = 0;
+
+struct TcCache {
+    TcParams params;
+    void* ptrs[kMaxArgs];
+    bool valid = false;
+};
 
 static thread_local std::string g_err;
 void set_error(const std::string& s) { g_err = s; }
@@ -219,6 +228,20 @@ static int build_spec(const std::string& name, KernelSpec* s) {
             s->dyn_smem = kConvSimtSmem;
             return REEF_SUCC;
         }
+        if (impl == 1) {
+            // tcgen05 TF32 implicit GEMM; "rt0" in the name keeps full fp32 bits in the stored activations
+            p.round_tf32 = (int)a.get("rt", 1);
+            if (tc_plan(p, &s->tc) != REEF_SUCC) {
+                set_error("shape not supported by the tensor-core convolution: " + name);
+                return REEF_NOT_FOUND;
+            }
+            t.family = F_CONV_TC;
+            t.nblocks = s->tc.splits * s->tc.n_tiles * s->tc.m_tiles;
+            s->dyn_smem = (uint32_t)s->tc.smem;
+            s->block[0] = TC_THREADS;
+            s->tensor_core = 1;
+            return REEF_SUCC;
+        }
         set_error("unknown conv2d variant in: " + name);
         return REEF_NOT_FOUND;
     }
@@ -232,6 +255,12 @@ bad:
 int plan_kernel(const char* name, KernelSpec* s) {
     int rc = build_spec(name, s);
     if (rc != REEF_SUCC) return rc;
+    if (s->task.family == F_CONV_TC) {
+        s->grid[0] = (uint32_t)s->tc.splits;
+        s->grid[1] = (uint32_t)(s->tc.n_tiles * s->tc.m_tiles);
+        s->grid[2] = 1;
+        return REEF_SUCC;
+    }
     s->grid[0] = (uint32_t)s->task.nblocks;
     s->grid[1] = 1;
     s->grid[2] = 1;
@@ -376,7 +405,6 @@ int launch_delay(cudaStream_t st, unsigned long long ns) {
 // ------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------
-static unsigned long long g_launches = 0;
 unsigned long long launch_count() { return g_launches; }
 void add_launches(unsigned long long n) { g_launches += n; }
 
@@ -417,11 +445,30 @@ static bool dims_match(const KernelSpec& s, const uint32_t dims[6], uint32_t sme
            dims[4] == s.block[1] && dims[5] == s.block[2] && smem == s.dyn_smem;
 }
 
+static int launch_tc(const KernelSpec& s, cudaStream_t st, void** args, const int* flag, int* slot, int tile_begin = 0,
+                     int tile_count = -1) {
+    if (!s.tc_cache) s.tc_cache = std::make_shared<TcCache>();
+    TcCache& c = *s.tc_cache;
+    bool same = c.valid;
+    for (int i = 0; i < s.nargs && same; i++) same = c.ptrs[i] == *reinterpret_cast<void**>(args[i]);
+    if (!same) {
+        void* ptrs[kMaxArgs] = {nullptr};
+        for (int i = 0; i < s.nargs; i++) ptrs[i] = *reinterpret_cast<void**>(args[i]);
+        int rc = tc_build_params(s.task.p.conv, s.tc, ptrs, &c.params);
+        if (rc != REEF_SUCC) return rc;
+        for (int i = 0; i < s.nargs; i++) c.ptrs[i] = ptrs[i];
+        c.valid = true;
+    }
+    g_launches++;
+    return tc_launch(c.params, s.tc, st, flag, slot, tile_begin, tile_count);
+}
+
 int launch_plain(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cudaStream_t st, void** args) {
     if (!dims_match(s, dims, smem)) {
         set_error("launch_params / shared_memory do not match the kernel plan of " + s.name);
         return REEF_OUT_OF_RANGE;
     }
+    if (s.task.family == F_CONV_TC) return launch_tc(s, st, args, nullptr, nullptr);
     KTask t;
     fill_args(s, args, &t);
     void* kargs[] = {&t};
@@ -437,6 +484,7 @@ int launch_be(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cudaSt
         set_error("launch_params / shared_memory do not match the kernel plan of " + s.name);
         return REEF_OUT_OF_RANGE;
     }
+    if (s.task.family == F_CONV_TC) return launch_tc(s, st, args, flag, slot);
     KTask t;
     fill_args(s, args, &t);
     void* kargs[] = {&t, (void*)&flag, (void*)&slot};
@@ -446,46 +494,115 @@ int launch_be(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cudaSt
     return check_cuda(e, "cudaLaunchKernel(be)");
 }
 
+// One padded step.  Two shapes:
+//  * both kernels are logical-block families and no separate best-effort stream is given: ONE persistent
+//    dispatcher grid on `st` runs the real-time blocks and the best-effort blocks (SM-partitioned);
+//  * otherwise (a tensor-core cluster kernel is involved, or `be_st` is given): the real-time kernel runs
+//    as its own launch on `st` and the best-effort block range runs beside it on `be_st` — the hardware
+//    block scheduler places the best-effort blocks on the SMs the real-time kernel leaves free, the
+//    real-time stream having the greater priority.  Best-effort blocks launched here do not read the
+//    preempt flag (they were sized to fit beside the real-time kernel) but do count into the task slot.
 int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, void** be_args, int be_off,
-                    int be_num, int sm_partition, int occupancy, int num_sms, int* be_slot, int* ctrl,
-                    cudaStream_t st) {
-    KTask trt, tbe;
-    uint32_t smem = 0;
-    if (rt != nullptr) {
-        fill_args(*rt, rt_args, &trt);
-        smem = rt->dyn_smem;
-    } else {
-        memset(&trt, 0, sizeof(trt));   // nblocks = 0: the real-time phase ends at once
-    }
-    if (be != nullptr && be_num > 0) {
-        fill_args(*be, be_args, &tbe);
-        if (be->dyn_smem > smem) smem = be->dyn_smem;
-        if (be_off < 0 || be_off + be_num > tbe.nblocks) {
-            set_error("best-effort block range outside the kernel");
-            return REEF_OUT_OF_RANGE;
-        }
-    } else {
-        memset(&tbe, 0, sizeof(tbe));
-        be_num = 0;
-    }
+                    int be_num, int sm_partition, int occupancy, int num_sms, int* be_slot, int* ctrl, int* be_ctrl,
+                    cudaStream_t st, cudaStream_t be_st) {
+    if (be == nullptr) be_num = 0;
+    const bool rt_tc = rt != nullptr && rt->task.family == F_CONV_TC;
+    const bool be_tc = be_num > 0 && be->task.family == F_CONV_TC;
     if (occupancy < 1) occupancy = 1;
-    int grid = num_sms * occupancy;
-    void* kargs[] = {&trt, &tbe, &be_off, &be_num, &sm_partition, (void*)&be_slot, (void*)&ctrl};
-    cudaError_t e = cudaLaunchKernel((const void*)k_dispatch, dim3(grid), dim3(kThreads), kargs, smem, st);
-    g_launches++;
-    return check_cuda(e, "cudaLaunchKernel(dispatch)");
+    if (be_num > 0 && (be_off < 0 || be_off + be_num > be->task.nblocks)) {
+        set_error("best-effort block range outside the kernel");
+        return REEF_OUT_OF_RANGE;
+    }
+    const bool split_launch = rt_tc || be_tc || (be_st != nullptr && be_num > 0);
+
+    if (!split_launch) {
+        KTask trt, tbe;
+        uint32_t smem = 0;
+        if (rt != nullptr) {
+            fill_args(*rt, rt_args, &trt);
+            smem = rt->dyn_smem;
+        } else {
+            memset(&trt, 0, sizeof(trt));   // nblocks = 0: the real-time phase ends at once
+        }
+        if (be_num > 0) {
+            fill_args(*be, be_args, &tbe);
+            if (be->dyn_smem > smem) smem = be->dyn_smem;
+        } else {
+            memset(&tbe, 0, sizeof(tbe));
+        }
+        int grid = num_sms * occupancy;
+        void* kargs[] = {&trt, &tbe, &be_off, &be_num, &sm_partition, (void*)&be_slot, (void*)&ctrl};
+        cudaError_t e = cudaLaunchKernel((const void*)k_dispatch, dim3(grid), dim3(kThreads), kargs, smem, st);
+        g_launches++;
+        return check_cuda(e, "cudaLaunchKernel(dispatch)");
+    }
+
+    // real-time part
+    if (rt != nullptr) {
+        int rc;
+        if (rt_tc) {
+            rc = launch_tc(*rt, st, rt_args, nullptr, nullptr);
+        } else {
+            KTask trt, tbe;
+            fill_args(*rt, rt_args, &trt);
+            memset(&tbe, 0, sizeof(tbe));
+            int zero = 0, part = num_sms;
+            int* null_slot = nullptr;
+            int grid = num_sms * occupancy;
+            if (grid > trt.nblocks) grid = trt.nblocks;
+            void* kargs[] = {&trt, &tbe, &zero, &zero, &part, (void*)&null_slot, (void*)&ctrl};
+            cudaError_t e = cudaLaunchKernel((const void*)k_dispatch, dim3(grid), dim3(kThreads), kargs, rt->dyn_smem, st);
+            g_launches++;
+            rc = check_cuda(e, "cudaLaunchKernel(dispatch rt)");
+        }
+        if (rc != REEF_SUCC) return rc;
+    }
+    // best-effort part
+    if (be_num > 0) {
+        cudaStream_t bs = be_st != nullptr ? be_st : st;
+        if (be_tc) {
+            const int sp = be->tc.splits;
+            if (be_off % sp != 0 || be_num % sp != 0) {
+                set_error("best-effort block range of a cluster kernel must be a multiple of its cluster size");
+                return REEF_OUT_OF_RANGE;
+            }
+            return launch_tc(*be, bs, be_args, nullptr, be_slot, be_off / sp, be_num / sp);
+        }
+        KTask trt, tbe;
+        memset(&trt, 0, sizeof(trt));
+        fill_args(*be, be_args, &tbe);
+        int part = 0;
+        int grid = be_num < num_sms * occupancy ? be_num : num_sms * occupancy;
+        // its own control block keeps this grid's tickets apart from the real-time grid's
+        int* ctrl2 = be_ctrl != nullptr ? be_ctrl : ctrl;
+        if (be_ctrl == nullptr && rt != nullptr) {
+            set_error("a separate best-effort launch needs its own control block");
+            return REEF_FAIL;
+        }
+        void* kargs[] = {&trt, &tbe, &be_off, &be_num, &part, (void*)&be_slot, (void*)&ctrl2};
+        cudaError_t e = cudaLaunchKernel((const void*)k_dispatch, dim3(grid), dim3(kThreads), kargs, be->dyn_smem, bs);
+        g_launches++;
+        return check_cuda(e, "cudaLaunchKernel(dispatch be)");
+    }
+    return REEF_SUCC;
 }
 
 int kernel_attrs(const KernelSpec& s, reef_kernel_attrs_t* out) {
     cudaFuncAttributes fa;
-    const void* fn = plain_fn(s.task.family);
-    int rc = check_cuda(cudaFuncGetAttributes(&fa, fn), "cudaFuncGetAttributes");
-    if (rc != REEF_SUCC) return rc;
     int threads = s.block[0] * s.block[1] * s.block[2];
     int occ = 0;
-    rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, threads, s.dyn_smem),
-                    "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
-    if (rc != REEF_SUCC) return rc;
+    int rc;
+    if (s.task.family == F_CONV_TC) {
+        rc = tc_func_attrs(s.tc, &fa, &occ);
+        if (rc != REEF_SUCC) return rc;
+    } else {
+        const void* fn = plain_fn(s.task.family);
+        rc = check_cuda(cudaFuncGetAttributes(&fa, fn), "cudaFuncGetAttributes");
+        if (rc != REEF_SUCC) return rc;
+        rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, threads, s.dyn_smem),
+                        "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
+        if (rc != REEF_SUCC) return rc;
+    }
     out->num_blocks = s.task.nblocks;
     out->threads = threads;
     out->regs_per_thread = fa.numRegs;
@@ -496,6 +613,7 @@ int kernel_attrs(const KernelSpec& s, reef_kernel_attrs_t* out) {
     out->flops = s.flops;
     out->bytes = s.bytes;
     out->tensor_core = s.tensor_core;
+    out->cluster = s.task.family == F_CONV_TC ? s.tc.splits : 1;
     return REEF_SUCC;
 }
 

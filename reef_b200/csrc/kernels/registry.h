@@ -3,12 +3,24 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <memory>
 #include <string>
 
 #include "../../../include/reef_cuda.h"
 #include "task.cuh"
 
 namespace reef {
+
+struct TcParams;
+
+// tile / split-K plan of the tcgen05 convolution (conv_tc.cu)
+struct TcPlan {
+    int spatial, rows, n_valid, n_mma, tmem_cols;
+    int n_tiles, m_tiles, cblocks, kb_total, kb_per_split, splits;
+    int b_bytes, smem;
+};
+
+struct TcCache;   // tensor maps of one kernel call, rebuilt when its pointers change
 
 struct KernelSpec {
     std::string name;
@@ -19,6 +31,8 @@ struct KernelSpec {
     int nargs;
     double flops, bytes;   // algorithmic work of one launch
     int tensor_core;
+    TcPlan tc;
+    mutable std::shared_ptr<TcCache> tc_cache;
 };
 
 void set_error(const std::string& s);
@@ -29,11 +43,19 @@ int launch_plain(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cud
 int launch_be(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cudaStream_t st, const int* flag,
               int* slot, void** args);
 int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, void** be_args, int be_off,
-                    int be_num, int sm_partition, int occupancy, int num_sms, int* be_slot, int* ctrl,
-                    cudaStream_t st);
+                    int be_num, int sm_partition, int occupancy, int num_sms, int* be_slot, int* ctrl, int* be_ctrl,
+                    cudaStream_t st, cudaStream_t be_st);
 int kernel_attrs(const KernelSpec& s, reef_kernel_attrs_t* out);
 int dispatch_occupancy(uint32_t smem, int* occ);
 int launch_delay(cudaStream_t st, unsigned long long ns);
+
+// conv_tc.cu
+int tc_plan(const ConvP& p, TcPlan* pl);
+int tc_build_params(const ConvP& p, const TcPlan& pl, void* const* args, TcParams* P);
+int tc_launch(const TcParams& P, const TcPlan& pl, cudaStream_t st, const int* flag, int* slot, int tile_begin = 0,
+              int tile_count = -1);
+int tc_func_attrs(const TcPlan& pl, cudaFuncAttributes* fa, int* occ);
+int tc_error_word(int** out);
 unsigned long long launch_count();
 void add_launches(unsigned long long n);
 

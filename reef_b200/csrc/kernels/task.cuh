@@ -29,7 +29,9 @@ enum Family : int {
     F_COPY,
     F_DENSE,
     F_SOFTMAX,
-    F_COUNT
+    F_COUNT,
+    // families with their own __global__ kernel (not hosted by the 256-thread logical-block wrappers)
+    F_CONV_TC = 100
 };
 
 // epilogue / option bits
@@ -42,6 +44,7 @@ struct ConvP {
     int tiles_p, tiles_c;    // tile grid: pixels x out-channels
     int ep;                  // EP_* bits
     int i_res, i_bias, i_gamma, i_beta;   // positions in the arg list, -1 when absent
+    int round_tf32;          // tensor-core variant: store activations rounded to the nearest TF32 value
 };
 
 struct PoolP {

@@ -26,19 +26,44 @@ _BUILDERS = {
 }
 
 
+def _generator_stamp() -> str:
+    """Changes whenever the generator sources or the kernel library (launch plans) change, so cached
+    resource directories written by an older build are regenerated instead of silently reused."""
+    import glob
+    import hashlib
+    h = hashlib.sha256()
+    here = os.path.dirname(os.path.abspath(__file__))
+    for f in sorted(glob.glob(os.path.join(here, "*.py"))):
+        with open(f, "rb") as fh:
+            h.update(fh.read())
+    stamp = os.path.join(os.path.dirname(here), "libreef_cuda.so.stamp")
+    if os.path.exists(stamp):
+        with open(stamp, "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()
+
+
 def available():
     return ["mocked_kernel"] + sorted(_BUILDERS)
 
 
 def generate(model: str, out_root: str | None = None, *, force: bool = False, variant: str = "", **kw) -> str:
-    """Write the resources of `model` under <out_root>/<model><variant>/ and return that directory."""
+    """Write the resources of `model` under <out_root>/<model><variant>/ and return that directory.
+
+    ``variant="_fp32"`` selects the exact-fp32 schedule (CUDA-core convolutions only); the default
+    schedule uses the tcgen05 TF32 convolution wherever the registry supports the shape."""
+    if variant == "_fp32":
+        kw.setdefault("conv_impl", "simt")
     from .. import capi
     out_root = out_root or DEFAULT_DIR
     name = model + variant
     out_dir = os.path.join(out_root, name)
     base = os.path.join(out_dir, name)
     exts = (".json", ".profile.json") if model == "mocked_kernel" else (".json", ".param", ".profile.json")
-    if not force and all(os.path.exists(base + ext) for ext in exts):
+    stamp_path = base + ".generator"
+    stamp = _generator_stamp() + repr(sorted(kw.items()))
+    if not force and all(os.path.exists(base + ext) for ext in exts) and os.path.exists(stamp_path) \
+            and open(stamp_path).read() == stamp:
         return out_dir
     if model == "mocked_kernel":
         g = build_mocked_kernel()
@@ -52,8 +77,12 @@ def generate(model: str, out_root: str | None = None, *, force: bool = False, va
         from .graph import default_profile
         with open(base + ".profile.json", "w") as f:
             json.dump(default_profile(j), f)
+        with open(stamp_path, "w") as f:
+            f.write(stamp)
         return out_dir
     b = _BUILDERS[model](**kw)
     b.g.name = name
     b.g.write(out_dir, capi.plan_fn)
+    with open(stamp_path, "w") as f:
+        f.write(stamp)
     return out_dir

@@ -39,6 +39,13 @@ from .graph import Graph, Tensor, kname
 BN_EPS = 2e-5
 
 
+def round_tf32(a):
+    """Round fp32 values to the nearest TF32 (10 explicit mantissa bits), ties away from zero."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    u = (u + np.uint32(0x1000)) & np.uint32(0xFFFFE000)
+    return u.view(np.float32)
+
+
 class Builder:
     def __init__(self, name: str, seed: int, conv_impl: str = "auto"):
         self.g = Graph(name)
@@ -101,9 +108,8 @@ class Builder:
         if out is None:
             out = self.new_act(ho, wo, co)
         assert (out.h, out.w, out.c) == (ho, wo, co)
-        w_idx = self.g.param(wgt)
         op = "fused_nn_conv2d"
-        args = [x.idx, w_idx, out.idx]
+        args = [x.idx, None, out.idx]   # weight slot filled once the variant (and its rounding) is known
         if residual is not None:
             assert (residual.h, residual.w, residual.c) == (ho, wo, co) and residual.cstride == co
             op += "_add"
@@ -127,18 +133,30 @@ class Builder:
         if out.cstride != co or out.coff:
             attrs["ocs"] = out.cstride
             attrs["ooff"] = out.coff
-        impl = self.pick_conv_impl(attrs)
+        impl = self.pick_conv_impl(op, attrs)
         if impl:
             attrs["v"] = impl
+            # the tensor core reads 19 bits of each fp32 operand; weights of tensor-core layers are stored
+            # already rounded to the nearest TF32 value, so the model in the .param file is exactly the
+            # model the hardware multiplies with (and the oracle reads the same bytes)
+            wgt = round_tf32(wgt)
+        args[1] = self.g.param(wgt)
         self.g.kernel(kname(op, **attrs), args)
         return out
 
-    def pick_conv_impl(self, attrs) -> int:
-        """0 = fp32 SIMT implicit GEMM (default).  Other variants are chosen by
-        the model builders through ``conv_impl``."""
-        if self.conv_impl in ("auto", "simt"):
+    def pick_conv_impl(self, op, attrs) -> int:
+        """0 = fp32 implicit GEMM on CUDA cores; 1 = tcgen05 TF32 implicit GEMM (fp32 accumulate).
+        ``conv_impl``: "simt" forces 0, "auto"/"tc" asks the kernel registry whether variant 1
+        supports the shape (channels a multiple of 32, stride 1 or 2, channels-last input) and
+        falls back to 0 otherwise."""
+        if self.conv_impl == "simt":
             return 0
-        return int(self.conv_impl)
+        from .. import capi
+        try:
+            capi.kernel_plan(kname(op, **attrs, v=1))
+            return 1
+        except capi.ReefError:
+            return 0
 
     def pool(self, x: Tensor, kind: str, k: int, stride: int, pad: int, *,
              bias=None, out: Tensor | None = None, count_include_pad=True, ceil_mode=False) -> Tensor:

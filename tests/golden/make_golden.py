@@ -24,8 +24,9 @@ from torch_ref import run_graph  # noqa: E402
 
 def main():
     root = os.environ.get("REEF_RESOURCE_DIR", "/tmp/reef_b200_resources")
-    d = resources.generate("resnet18_64", root)
-    base = os.path.join(d, "resnet18_64")
+    # the exact-fp32 schedule (unrounded weights, CUDA-core convolutions)
+    d = resources.generate("resnet18_64", root, variant="_fp32")
+    base = os.path.join(d, "resnet18_64_fp32")
     x = np.full(3 * 64 * 64, 10.0, np.float32)
     o = oracle.OracleExecutor(base + ".json", base + ".param", acc64=True)
     o.set_input("data", x)
@@ -35,7 +36,7 @@ def main():
     li = j["kernels"][-1]["args"][0]
     err = np.abs(o.storage[li] - st[li]).max() / np.abs(st[li]).max()
     assert err < 1e-6, err
-    np.savez(os.path.join(HERE, "resnet18_64_const10.npz"), logits=st[li].astype(np.float32),
+    np.savez(os.path.join(HERE, "resnet18_64_fp32_const10.npz"), logits=st[li].astype(np.float32),
              probs=st[names.index("output")].astype(np.float32))
     print("wrote resnet18_64_const10.npz; oracle(acc64) vs torch(float64) rel err", err)
 

@@ -13,6 +13,12 @@ FP32_TOL = 1e-3    # fp32 kernels: max |y - ref| / max |ref|
 TF32_TOL = 1e-2    # TF32 tensor-core kernels
 
 
+def tol_for(base):
+    """1e-2 when the schedule contains tensor-core (TF32) kernels, else 1e-3."""
+    j = json.load(open(base + ".json"))
+    return TF32_TOL if any("_v1" in k["name"] for k in j["kernels"]) else FP32_TOL
+
+
 def load_executor(base, params=True):
     e = capi.HybridExecutor(0)
     e.load_model_from_file(base + ".json", base + ".profile.json" if os.path.exists(base + ".profile.json") else None)

@@ -94,10 +94,10 @@ def test_oracle_graph_vs_torch(gen, model):
 
 
 def test_golden_resnet18_64(gen):
-    """Committed fixture (tests/golden/make_golden.py): logits and probabilities of resnet18_64 for the
+    """Committed fixture (tests/golden/make_golden.py): logits and probabilities of resnet18_64 (fp32 schedule) for the
     constant input 10.0 — the input the reference's own DNN test uses (reference: test.cpp:44-46)."""
-    base = gen("resnet18_64")
-    g = np.load(os.path.join(GOLDEN, "resnet18_64_const10.npz"))
+    base = gen("resnet18_64", variant="_fp32")
+    g = np.load(os.path.join(GOLDEN, "resnet18_64_fp32_const10.npz"))
     o = oracle.OracleExecutor(base + ".json", base + ".param")
     o.set_input("data", np.full(3 * 64 * 64, 10.0, np.float32))
     o.execute()

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from conftest import rel_err, seeded_input
-from gpu_util import FP32_TOL, all_storage, compare_layers, load_executor, single_kernel_model
+from gpu_util import FP32_TOL, TF32_TOL, all_storage, compare_layers, load_executor, single_kernel_model, tol_for
 from oracle import oracle
 from reef_b200 import capi
 
@@ -66,11 +66,41 @@ CONV_CASES = [
 ]
 
 
+# tensor-core variant (v1): flat 1x1, spatial 3x3, stride-2 sub-lattices, cluster split-K, ragged tiles,
+# fewer than 128 output channels, a K range that does not divide evenly over the cluster
+TC_CASES = [
+    ("fused_nn_conv2d", 64, 8, 8, 128, 1, 1, 1, 0, 0),
+    ("fused_nn_conv2d_add_nn_relu", 32, 8, 8, 64, 1, 1, 1, 0, 0),
+    ("fused_nn_conv2d_add", 256, 14, 14, 1024, 1, 1, 1, 0, 0),
+    ("fused_nn_conv2d_add_nn_relu", 1024, 14, 14, 256, 1, 1, 1, 0, 0),
+    ("fused_nn_conv2d_add_nn_relu", 256, 14, 14, 256, 3, 3, 1, 1, 1),
+    ("fused_nn_conv2d_add_nn_relu", 64, 56, 56, 64, 3, 3, 1, 1, 1),
+    ("fused_nn_conv2d_add_add_nn_relu", 64, 56, 56, 256, 1, 1, 1, 0, 0),
+    ("fused_nn_conv2d_add_nn_relu", 256, 56, 56, 128, 1, 1, 2, 0, 0),
+    ("fused_nn_conv2d_add_nn_relu", 128, 28, 28, 256, 3, 3, 2, 1, 1),
+    ("fused_nn_conv2d_add_multiply_add_nn_relu", 512, 7, 7, 2048, 1, 1, 1, 0, 0),
+    ("fused_nn_conv2d_add_nn_relu", 512, 7, 7, 512, 3, 3, 1, 1, 1),
+    ("fused_nn_conv2d_nn_relu", 96, 17, 17, 160, 1, 7, 1, 0, 3),
+    ("fused_nn_conv2d_add_nn_relu", 160, 9, 13, 72, 5, 5, 1, 2, 2),
+    ("fused_nn_conv2d_add_nn_relu", 64, 15, 15, 96, 3, 3, 2, 0, 0),
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES, ids=[c[0][9:] + f"_{c[1]}x{c[4]}k{c[5]}{c[6]}s{c[7]}h{c[2]}" for c in TC_CASES])
+def test_conv_tensor_core_parity(tmp_path, case):
+    from gpu_util import TF32_TOL
+    _conv_case(tmp_path, case, "_v1", TF32_TOL)
+
+
 @pytest.mark.parametrize("case", CONV_CASES, ids=[c[0][9:] + f"_{c[1]}x{c[4]}k{c[5]}{c[6]}s{c[7]}" for c in CONV_CASES])
 def test_conv_kernel_parity(tmp_path, case):
+    _conv_case(tmp_path, case, "", FP32_TOL)
+
+
+def _conv_case(tmp_path, case, suffix, tol):
     fam, ci, hi, wi, co, kh, kw, s, ph, pw = case
     ho, wo = (hi + 2 * ph - kh) // s + 1, (wi + 2 * pw - kw) // s + 1
-    name = f"{fam}__ci{ci}_hi{hi}_wi{wi}_co{co}_kh{kh}_kw{kw}_sh{s}_sw{s}_ph{ph}_pw{pw}"
+    name = f"{fam}__ci{ci}_hi{hi}_wi{wi}_co{co}_kh{kh}_kw{kw}_sh{s}_sw{s}_ph{ph}_pw{pw}{suffix}"
     specs = [("in", ci * hi * wi), ("param", co * kh * kw * ci), ("out", ho * wo * co)]
     tail = fam[len("fused_nn_conv2d"):].replace("_nn_relu", "")
     if tail == "_add":
@@ -87,18 +117,27 @@ def test_conv_kernel_parity(tmp_path, case):
         o.set_input(k, v)
     e.execute()
     o.execute()
-    assert rel_err(e.get_output(), o.get_output()) < FP32_TOL
+    err = rel_err(e.get_output(), o.get_output())
+    print(name, "rel err", err, "launch", capi.kernel_plan(name)[0])
+    assert capi.device_error() == 0
+    assert err < tol
     # the best-effort flavour and the dispatcher run the same body: bit-identical to the raw launch
     raw = e.get_output()
     e.execute_preemptable()
     assert np.array_equal(e.get_output(), raw)
     e.execute_dispatch()
     assert np.array_equal(e.get_output(), raw)
+    e.execute_graph()
+    assert np.array_equal(e.get_output(), raw)
+    assert capi.device_error() == 0
 
 
+@pytest.mark.parametrize("variant", ["", "_fp32"])
 @pytest.mark.parametrize("model", ["resnet18_64", "resnet50_64"])
-def test_small_resnet_layer_by_layer(gen, model):
-    base = gen(model)
+def test_small_resnet_layer_by_layer(gen, model, variant):
+    base = gen(model, variant=variant)
+    tol = tol_for(base)
+    assert tol == (TF32_TOL if variant == "" else FP32_TOL)
     j = json.load(open(base + ".json"))
     x = seeded_input(3 * 64 * 64)
     e = load_executor(base)
@@ -107,27 +146,30 @@ def test_small_resnet_layer_by_layer(gen, model):
     o.set_input("data", x)
     e.execute()
     o.execute()
-    worst = compare_layers(e, o, j)
-    print(model, "worst layer rel err", worst)
+    worst = compare_layers(e, o, j, lambda kname: tol)
+    print(model + variant, "worst layer rel err", worst)
+    assert capi.device_error() == 0
     assert abs(float(e.get_output().sum()) - 1.0) < 1e-4
 
 
 def test_resnet18_golden_const10(gen):
     import os
-    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "resnet18_64_const10.npz"))
-    base = gen("resnet18_64")
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "resnet18_64_fp32_const10.npz"))
+    base = gen("resnet18_64", variant="_fp32")
+    tol = tol_for(base)
     j = json.load(open(base + ".json"))
     e = load_executor(base)
     e.set_input("data", np.full(3 * 64 * 64, 10.0, np.float32))
     e.execute()
     li = j["kernels"][-1]["args"][0]
-    assert rel_err(e.get_data(li, 4000), g["logits"]) < FP32_TOL
-    assert rel_err(e.get_output(), g["probs"]) < FP32_TOL
+    assert rel_err(e.get_data(li, 4000), g["logits"]) < tol
+    assert rel_err(e.get_output(), g["probs"]) < tol
 
 
-@pytest.mark.parametrize("model,tol", [("resnet18", FP32_TOL), ("resnet152", FP32_TOL)])
-def test_full_size_resnet_logits_and_probs(gen, model, tol):
-    base = gen(model)
+@pytest.mark.parametrize("model,variant", [("resnet18", ""), ("resnet18", "_fp32"), ("resnet152", ""), ("resnet152", "_fp32")])
+def test_full_size_resnet_logits_and_probs(gen, model, variant):
+    base = gen(model, variant=variant)
+    tol = tol_for(base)
     j = json.load(open(base + ".json"))
     x = seeded_input(3 * 224 * 224, seed=11)
     e = load_executor(base)
@@ -139,7 +181,8 @@ def test_full_size_resnet_logits_and_probs(gen, model, tol):
     li = j["kernels"][-1]["args"][0]
     err_logits = rel_err(e.get_data(li, 4000), o.storage[li])
     err_probs = rel_err(e.get_output(), o.get_output())
-    print(model, "logits rel err", err_logits, "probs rel err", err_probs)
+    print(model + variant, "logits rel err", err_logits, "probs rel err", err_probs, "tol", tol)
+    assert capi.device_error() == 0
     assert err_logits < tol and err_probs < tol
     # graph replay, dispatcher and best-effort flavour give the same bytes as the raw launches
     raw = e.get_output()

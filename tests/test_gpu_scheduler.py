@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from conftest import rel_err, seeded_input
-from gpu_util import FP32_TOL
+from gpu_util import FP32_TOL, tol_for
 from oracle import oracle
 from reef_b200 import capi
 
@@ -67,6 +67,7 @@ def test_scheduler_resnet18_rt_and_be_all_modes(gen, mode):
     base = gen("resnet18")
     x = seeded_input(3 * 224 * 224, seed=3)
     want = _oracle_out(base, x)
+    FP32_TOL = tol_for(base)
     s = S(mode)
     s.run()
     rt = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
@@ -153,6 +154,7 @@ def test_closed_loop_clients_rt_with_be(gen):
     base = gen("resnet18")
     x = seeded_input(3 * 224 * 224, seed=9)
     want = _oracle_out(base, x)
+    FP32_TOL = tol_for(base)
     s = S(S.REEF)
     s.run()
     rt = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
