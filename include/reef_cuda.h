@@ -106,6 +106,12 @@ REEF_API reef_status reef_module_get_kernel(reef_module_t mod, const char* name,
  * "shared_memory".  Needs no GPU; the resource generator calls it so json and registry agree. */
 REEF_API reef_status reef_kernel_plan(const char* name, uint32_t dims[6], uint32_t* dyn_smem, int* num_args);
 
+/* Binds a kernel handle to its device pointers ahead of the first launch (no reference counterpart): builds
+ * the TMA tensor maps of tensor-core kernels and does every one-time allocation or attribute call, so
+ * that the first reef_launch can already be part of a CUDA-graph capture.  Optional: a launch prepares
+ * lazily when the pointers it is given differ from the prepared ones. */
+REEF_API reef_status reef_kernel_prepare(reef_kernel_t k, void** args);
+
 /* GPUConfig::KernelResource + calculate_occupancy (reference: hip_impl.h:62-74, hip_impl.cpp:34-74). */
 typedef struct {
     int num_blocks;        /* logical thread blocks of one launch                           */
@@ -170,6 +176,14 @@ REEF_API reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us);
  * instead of hanging or trapping.  Reads the word of the current device (after the caller synchronised the
  * stream of interest) and clears it; *value != 0 means some wait expired and the outputs are not valid. */
 REEF_API reef_status reef_device_error(int* value);
+
+/* Phase trace of the tensor-core convolution (no reference counterpart; the reference has wall-clock stamps
+ * only, scheduler.h:54-56).  While enabled, block (0,0) of every tensor-core launch records the SM clock at
+ * {0 entry, 1 set-up done, 2 ring filled, 3 peers up, 4 first K block landed, 5 last K block landed,
+ * 6 accumulator complete, 7 tile staged, 8 exchange complete, 9 rows finished, 10 TMEM freed};
+ * reef_trace_read copies the 16-word record of the latest launch (call after synchronising). */
+REEF_API reef_status reef_trace_enable(int on);
+REEF_API reef_status reef_trace_read(int64_t* stamps16);
 
 /* Profiling aid (no reference counterpart): occupies `s` with a one-thread kernel for `ns` nanoseconds
  * (clamped to 20 ms, bounded loop) so that launches queued behind it run back to back. */

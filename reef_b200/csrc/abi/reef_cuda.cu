@@ -281,6 +281,10 @@ reef_status reef_kernel_plan(const char* name, uint32_t dims[6], uint32_t* dyn_s
     if (num_args) *num_args = s.nargs;
     return REEF_SUCC;
 }
+reef_status reef_kernel_prepare(reef_kernel_t k, void** args) {
+    if (!k || !args) return REEF_FAIL;
+    return prepare_kernel(k->spec, args);
+}
 reef_status reef_kernel_attrs(reef_kernel_t k, reef_kernel_attrs_t* out) {
     if (!k || !out) return REEF_FAIL;
     return kernel_attrs(k->spec, out);
@@ -329,6 +333,9 @@ reef_status reef_device_error(int* value) {
     if (*value != 0) CK(cudaMemset(w, 0, 4));
     return REEF_SUCC;
 }
+
+reef_status reef_trace_enable(int on) { return tc_trace_enable(on); }
+reef_status reef_trace_read(int64_t* stamps16) { return tc_trace_read((long long*)stamps16); }
 
 reef_status reef_stream_delay(reef_stream_t s, uint64_t ns) { return launch_delay((cudaStream_t)s, ns); }
 

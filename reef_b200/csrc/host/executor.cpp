@@ -86,6 +86,15 @@ Status ExecutorBase::init_executor_base(const char* json_file_path, GPUModule_t 
         for (size_t idx : ki.args) ka.push_back(&storage[idx]);
         raw_args.push_back(ka);
     }
+    // bind kernels to their buffers now (tensor maps, one-time device set-up), so that the first pass may
+    // already be recorded into a CUDA graph
+    for (size_t i = 0; i < kernels.size(); i++) {
+        int rc = reef_kernel_prepare(kernels[i], raw_args[i].data());
+        if (rc != REEF_SUCC) {
+            err_ = reef_last_error();
+            RETURN_STATUS(rc);
+        }
+    }
     if (s == nullptr) GPU_RETURN_STATUS(reef_stream_create(&s, 0));
     return Status::Succ;
 }

@@ -453,7 +453,10 @@ void REEFScheduler::execute_rt_task(std::shared_ptr<Task>& task) {
         dynamic_kernel_padding(task);
         reef_stream_sync(rt_queue->stream);
     } else if (rt_graph) {
-        exe.execute_graph(rt_queue->stream);
+        if (exe.execute_graph(rt_queue->stream) != Status::Succ) {
+            err_ = "real-time graph launch failed: " + exe.error();
+            fprintf(stderr, "[reef] %s\n", err_.c_str());
+        }
         reef_stream_sync(rt_queue->stream);
     } else {
         exe.execute(rt_queue->stream);

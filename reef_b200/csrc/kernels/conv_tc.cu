@@ -12,24 +12,23 @@ namespace reef {
 static int ceil_div_i(int a, int b) { return (a + b - 1) / b; }
 
 // ---- planning (needs no GPU) --------------------------------------------------------------------
-int tc_plan(const ConvP& p, TcPlan* pl) {
+// One candidate plan: pixel tiles of at most `cap` pixels.
+static int tc_plan_cap(const ConvP& p, int cap, TcPlan* pl) {
     memset(pl, 0, sizeof(*pl));
-    if (p.nchw || (p.ci % TC_BK) != 0 || p.sh != p.sw || (p.sh != 1 && p.sh != 2)) return REEF_NOT_FOUND;
-    if ((p.ics & 3) || (p.ioff & 3) || (p.ocs & 3) || (p.ooff & 3)) return REEF_NOT_FOUND;
-    if (p.kh * p.kw > 64 || p.ph >= p.kh || p.pw >= p.kw) return REEF_NOT_FOUND;
     pl->spatial = (p.kh * p.kw > 1 || p.sh > 1 || p.ph || p.pw) ? 1 : 0;
     if (pl->spatial) {
-        if (p.wo > 224) return REEF_NOT_FOUND;
+        if (p.wo > cap) return REEF_NOT_FOUND;
         int best = 1;
-        const int rmax = 224 / p.wo;
-        for (int r = 1; r <= rmax && r <= p.ho; r++)
+        const int rmax = cap / p.wo;
+        const int lim = rmax < p.ho ? rmax : p.ho;
+        for (int r = 1; r <= lim; r++)
             if (p.ho % r == 0) best = r;               // largest divisor of Ho that fits the tile
-        if (best * 2 <= (rmax < p.ho ? rmax : p.ho)) best = rmax < p.ho ? rmax : p.ho;   // no useful divisor: ragged last tile
+        if (best * 2 <= lim) best = lim;               // no useful divisor: ragged last tile
         pl->rows = best;
         pl->n_valid = best * p.wo;
         pl->n_tiles = ceil_div_i(p.ho, best);
     } else {
-        int t = ceil_div_i(p.ptot, 224);
+        int t = ceil_div_i(p.ptot, cap);
         pl->n_valid = ceil_div_i(p.ptot, t);
         pl->rows = 0;
         pl->n_tiles = ceil_div_i(p.ptot, pl->n_valid);
@@ -52,7 +51,50 @@ int tc_plan(const ConvP& p, TcPlan* pl) {
         if (pl->splits == s || s == 1) break;
     }
     pl->b_bytes = pl->n_valid * 128;
-    pl->smem = 1024 + TC_STAGES * (TC_A_BYTES + pl->n_mma * 128) + 128;
+    // shared memory: the stage ring is reused by the epilogue for the staged accumulator tile (pixel rows
+    // rounded up to 32, 512 bytes each) and, with a K split, the exchange area recv[rank][cpc_max][128]
+    // ring depth: the whole K range of a CTA in flight when it fits (a batch-1 layer is bound by load latency)
+    const int stage_bytes = TC_A_BYTES + pl->n_mma * 128;
+    pl->stages = pl->kb_per_split < TC_MAX_STAGES ? pl->kb_per_split : TC_MAX_STAGES;
+    while (pl->stages > 2 && pl->stages * stage_bytes > 200 * 1024) pl->stages--;
+    const int ring = pl->stages * stage_bytes;
+    const int n32 = ((pl->n_valid + 31) / 32) * 32;
+    pl->cpc_max = ceil_div_i(pl->n_valid, pl->splits);
+    pl->recv_offset_floats = n32 * TC_BM;
+    const int epi = n32 * 512 + (pl->splits > 1 ? pl->splits * pl->cpc_max * 512 : 0);
+    pl->region_bytes = ring > epi ? ring : epi;
+    pl->region_bytes = ((pl->region_bytes + 127) / 128) * 128;
+    pl->smem = 1024 + pl->region_bytes + 256;   // alignment slack + data region + control words
+    if (pl->smem > 225 * 1024) return REEF_NOT_FOUND;
+    return REEF_SUCC;
+}
+
+// ---- planning (needs no GPU) --------------------------------------------------------------------
+// Tile caps are tried from large to small; the first plan that fits shared memory and puts at least 48
+// CTAs in flight wins, else the feasible plan with the most CTAs (a batch-1 layer is latency-bound: more
+// CTAs shorten every CTA's load stream, at the price of re-reading weights from L2).
+int tc_plan(const ConvP& p, TcPlan* pl) {
+    if (p.nchw || (p.ci % TC_BK) != 0 || p.sh != p.sw || (p.sh != 1 && p.sh != 2)) return REEF_NOT_FOUND;
+    if ((p.ics & 3) || (p.ioff & 3) || (p.ocs & 3) || (p.ooff & 3) || (p.co & 3)) return REEF_NOT_FOUND;
+    if (p.kh * p.kw > 64) return REEF_NOT_FOUND;
+    static const int caps[] = {224, 160, 112, 64, 32};
+    TcPlan best;
+    int best_ctas = 0;
+    for (int cap : caps) {
+        TcPlan c;
+        if (tc_plan_cap(p, cap, &c) != REEF_SUCC) continue;
+        const int ctas = c.splits * c.n_tiles * c.m_tiles;
+        if (ctas > best_ctas && ctas <= 148) {
+            best = c;
+            best_ctas = ctas;
+        } else if (best_ctas == 0) {
+            best = c;
+            best_ctas = ctas;
+        }
+        if (best_ctas >= 48) break;
+    }
+    if (best_ctas == 0) return REEF_NOT_FOUND;
+    *pl = best;
     return REEF_SUCC;
 }
 
@@ -156,6 +198,20 @@ int tc_build_params(const ConvP& p, const TcPlan& pl, void* const* a, TcParams* 
     if (p.ep & EP_RELU) P->ep |= TC_EP_RELU;
     if (p.round_tf32) P->ep |= TC_EP_ROUND;
     P->b_bytes = pl.b_bytes;
+    P->cb_magic = (unsigned)((0x100000000ull + (unsigned long long)pl.cblocks - 1) / (unsigned long long)pl.cblocks);
+    for (int ky = 0; ky < p.kh; ky++)
+        for (int kx = 0; kx < p.kw; kx++) {
+            const int s = p.sh, dy = ky - p.ph, dx = kx - p.pw;
+            const int ry = ((dy % s) + s) % s, rx = ((dx % s) + s) % s;
+            const int tap = ky * p.kw + kx;
+            P->tap_map[tap] = (signed char)(ry * s + rx);
+            P->tap_qx[tap] = (signed char)((dx - rx) / s);
+            P->tap_qy[tap] = (signed char)((dy - ry) / s);
+        }
+    P->stages = pl.stages;
+    P->region_bytes = pl.region_bytes;
+    P->recv_offset_floats = pl.recv_offset_floats;
+    P->cpc_max = pl.cpc_max;
     P->n_tiles = pl.n_tiles;
     P->tile_begin = 0;
     P->pdl = 1;
@@ -163,21 +219,57 @@ int tc_build_params(const ConvP& p, const TcPlan& pl, void* const* a, TcParams* 
 }
 
 static bool g_attr_set[16] = {false};
+static long long* g_trace[16] = {nullptr};
+
+// Phase trace of the tensor-core convolution: when enabled, block (0,0) of every launch stamps the SM clock
+// at 11 points (entry, set-up done, ring filled, peers up, first K block landed, last K block landed,
+// accumulator complete, tile staged, exchange complete, rows finished, TMEM freed) into one 16-word device
+// record that the host reads back.
+int tc_trace_enable(int on) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 16) return REEF_FAIL;
+    if (on && !g_trace[dev]) {
+        if (cudaMalloc(&g_trace[dev], 128) != cudaSuccess || cudaMemset(g_trace[dev], 0, 128) != cudaSuccess) {
+            set_error("cannot allocate the trace record");
+            return REEF_FAIL;
+        }
+    } else if (!on && g_trace[dev]) {
+        cudaFree(g_trace[dev]);
+        g_trace[dev] = nullptr;
+    }
+    return REEF_SUCC;
+}
+int tc_trace_read(long long* out16) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 16 || !g_trace[dev]) return REEF_NOT_FOUND;
+    if (cudaMemcpy(out16, g_trace[dev], 128, cudaMemcpyDeviceToHost) != cudaSuccess) return REEF_FAIL;
+    return REEF_SUCC;
+}
 static int g_use_pdl = -1;
 
-int tc_launch(const TcParams& P0, const TcPlan& pl, cudaStream_t st, const int* flag, int* slot, int tile_begin,
-              int tile_count) {
+// one-time, per device: shared-memory opt-in of the kernel and the error word (never during a capture)
+int tc_prepare_device() {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 16 && !g_attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute((const void*)reef_conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             200 * 1024);
+                                             226 * 1024);
         if (e != cudaSuccess) {
             set_error(std::string("cudaFuncSetAttribute(conv_tc): ") + cudaGetErrorString(e));
             return REEF_FAIL;
         }
+        int* w = nullptr;
+        int rc = tc_error_word(&w);
+        if (rc != REEF_SUCC) return rc;
         g_attr_set[dev] = true;
     }
+    return REEF_SUCC;
+}
+
+int tc_launch(const TcParams& P0, const TcPlan& pl, cudaStream_t st, const int* flag, int* slot, int tile_begin,
+              int tile_count) {
     if (g_use_pdl < 0) {
         const char* v = getenv("REEF_PDL");
         g_use_pdl = (v && v[0] == '0') ? 0 : 1;
@@ -192,6 +284,11 @@ int tc_launch(const TcParams& P0, const TcPlan& pl, cudaStream_t st, const int* 
         return REEF_OUT_OF_RANGE;
     }
     P.tile_begin = tile_begin;
+    {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        P.trace = (dev >= 0 && dev < 16) ? g_trace[dev] : nullptr;
+    }
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(pl.splits, tile_count, 1);

@@ -15,7 +15,7 @@
 // distributed shared memory in rank order 0..S-1 — a fixed order, so results are bit-reproducible (no
 // float atomics, no global scratch, no counters to reset when a best-effort run is preempted and re-run).
 //
-// One thread issues TMA, one thread issues tcgen05.mma, all four warps run the epilogue
+// One thread issues TMA, one thread issues tcgen05.mma, all eight warps run the epilogue
 // (tcgen05.ld -> +residual -> +bias | *gamma+beta -> ReLU -> coalesced 128-byte stores, one output
 // channel per lane).  Every mbarrier wait is bounded: on expiry the kernel records an error word,
 // skips further waits, still joins every cluster barrier, frees its TMEM and returns.
@@ -73,6 +73,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm,
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// split form: arrive early, wait where the guarantee is needed, so the barrier latency hides behind other work
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+// control-only arrive: what the barrier orders was already observed complete through an mbarrier
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -83,9 +88,16 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
     return r;
 }
+// volatile keeps the load behind the cluster barrier (also a volatile asm); no "memory" clobber, so the
+// loads of one reduction batch are issued back to back and overlap
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
     float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float4 ld_dsmem_v4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ void st_dsmem_u32(uint32_t addr, uint32_t v) {
@@ -126,14 +138,26 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// 32 columns of one TMEM lane per thread; the wait is separate so that several loads can be in flight
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 enum : int { TC_EP_RES = 1, TC_EP_BIAS = 2, TC_EP_GB = 4, TC_EP_RELU = 8, TC_EP_ROUND = 16 };
 
-__device__ __forceinline__ float tc_epilogue(float v, float r, float sc, float sh, int ep) {
-    if (ep & TC_EP_RES) v += r;
-    if (ep & TC_EP_GB) v = fmaf(v, sc, sh);
-    else v += sh;
-    if (ep & TC_EP_RELU) v = fmaxf(v, 0.f);
-    if (ep & TC_EP_ROUND) {
+// Branch-free form of (+residual) (+bias | *gamma+beta) (ReLU): r = 0, sc = 1, sh = 0, lo = -inf stand in for
+// the absent terms (v + 0 and fma(v, 1, b) are exact, so this equals the conditional form bit for bit).
+__device__ __forceinline__ float tc_epilogue(float v, float r, float sc, float sh, float lo, bool rnd) {
+    v = fmaxf(fmaf(v + r, sc, sh), lo);
+    if (rnd) {
         // The tensor core reads only the upper 19 bits of an fp32 operand (truncation, a bias toward zero).
         // Rounding the stored activation to the nearest TF32 value makes the consumer's truncation exact.
         uint32_t u;
@@ -143,6 +167,10 @@ __device__ __forceinline__ float tc_epilogue(float v, float r, float sc, float s
     return v;
 }
 
+__device__ __forceinline__ void tc_stamp(const TcParams& P, int slot) {
+    if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) P.trace[slot] = clock64();
+}
+
 __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __grid_constant__ TcParams P) {
     extern __shared__ __align__(16) unsigned char tc_smem_raw[];
     // stage buffers need 1024-byte alignment (swizzle atom); carve barriers behind them
@@ -150,12 +178,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* smem = tc_smem_raw + (base - raw);
     const uint32_t stage_bytes = TC_A_BYTES + (uint32_t)P.n_mma * 128u;
-    const uint32_t ctrl = base + TC_STAGES * stage_bytes;
-    const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * TC_STAGES, bar_acc = ctrl + 16 * TC_STAGES;
-    volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + TC_STAGES * stage_bytes + 16 * TC_STAGES + 8);
+    // the control words sit behind the data region (stage ring, reused by the epilogue's staging + exchange area)
+    const uint32_t ctrl = base + (uint32_t)P.region_bytes;
+    const int NS = P.stages;   // ring depth of this launch (<= TC_MAX_STAGES)
+    const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * TC_MAX_STAGES, bar_acc = ctrl + 16 * TC_MAX_STAGES;
+    const uint32_t bar_red = bar_acc + 8;
+    volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + P.region_bytes + 16 * TC_MAX_STAGES + 16);
     volatile uint32_t* s_flags = s_tmem + 1;    // [0] abort (preempt flag seen), [1] wait expired
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) tc_stamp(P, 0);
     // grid = (K splits = cluster, tiles of this launch); a launch may cover a sub-range of the tiles
     const int split = blockIdx.x;
     const int tile = P.tile_begin + (int)blockIdx.y;
@@ -167,11 +199,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may begin its prologue
     if (tid == 0) {
-        for (int s = 0; s < TC_STAGES; s++) {
+        for (int s = 0; s < NS; s++) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
         mbar_init(bar_acc, 1);
+        mbar_init(bar_red, 1);
         s_flags[0] = 0;
         s_flags[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -189,15 +222,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *s_tmem;
+    if (tid == 0) tc_stamp(P, 1);   // set-up done (barriers, TMEM)
+
+    // K-split exchange barrier: armed now, so that peers may send as soon as their own tile is staged.  The
+    // cluster barrier below (cheap here: all CTAs of a cluster start together, and it overlaps the first loads'
+    // latency) guarantees every peer's barrier is initialised and armed before any remote completion.
+    const int pix0 = P.spatial ? (tile % P.n_tiles) * P.rows * P.wo : (tile % P.n_tiles) * P.n_valid;
+    const int n_lim = min(P.n_valid, P.ptot - pix0);   // columns of this tile that are real pixels
+    const int cpc = (n_lim + S - 1) / S;               // pixel rows one rank finishes
+    const int jb = min(split * cpc, n_lim), je = min(jb + cpc, n_lim);
+    if (S > 1 && P.preempt_flag == nullptr && tid == 0) mbar_expect_tx(bar_red, (uint32_t)((S - 1) * (je - jb) * TC_BM * 4));
 
     // best-effort flavour: one flag read per cluster (rank 0), published to every CTA, so that all CTAs of
     // a cluster take the same decision and none is left alone at a cluster barrier
     bool abort = false;
     if (P.preempt_flag != nullptr) {
-        if (tid == 0) s_flags[0] = (uint32_t)(*reinterpret_cast<const volatile int*>(P.preempt_flag) != 0);
+        if (tid == 0) {
+            s_flags[0] = (uint32_t)(*reinterpret_cast<const volatile int*>(P.preempt_flag) != 0);
+            if (S > 1) mbar_expect_tx(bar_red, (uint32_t)((S - 1) * (je - jb) * TC_BM * 4));
+        }
         __syncthreads();
         if (S > 1) {
-            cluster_sync_all();   // rank 0's observation is written and every CTA of the cluster is running
+            cluster_sync_all();   // rank 0's observation is written, every peer is running and has armed its barrier
             uint32_t f;
             asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(f) : "r"(mapa_shared(smem_u32((const void*)&s_flags[0]), 0)) : "memory");
             abort = f != 0;
@@ -209,44 +255,46 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
 
     if (!abort) {
         const int m0 = tile_m * TC_BM;
-        if (warp == 0 && lane == 0) {
-            // ---------------- TMA producer ----------------
-            bool ok = true;
-            const uint32_t tx = TC_A_BYTES + (uint32_t)P.b_bytes;
-            int issued_a = 0;
-            if (P.pdl) {
-                // weights do not depend on the previous kernel: start fetching them before the dependency wait
-                for (; issued_a < nkb && issued_a < TC_STAGES; issued_a++) {
-                    const uint32_t st = base + issued_a * stage_bytes;
-                    mbar_expect_tx(bar_full + 8 * issued_a, tx);
-                    tma_load_2d(st, &P.tm_w, bar_full + 8 * issued_a, (kb_begin + issued_a) * TC_BK, m0);
-                }
-                asm volatile("griddepcontrol.wait;" ::: "memory");
+        // ---------------- TMA producer, part 1: fill the ring (no waits) ----------------
+        const uint32_t tx = TC_A_BYTES + (uint32_t)P.b_bytes;
+        const int first = nkb < NS ? nkb : NS;
+        auto load_b = [&](int i) {
+            const int s = i % NS;
+            const uint32_t st = base + s * stage_bytes;
+            const int kb = kb_begin + i;
+            // tap and channel block of this K block; the per-tap sub-lattice and offsets come from a host table
+            const int tap = (int)__umulhi((unsigned)kb, P.cb_magic), cb = kb - tap * P.cblocks;
+            if (P.spatial) {
+                tma_load_3d(st + TC_A_BYTES, &P.tm_x[P.tap_map[tap]], bar_full + 8 * s, cb * TC_BK, P.tap_qx[tap],
+                            tile_n * P.rows + P.tap_qy[tap]);
+            } else {
+                tma_load_2d(st + TC_A_BYTES, &P.tm_x[0], bar_full + 8 * s, cb * TC_BK, tile_n * P.n_valid);
             }
-            for (int i = 0; i < nkb && ok; i++) {
-                const int s = i % TC_STAGES;
-                const uint32_t st = base + s * stage_bytes;
-                const int kb = kb_begin + i;
-                if (i >= TC_STAGES) {
-                    ok = mbar_wait(bar_empty + 8 * s, ((i / TC_STAGES) - 1) & 1);
-                    if (!ok) break;
-                }
-                if (i >= issued_a) {
-                    mbar_expect_tx(bar_full + 8 * s, tx);
-                    tma_load_2d(st, &P.tm_w, bar_full + 8 * s, kb * TC_BK, m0);
-                }
-                const int tap = kb / P.cblocks, cb = kb - tap * P.cblocks;
-                if (P.spatial) {
-                    const int ky = tap / P.kw, kx = tap - ky * P.kw;
-                    const int dy = ky - P.ph, dx = kx - P.pw;
-                    const int sdiv = P.stride;
-                    const int ry = ((dy % sdiv) + sdiv) % sdiv, rx = ((dx % sdiv) + sdiv) % sdiv;
-                    const int qy = (dy - ry) / sdiv, qx = (dx - rx) / sdiv;
-                    tma_load_3d(st + TC_A_BYTES, &P.tm_x[ry * sdiv + rx], bar_full + 8 * s, cb * TC_BK, qx,
-                                tile_n * P.rows + qy);
-                } else {
-                    tma_load_2d(st + TC_A_BYTES, &P.tm_x[0], bar_full + 8 * s, cb * TC_BK, tile_n * P.n_valid);
-                }
+        };
+        if (warp == 0) {
+            // one lane per stage: issuing a load costs a few hundred cycles of address arithmetic and
+            // descriptor traffic, so the ring is filled by up to eight lanes at once.  Weights do not depend
+            // on the previous kernel: they are requested before the dependency wait, activations after it.
+            if (lane < first) {
+                mbar_expect_tx(bar_full + 8 * lane, tx);
+                tma_load_2d(base + lane * stage_bytes, &P.tm_w, bar_full + 8 * lane, (kb_begin + lane) * TC_BK, m0);
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (lane < first) load_b(lane);
+            if (lane == 0) tc_stamp(P, 2);   // ring filled (loads issued)
+        }
+        __syncwarp();
+
+        if (warp == 0 && lane == 0) {
+            // ---------------- TMA producer, part 2: refill stages as the MMAs release them ----------------
+            bool ok = true;
+            for (int i = first; i < nkb && ok; i++) {
+                const int s = i % NS;
+                ok = mbar_wait(bar_empty + 8 * s, ((i / NS) - 1) & 1);
+                if (!ok) break;
+                mbar_expect_tx(bar_full + 8 * s, tx);
+                tma_load_2d(base + s * stage_bytes, &P.tm_w, bar_full + 8 * s, (kb_begin + i) * TC_BK, m0);
+                load_b(i);
             }
             if (!ok) s_flags[1] = 1;
         } else if (warp == 1 && lane == 0) {
@@ -254,10 +302,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
             bool ok = true;
             const uint32_t idesc = umma_idesc_tf32(P.n_mma);
             for (int i = 0; i < nkb && ok; i++) {
-                const int s = i % TC_STAGES;
+                const int s = i % NS;
                 const uint32_t st = base + s * stage_bytes;
-                ok = mbar_wait(bar_full + 8 * s, (i / TC_STAGES) & 1);
+                ok = mbar_wait(bar_full + 8 * s, (i / NS) & 1);
                 if (!ok) break;
+                if (i == 0) tc_stamp(P, 4);          // first K block landed
+                if (i == nkb - 1) tc_stamp(P, 5);    // last K block landed
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t da = umma_desc_sw128(st), db = umma_desc_sw128(st + TC_A_BYTES);
 #pragma unroll
@@ -269,69 +319,161 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
             else s_flags[1] = 1;
         }
         __syncwarp();   // lanes 1..31 of the two role warps park here instead of spinning beside their lane 0
-        if (P.pdl && tid != 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (warp != 0) asm volatile("griddepcontrol.wait;" ::: "memory");
 
-        // ---------------- epilogue: all four warps ----------------
+        // ---------------- epilogue: all eight warps ----------------
         bool ok = mbar_wait(bar_acc, 0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         __syncthreads();
+        if (tid == 0) tc_stamp(P, 6);   // accumulator complete
+        // cluster barrier #1 (arrive here, wait after staging): every rank has finished its main loop, so its
+        // stage ring is free to receive exchange data
+        if (S > 1) cluster_arrive_relaxed();
         if (!ok || s_flags[1]) {
             ok = false;
             if (tid == 0 && P.error_word) atomicExch(P.error_word, 1);
         }
-        const int co = m0 + tid;                       // TMEM lane == output channel of the tile
-        const bool cvalid = co < P.co;
-        const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
-        const int pix0 = P.spatial ? tile_n * P.rows * P.wo : tile_n * P.n_valid;
-        float sc = 1.f, sh = 0.f;
-        if (cvalid) {
-            if (P.ep & TC_EP_GB) { sc = P.gamma[co]; sh = P.beta[co]; }
-            else if (P.ep & TC_EP_BIAS) sh = P.bias[co];
-        }
-        if (S == 1) {
-            if (ok) {
-                for (int j0 = 0; j0 < P.n_valid; j0 += 16) {
-                    uint32_t r[16];
-                    tmem_ld16(taddr + j0, r);
+        // Phase A — eight warps move the accumulator tile TMEM -> registers -> shared memory as
+        // stage[pixel][channel] (warp w reads TMEM lanes 32*(w%4).., its hardware quadrant, and the column
+        // chunks of parity w/4).  The stage ring is free by now and is reused for this.
+        // Phase B — the tile is finished pixel row by pixel row with 128-bit accesses: one warp per pixel,
+        // a lane owns 4 consecutive output channels; it sums the K-split partials of all cluster ranks in
+        // rank order 0..S-1 through distributed shared memory (S = 1: its own tile), adds the residual,
+        // applies bias | gamma,beta and ReLU, and stores one coalesced 512-byte row per warp.
+        const int quad = warp & 3, half = warp >> 2;
+        const int row = quad * 32 + lane;              // TMEM lane == output channel within the tile
+        const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
+        float* stage = reinterpret_cast<float*>(smem);
+        if (ok) {
+            for (int j0 = half * 32; j0 < n_lim; j0 += 64) {
+                uint32_t r[32];
+                tmem_ld32_nowait(taddr + j0, r);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const int pix = pix0 + j0 + j;
-                        if (cvalid && j0 + j < P.n_valid && pix < P.ptot) {
-                            const float rv = (P.ep & TC_EP_RES) ? P.res[(size_t)pix * P.co + co] : 0.f;
-                            P.out[(size_t)pix * P.ocs + P.ooff + co] = tc_epilogue(__uint_as_float(r[j]), rv, sc, sh, P.ep);
+                for (int j = 0; j < 32; j++) stage[(j0 + j) * TC_BM + row] = __uint_as_float(r[j]);
+            }
+        }
+        if (tid == 0) tc_stamp(P, 7);   // accumulator tile staged in shared memory
+        // K-split exchange: rank q finishes pixel rows [q*cpc, (q+1)*cpc).  Every rank sends the rows owned
+        // by each peer with ONE bulk shared-memory-to-shared-memory copy per peer (the copy engine moves the
+        // bytes and completes the owner's mbarrier); remote loads from distributed shared memory proved an
+        // order of magnitude slower here.  Owners then read only their own shared memory.
+        float* recv = stage + P.recv_offset_floats;    // recv[rank][cpc_max][128]
+        if (S > 1) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staged tile -> visible to the copy engine
+            __syncthreads();      // the whole tile is staged
+            cluster_wait();       // barrier #1: all peers are past their main loops (and their barriers are armed)
+            if (tid == 0) tc_stamp(P, 3);
+            if (tid == 0) {
+                for (int q = 0; q < S; q++) {
+                    if (q == split) continue;
+                    const int qb = min(q * cpc, n_lim), qe = min(qb + cpc, n_lim);
+                    const uint32_t bytes = (uint32_t)((qe - qb) * TC_BM * 4);
+                    if (bytes == 0) continue;
+                    const uint32_t dst = mapa_shared(smem_u32(recv + (size_t)split * P.cpc_max * TC_BM), (uint32_t)q);
+                    const uint32_t rbar = mapa_shared(bar_red, (uint32_t)q);
+                    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(dst), "r"(smem_u32(stage + (size_t)qb * TC_BM)), "r"(bytes), "r"(rbar)
+                                 : "memory");
+                }
+            }
+            if (!mbar_wait(bar_red, 0)) {
+                ok = false;
+                if (tid == 0 && P.error_word) atomicExch(P.error_word, 1);
+            }
+            // cluster barrier #2 (arrive here, wait before leaving): once all ranks have received what they are
+            // owed, nobody reads a peer's shared memory any more and every CTA may exit
+            cluster_arrive();
+        } else {
+            __syncthreads();
+        }
+
+        if (tid == 0) tc_stamp(P, 8);   // exchange complete
+        const int cbase = lane * 4;                    // 4 channels of this lane
+        const int co = m0 + cbase;
+        const bool cvalid = co < P.co;
+        float4 sc = make_float4(1.f, 1.f, 1.f, 1.f), sh = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (cvalid) {
+            if (P.ep & TC_EP_GB) {
+                sc = *reinterpret_cast<const float4*>(P.gamma + co);
+                sh = *reinterpret_cast<const float4*>(P.beta + co);
+            } else if (P.ep & TC_EP_BIAS) {
+                sh = *reinterpret_cast<const float4*>(P.bias + co);
+            }
+        }
+        const float lo = (P.ep & TC_EP_RELU) ? 0.f : -__int_as_float(0x7f800000);
+        const bool has_res = (P.ep & TC_EP_RES) != 0;
+        const bool rnd = (P.ep & TC_EP_ROUND) != 0;
+        // Four pixel rows per warp are in flight at a time (all partial and residual loads issued before the
+        // first use): with one or two warps per scheduler the loop is latency-bound, not bandwidth-bound.
+        if (ok && cvalid) {
+            constexpr int RB = 4;
+            if (S == 1) {
+                for (int jbase = jb + warp; jbase < je; jbase += 8 * RB) {
+                    float4 v[RB], rv[RB];
+#pragma unroll
+                    for (int u = 0; u < RB; u++) {
+                        const int j = jbase + 8 * u;
+                        rv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (j < je) {
+                            v[u] = *reinterpret_cast<const float4*>(stage + j * TC_BM + cbase);
+                            if (has_res) rv[u] = __ldg(reinterpret_cast<const float4*>(P.res + (size_t)(pix0 + j) * P.co + co));
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < RB; u++) {
+                        const int j = jbase + 8 * u;
+                        if (j < je) {
+                            float4 o;
+                            o.x = tc_epilogue(v[u].x, rv[u].x, sc.x, sh.x, lo, rnd);
+                            o.y = tc_epilogue(v[u].y, rv[u].y, sc.y, sh.y, lo, rnd);
+                            o.z = tc_epilogue(v[u].z, rv[u].z, sc.z, sh.z, lo, rnd);
+                            o.w = tc_epilogue(v[u].w, rv[u].w, sc.w, sh.w, lo, rnd);
+                            *reinterpret_cast<float4*>(P.out + (size_t)(pix0 + j) * P.ocs + P.ooff + co) = o;
+                        }
+                    }
+                }
+            } else {
+                // partial of rank q for row j: own rows come from the staged tile, the others from recv[q]
+                const float* src[TC_MAX_SPLITS];
+#pragma unroll
+                for (int q = 0; q < TC_MAX_SPLITS; q++)
+                    src[q] = (q == split) ? stage + (size_t)jb * TC_BM + cbase
+                                          : recv + (size_t)(q < S ? q : 0) * P.cpc_max * TC_BM + cbase;
+                for (int jbase = warp; jbase < je - jb; jbase += 8 * RB) {
+                    float4 part[RB][TC_MAX_SPLITS], rv[RB];
+#pragma unroll
+                    for (int u = 0; u < RB; u++) {
+                        const int jr = jbase + 8 * u;   // row within this rank's slice
+                        rv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (jr < je - jb) {
+#pragma unroll
+                            for (int q = 0; q < TC_MAX_SPLITS; q++)
+                                if (q < S) part[u][q] = *reinterpret_cast<const float4*>(src[q] + (size_t)jr * TC_BM);
+                            if (has_res) rv[u] = __ldg(reinterpret_cast<const float4*>(P.res + (size_t)(pix0 + jb + jr) * P.co + co));
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < RB; u++) {
+                        const int jr = jbase + 8 * u;
+                        if (jr < je - jb) {
+                            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                            for (int q = 0; q < TC_MAX_SPLITS; q++)   // fixed rank order: deterministic sum
+                                if (q < S) { v.x += part[u][q].x; v.y += part[u][q].y; v.z += part[u][q].z; v.w += part[u][q].w; }
+                            float4 o;
+                            o.x = tc_epilogue(v.x, rv[u].x, sc.x, sh.x, lo, rnd);
+                            o.y = tc_epilogue(v.y, rv[u].y, sc.y, sh.y, lo, rnd);
+                            o.z = tc_epilogue(v.z, rv[u].z, sc.z, sh.z, lo, rnd);
+                            o.w = tc_epilogue(v.w, rv[u].w, sc.w, sh.w, lo, rnd);
+                            *reinterpret_cast<float4*>(P.out + (size_t)(pix0 + jb + jr) * P.ocs + P.ooff + co) = o;
                         }
                     }
                 }
             }
-        } else {
-            // park the partial tile in shared memory as red[column][lane]; the stage ring is free now
-            float* red = reinterpret_cast<float*>(smem);
-            if (ok) {
-                for (int j0 = 0; j0 < P.n_mma; j0 += 16) {
-                    uint32_t r[16];
-                    tmem_ld16(taddr + j0, r);
-#pragma unroll
-                    for (int j = 0; j < 16; j++) red[(j0 + j) * TC_BM + tid] = __uint_as_float(r[j]);
-                }
-            }
-            cluster_sync_all();
-            const int cpc = (P.n_valid + S - 1) / S;   // columns this CTA finishes
-            const int jb = split * cpc, je = min(jb + cpc, P.n_valid);
-            const uint32_t red_u32 = smem_u32(red);
-            if (ok) {
-                for (int j = jb; j < je; j++) {
-                    float v = 0.f;
-                    for (int q = 0; q < S; q++)   // fixed rank order: deterministic sum
-                        v += ld_dsmem_f32(mapa_shared(red_u32 + (uint32_t)(j * TC_BM + tid) * 4u, (uint32_t)q));
-                    const int pix = pix0 + j;
-                    if (cvalid && pix < P.ptot) {
-                        const float rv = (P.ep & TC_EP_RES) ? P.res[(size_t)pix * P.co + co] : 0.f;
-                        P.out[(size_t)pix * P.ocs + P.ooff + co] = tc_epilogue(v, rv, sc, sh, P.ep);
-                    }
-                }
-            }
-            cluster_sync_all();   // nobody leaves while a peer still reads its shared memory
         }
+        if (S > 1) cluster_wait();      // barrier #2
+        if (tid == 0) tc_stamp(P, 9);   // rows finished
         if (P.task_slot != nullptr && ok) {
             __syncthreads();
             if (tid == 0) {
@@ -346,6 +488,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)P.tmem_cols) : "memory");
     }
+    if (tid == 32) tc_stamp(P, 10);   // TMEM freed
 }
 
 }  // namespace reef

@@ -6,6 +6,7 @@
 #include "registry.h"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <string>
@@ -305,8 +306,16 @@ __device__ __forceinline__ bool run_any(const KTask& t, int vb, unsigned char* s
 
 extern __shared__ __align__(16) unsigned char reef_dyn_smem[];
 
+// Programmatic dependent launch: the next kernel may start its prologue at once (launch_dependents) and this
+// one waits for its predecessor's results before touching memory (wait is a no-op for an ordinary launch).
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 template <int F>
 __global__ void __launch_bounds__(kThreads) k_plain(const __grid_constant__ KTask t) {
+    pdl_prologue();
     run_body<F>(t, blockIdx.x, reef_dyn_smem, nullptr);
 }
 
@@ -316,6 +325,7 @@ __global__ void __launch_bounds__(kThreads) k_plain(const __grid_constant__ KTas
 template <int F>
 __global__ void __launch_bounds__(kThreads) k_be(const __grid_constant__ KTask t, const int* __restrict__ flag,
                                                  int* __restrict__ task_slot) {
+    pdl_prologue();
     if (ld_flag(flag)) return;
     const bool done = run_body<F>(t, blockIdx.x, reef_dyn_smem, flag);
     __syncthreads();
@@ -429,6 +439,28 @@ static const void* be_fn(int family) {
     }
 }
 
+// Launch with the programmatic-stream-serialization attribute (REEF_PDL=0 turns it off): the kernel may be
+// scheduled while its predecessor in the stream still runs; all kernels here wait in their prologue.
+static cudaError_t launch_pdl(const void* fn, dim3 grid, dim3 block, void** kargs, uint32_t smem, cudaStream_t st) {
+    static int use_pdl = -1;
+    if (use_pdl < 0) {
+        const char* v = getenv("REEF_PDL");
+        use_pdl = (v && v[0] == '0') ? 0 : 1;
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    return cudaLaunchKernelExC(&cfg, fn, kargs);
+}
+
 static int check_cuda(cudaError_t e, const char* what) {
     if (e == cudaSuccess) return REEF_SUCC;
     set_error(std::string(what) + ": " + cudaGetErrorString(e));
@@ -445,8 +477,7 @@ static bool dims_match(const KernelSpec& s, const uint32_t dims[6], uint32_t sme
            dims[4] == s.block[1] && dims[5] == s.block[2] && smem == s.dyn_smem;
 }
 
-static int launch_tc(const KernelSpec& s, cudaStream_t st, void** args, const int* flag, int* slot, int tile_begin = 0,
-                     int tile_count = -1) {
+static int bind_tc(const KernelSpec& s, void** args) {
     if (!s.tc_cache) s.tc_cache = std::make_shared<TcCache>();
     TcCache& c = *s.tc_cache;
     bool same = c.valid;
@@ -454,11 +485,26 @@ static int launch_tc(const KernelSpec& s, cudaStream_t st, void** args, const in
     if (!same) {
         void* ptrs[kMaxArgs] = {nullptr};
         for (int i = 0; i < s.nargs; i++) ptrs[i] = *reinterpret_cast<void**>(args[i]);
-        int rc = tc_build_params(s.task.p.conv, s.tc, ptrs, &c.params);
+        int rc = tc_prepare_device();
+        if (rc != REEF_SUCC) return rc;
+        rc = tc_build_params(s.task.p.conv, s.tc, ptrs, &c.params);
         if (rc != REEF_SUCC) return rc;
         for (int i = 0; i < s.nargs; i++) c.ptrs[i] = ptrs[i];
         c.valid = true;
     }
+    return REEF_SUCC;
+}
+
+int prepare_kernel(const KernelSpec& s, void** args) {
+    if (s.task.family == F_CONV_TC) return bind_tc(s, args);
+    return REEF_SUCC;
+}
+
+static int launch_tc(const KernelSpec& s, cudaStream_t st, void** args, const int* flag, int* slot, int tile_begin = 0,
+                     int tile_count = -1) {
+    int rc = bind_tc(s, args);
+    if (rc != REEF_SUCC) return rc;
+    TcCache& c = *s.tc_cache;
     g_launches++;
     return tc_launch(c.params, s.tc, st, flag, slot, tile_begin, tile_count);
 }
@@ -472,8 +518,8 @@ int launch_plain(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cud
     KTask t;
     fill_args(s, args, &t);
     void* kargs[] = {&t};
-    cudaError_t e = cudaLaunchKernel(plain_fn(t.family), dim3(dims[0], dims[1], dims[2]),
-                                     dim3(dims[3], dims[4], dims[5]), kargs, smem, st);
+    cudaError_t e = launch_pdl(plain_fn(t.family), dim3(dims[0], dims[1], dims[2]), dim3(dims[3], dims[4], dims[5]), kargs,
+                               smem, st);
     g_launches++;
     return check_cuda(e, "cudaLaunchKernel");
 }
@@ -488,8 +534,8 @@ int launch_be(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cudaSt
     KTask t;
     fill_args(s, args, &t);
     void* kargs[] = {&t, (void*)&flag, (void*)&slot};
-    cudaError_t e = cudaLaunchKernel(be_fn(t.family), dim3(dims[0], dims[1], dims[2]),
-                                     dim3(dims[3], dims[4], dims[5]), kargs, smem, st);
+    cudaError_t e = launch_pdl(be_fn(t.family), dim3(dims[0], dims[1], dims[2]), dim3(dims[3], dims[4], dims[5]), kargs, smem,
+                               st);
     g_launches++;
     return check_cuda(e, "cudaLaunchKernel(be)");
 }

@@ -18,6 +18,7 @@ struct TcPlan {
     int spatial, rows, n_valid, n_mma, tmem_cols;
     int n_tiles, m_tiles, cblocks, kb_total, kb_per_split, splits;
     int b_bytes, smem;
+    int region_bytes, recv_offset_floats, cpc_max, stages;
 };
 
 struct TcCache;   // tensor maps of one kernel call, rebuilt when its pointers change
@@ -46,6 +47,7 @@ int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, 
                     int be_num, int sm_partition, int occupancy, int num_sms, int* be_slot, int* ctrl, int* be_ctrl,
                     cudaStream_t st, cudaStream_t be_st);
 int kernel_attrs(const KernelSpec& s, reef_kernel_attrs_t* out);
+int prepare_kernel(const KernelSpec& s, void** args);
 int dispatch_occupancy(uint32_t smem, int* occ);
 int launch_delay(cudaStream_t st, unsigned long long ns);
 
@@ -56,6 +58,9 @@ int tc_launch(const TcParams& P, const TcPlan& pl, cudaStream_t st, const int* f
               int tile_count = -1);
 int tc_func_attrs(const TcPlan& pl, cudaFuncAttributes* fa, int* occ);
 int tc_error_word(int** out);
+int tc_prepare_device();
+int tc_trace_enable(int on);
+int tc_trace_read(long long* out16);
 unsigned long long launch_count();
 void add_launches(unsigned long long n);
 
