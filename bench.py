@@ -176,6 +176,9 @@ def main():
 
     if rank == 0:
         d = resources.generate(MODEL)
+        # latency tables for the padding policy, measured on this GPU (the reference ships them per model)
+        from reef_b200 import profiler
+        profiler.profile_model(os.path.join(d, MODEL), iters=10, device=local_rank)
     barrier()
     d = resources.generate(MODEL)
     base = os.path.join(d, MODEL)

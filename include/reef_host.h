@@ -62,6 +62,11 @@ REEF_HOST_API int reef_executor_profile_kernels(reef_executor_t e, int iters, fl
 /* One persistent wave of kernel idx at `occupancy` blocks per SM on every SM (latency[occupancy-1] of profile.json) */
 REEF_HOST_API int reef_executor_profile_wave(reef_executor_t e, int idx, int occupancy, int iters, float* us);
 
+/* Measures the latency tables of the loaded model on the current GPU and writes them as <model>.profile.json
+ * (schema of the reference's ModelProfile::to_json, src/reef/executor/model.cpp:123-145, plus
+ * "latency_unit_ns": 1).  Replaces the `profiler` binary the reference's resource/Makefile:32-36 calls. */
+REEF_HOST_API int reef_executor_write_profile(reef_executor_t e, int iters, const char* out_path);
+
 /* ---- scheduler (REEFScheduler) ------------------------------------------------------------ */
 /* mode: 0 NoPreempt, 1 MultiStream, 2 WaitPreempt, 3 REEF, 4 Reset (reference: scheduler.h:22-28) */
 REEF_HOST_API int reef_sched_create(int mode, int device, reef_scheduler_t* s);

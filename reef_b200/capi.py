@@ -227,6 +227,10 @@ class HybridExecutor:
         return [dict(us=us[i], flops=flops[i], bytes=nbytes[i], tensor_core=tc[i], blocks=blocks[i],
                      max_blocks_per_sm=occ[i]) for i in range(n)]
 
+    def write_profile(self, out_path: str, iters: int = 20):
+        _check(self._lib.reef_executor_write_profile(self._h, C.c_int(iters), out_path.encode()), "write_profile",
+               self._err())
+
     def profile_wave(self, idx: int, occupancy: int, iters: int = 10) -> float:
         us = C.c_float()
         _check(self._lib.reef_executor_profile_wave(self._h, C.c_int(idx), C.c_int(occupancy), C.c_int(iters),

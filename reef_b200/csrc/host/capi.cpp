@@ -164,6 +164,18 @@ int reef_executor_profile_wave(reef_executor_t e, int idx, int occupancy, int it
     return e->exe.profile_wave(idx, occupancy, iters, us);
 }
 
+int reef_executor_write_profile(reef_executor_t e, int iters, const char* out_path) {
+    executor::ModelProfile prof;
+    Status st = e->exe.measure_profile(iters, &prof);
+    if (st != Succ) return st;
+    FILE* f = fopen(out_path, "w");
+    if (!f) return Fail;
+    std::string js = prof.to_json();
+    fwrite(js.data(), 1, js.size(), f);
+    fclose(f);
+    return Succ;
+}
+
 // ---- scheduler -----------------------------------------------------------------------------
 int reef_sched_create(int mode, int device, reef_scheduler_t* s) {
     if (mode < 0 || mode > 4) return OutOfRange;

@@ -335,6 +335,14 @@ Status HybridExecutor::launch_dispatch(int rt_idx, HybridExecutor* be, int be_id
     return Status::Succ;
 }
 
+Status HybridExecutor::launch_pad_piece(int idx, int block_offset, int block_num, int occupancy, GPUStream_t stream) {
+    int rc = reef_dispatch(nullptr, nullptr, kernels[idx], raw_args[idx].data(), block_offset, block_num, 0, occupancy,
+                           task_slot_base + (size_t)idx * 4, dispatch_ctrl, dispatch_ctrl, stream, stream);
+    if (rc != REEF_SUCC) err_ = reef_last_error();
+    GPU_RETURN_STATUS(rc);
+    return Status::Succ;
+}
+
 Status HybridExecutor::execute_graph(GPUStream_t stream) {
     if (graph == nullptr || graph_stream != stream) {
         if (graph) reef_graph_destroy(graph);
@@ -460,6 +468,54 @@ Status HybridExecutor::profile_wave(int idx, int occupancy, int iters, float* us
     *us = ms * 1000.f / (float)std::max(1, iters);
     reset_task_slots(s, 0);
     reef_stream_sync(s);
+    reef_event_destroy(a);
+    reef_event_destroy(b);
+    return st;
+}
+
+Status HybridExecutor::measure_profile(int iters, ModelProfile* out) {
+    if (iters < 1) iters = 1;
+    reef_event_t a, b;
+    GPU_RETURN_STATUS(reef_event_create(&a));
+    GPU_RETURN_STATUS(reef_event_create(&b));
+    out->kernel_latency.clear();
+    out->latency_unit_ns = 1;
+    Status st = Status::Succ;
+    auto elapsed_ns = [&](int n) {
+        float ms = 0;
+        reef_event_sync(b);
+        reef_event_elapsed_ms(a, b, &ms);
+        return (int)(ms * 1e6f / (float)n);
+    };
+    for (size_t i = 0; i < num_kernels() && st == Status::Succ; i++) {
+        const std::string& name = model->kernels[i].name;
+        if (out->kernel_latency.count(name)) continue;
+        KernelProfile kp;
+        for (int r = 0; r < 3 && st == Status::Succ; r++) st = ExecutorBase::launch_kernel((int)i, s);   // warm
+        reef_event_record(a, s);
+        for (int r = 0; r < iters && st == Status::Succ; r++) st = ExecutorBase::launch_kernel((int)i, s);
+        reef_event_record(b, s);
+        kp.total_latency = std::max(1, elapsed_ns(iters));
+        const KernelArg& ka = trans_args[i];
+        const int max_occ = std::max(1, std::min(4, ka.resource.max_blocks_per_sm));
+        for (int occ = 1; occ <= max_occ && st == Status::Succ; occ++) {
+            if (ka.resource.tensor_core) {
+                kp.latency.push_back(kp.total_latency);   // one CTA per SM: a wave is the kernel
+                continue;
+            }
+            float us = 0;
+            st = profile_wave((int)i, occ, iters, &us);
+            kp.latency.push_back(std::max(1, (int)(us * 1000.f)));
+        }
+        out->kernel_latency.insert({name, kp});
+    }
+    if (st == Status::Succ) {
+        for (int r = 0; r < 3 && st == Status::Succ; r++) st = execute_graph(s);
+        reef_event_record(a, s);
+        for (int r = 0; r < iters && st == Status::Succ; r++) st = execute_graph(s);
+        reef_event_record(b, s);
+        out->model_latency = std::max(1, elapsed_ns(iters));
+    }
     reef_event_destroy(a);
     reef_event_destroy(b);
     return st;

@@ -114,6 +114,8 @@ public:
     // beside the real-time kernel on be_stream instead of inside one grid
     Status launch_dispatch(int rt_idx, HybridExecutor* be, int be_idx, int be_block_offset, int be_block_num,
                            int sm_partition, int occupancy, GPUStream_t stream, GPUStream_t be_stream = nullptr);
+    // best-effort logical blocks [offset, offset+num) of kernel idx alone, non-preemptible, counted into the task slot
+    Status launch_pad_piece(int idx, int block_offset, int block_num, int occupancy, GPUStream_t stream);
     bool has_tensor_core_kernels() const { return has_tc; }
     // CUDA graph of the whole kernel list on `stream` (captured lazily on first use)
     Status execute_graph(GPUStream_t stream);
@@ -125,6 +127,11 @@ public:
     Status profile_kernels(int iters, float* us);
     // one persistent wave of kernel idx: sms*occupancy logical blocks through the dispatcher (us)
     Status profile_wave(int idx, int occupancy, int iters, float* us);
+    // Measures the latency tables the padding policy reads (the reference's profile.json, produced there by a
+    // `profiler` binary that is not in its tree, resource/Makefile:32-36): per distinct kernel name the average
+    // duration of back-to-back launches (total_latency) and of one persistent wave at occupancy j+1
+    // (latency[j]); model_latency = one graph replay.  All in nanoseconds (latency_unit_ns = 1).
+    Status measure_profile(int iters, ModelProfile* out);
     const int* host_task_slots() const { return task_slots_host; }
 
     std::vector<KernelArg> trans_args;

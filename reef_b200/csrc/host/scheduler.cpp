@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <cassert>
+#include <cstdlib>
 
 namespace reef {
 namespace server {
@@ -46,6 +47,10 @@ REEFScheduler::REEFScheduler(ScheduleMode _mode, int _device)
         num_sms = 0;   // run()/load_model() refuse to work
     }
     be_stream_device_queue_cap = mode == WaitPreempt ? 1024 : 2;
+    for (auto& pp : pad_pieces) reef_event_create(&pp.ev);
+    if (const char* v = getenv("REEF_PAD_INFLIGHT")) set_pad_limits(atoi(v), pad_overcommit_sms);
+    if (const char* v = getenv("REEF_PAD_OVERCOMMIT")) set_pad_limits(pad_inflight_max, atoi(v));
+    if (const char* v = getenv("REEF_PAD_WINDOW")) set_pad_window(atoi(v));
 }
 
 REEFScheduler::~REEFScheduler() {
@@ -60,6 +65,8 @@ REEFScheduler::~REEFScheduler() {
             if (q->stream) reef_stream_destroy(q->stream);
         }
     if (rt_queue && rt_queue->stream) reef_stream_destroy(rt_queue->stream);
+    for (auto& pp : pad_pieces)
+        if (pp.ev) reef_event_destroy(pp.ev);
     if (preempt_stream) reef_stream_destroy(preempt_stream);
     if (preempt_flag) reef_free(preempt_flag);
 }
@@ -450,7 +457,8 @@ void REEFScheduler::execute_rt_task(std::shared_ptr<Task>& task) {
     task->start = std::chrono::system_clock::now();
     auto& exe = task->model->executor;
     if (mode == ScheduleMode::REEF && any_be_waiting()) {
-        dynamic_kernel_padding(task);
+        if (side_padding_needed(exe)) timeline_padding(task);
+        else dynamic_kernel_padding(task);
         reef_stream_sync(rt_queue->stream);
     } else if (rt_graph) {
         if (exe.execute_graph(rt_queue->stream) != Status::Succ) {
@@ -466,19 +474,166 @@ void REEFScheduler::execute_rt_task(std::shared_ptr<Task>& task) {
     finish_task(task);
 }
 
+// Best-effort progress after `blocks` logical blocks of the task's current kernel were issued as padding
+// (reference: scheduler.cpp:655-672).
+void REEFScheduler::advance_padded(Task* be_task, TaskQueue* q, int blocks, bool side_launch,
+                                   std::vector<std::shared_ptr<Task>>* complete) {
+    auto& be_exe = be_task->model->executor;
+    const HybridExecutor::KernelArg& be_args = be_exe.trans_args[be_task->kernel_offset];
+    be_task->padding = true;
+    be_task->needs_recover = true;   // resuming on its own stream must re-arm the counters
+    be_task->block_offset += blocks;
+    n_padded_kernels++;
+    n_padded_blocks += blocks;
+    if (be_task->block_offset < be_args.block_num) return;
+    be_task->block_offset = 0;
+    be_task->kernel_offset++;
+    be_task->launch_offset = be_task->kernel_offset;
+    const int n_be = (int)be_exe.num_kernels();
+    if (be_task->kernel_offset < n_be) return;
+    be_task->padding_to_finish = true;
+    if (side_launch) {
+        // its last blocks are on the best-effort stream: the task completes when that stream has drained,
+        // which the best-effort branch of the loop sees through the window
+        reef_event_t ev;
+        if (!q->free_events.empty()) {
+            ev = q->free_events.back();
+            q->free_events.pop_back();
+        } else {
+            reef_event_create(&ev);
+        }
+        reef_event_record(ev, q->stream);
+        q->inflight.push_back(InFlight{ev, n_be - 1});
+        be_task->all_issued_by_padding = true;
+        be_task->state.store(TaskState::Executing);
+    } else {
+        be_task->kernel_offset = 0;
+        complete->push_back(q->task_queue.front());
+        q->task_queue.pop();
+    }
+}
+
+bool REEFScheduler::side_padding_needed(HybridExecutor& rt_exe) {
+    if (rt_exe.has_tensor_core_kernels()) return true;
+    const uint32_t nq = be_queue_cnt.load();
+    for (uint32_t i = 0; i < nq; i++) {
+        auto t = be_queues[i]->task_queue.front();
+        if (t && t->model->executor.has_tensor_core_kernels()) return true;
+    }
+    return false;
+}
+
+// Dynamic kernel padding when a tensor-core (cluster) kernel is involved on either side.  Such kernels are
+// not hosted by the logical-block dispatcher, so the padding is done in space and time by separate launches:
+//  * the real-time task replays its CUDA graph on the high-priority stream (full speed, no per-kernel host work);
+//  * while it runs, this thread issues best-effort PIECES — block ranges of the head kernel of a best-effort
+//    queue, round-robin over the queues — on that queue's own low-priority stream, one piece in flight at a time;
+//  * a piece is sized from the SMs the real-time kernels of the next `pad_window` positions leave free
+//    (position = elapsed time mapped onto the measured latency profile, reference policy scheduler.cpp:566-595
+//    restated for a free-running real-time stream), whole clusters only.
+// Pieces are launched in the plain flavour (they do not poll the preempt flag; they are short and sized to the
+// idle SMs) and count into the task's completion slots.
+void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
+    auto& rt_exe = rt_task->model->executor;
+    const size_t n_rt = rt_exe.num_kernels();
+    const uint32_t nq = be_queue_cnt.load();
+    // cumulative profile time and SM footprint per real-time kernel
+    std::vector<double> cum(n_rt + 1, 0.0);
+    std::vector<int> part(n_rt, 0);
+    for (size_t k = 0; k < n_rt; k++) {
+        const HybridExecutor::KernelArg& a = rt_exe.trans_args[k];
+        const int layers = std::max(1, align_up<int>(a.block_num, num_sms) / num_sms);
+        part[k] = std::min(num_sms, align_up(a.block_num, layers) / layers);
+        cum[k + 1] = cum[k] + std::max(1, a.profile.total_latency);
+    }
+    const double unit = rt_exe.profile() ? rt_exe.profile()->latency_unit_ns : 1000;
+    const double model_ns = rt_exe.profile() && rt_exe.profile()->model_latency > 0
+                                ? rt_exe.profile()->model_latency * unit : cum[n_rt] * unit;
+    const double scale = cum[n_rt] > 0 ? model_ns / cum[n_rt] : 1.0;   // profile units -> ns of the graph replay
+
+    auto t0 = sclock::now();
+    if (rt_exe.execute_graph(rt_queue->stream) != Status::Succ) {
+        err_ = "real-time graph launch failed: " + rt_exe.error();
+        fprintf(stderr, "[reef] %s\n", err_.c_str());
+        return;
+    }
+    size_t pos = 0;
+    for (;;) {
+        int busy = 0;
+        if (reef_stream_query(rt_queue->stream, &busy) != REEF_SUCC || !busy) break;
+        // retire finished pieces; count what is still out
+        int inflight = 0, sms_out = 0, slot = -1;
+        uint32_t busy_queues = 0;
+        for (int p = 0; p < pad_inflight_max; p++) {
+            PadPiece& pp = pad_pieces[p];
+            if (pp.pending) {
+                int pending = 1;
+                if (reef_event_query(pp.ev, &pending) == REEF_SUCC && !pending) pp.pending = false;
+            }
+            if (pp.pending) {
+                inflight++;
+                sms_out += pp.sms;
+                busy_queues |= 1u << pp.queue;
+            } else if (slot < 0) {
+                slot = p;
+            }
+        }
+        if (slot < 0) continue;
+        // estimated position of the real-time stream
+        const double now_ns = (double)ns_since(t0);
+        while (pos < n_rt && cum[pos + 1] * scale <= now_ns) pos++;
+        if (pos >= n_rt) continue;   // in the tail: let the task finish
+        int part_w = 0;
+        for (size_t k = pos; k < std::min(n_rt, pos + (size_t)pad_window); k++) part_w = std::max(part_w, part[k]);
+        const int free_sms = num_sms - part_w + pad_overcommit_sms - sms_out;
+        if (free_sms <= 0) continue;
+
+        auto sel_start = sclock::now();
+        for (uint32_t n = 0; n < nq; n++) {
+            const uint32_t qi = (dkp_next_queue + n) % nq;
+            if (busy_queues & (1u << qi)) continue;   // one piece per best-effort stream: pieces of a task stay ordered
+            auto& q = *be_queues[qi];
+            if (q.task_queue.empty()) continue;
+            auto be_task = q.task_queue.front();
+            auto& be_exe = be_task->model->executor;
+            if (be_task->kernel_offset >= (int)be_exe.num_kernels()) continue;   // fully issued, draining
+            HybridExecutor::KernelArg& be_args = be_exe.trans_args[be_task->kernel_offset];
+            int occ = 1;
+            if (!be_args.resource.tensor_core) occ = std::max(1, std::min(2, be_args.resource.max_blocks_per_sm));
+            int blocks = std::min(free_sms * occ, be_args.block_num - be_task->block_offset);
+            blocks -= blocks % be_args.granularity;
+            if (blocks <= 0) continue;
+            if (be_task->start.time_since_epoch().count() == 0) be_task->start = std::chrono::system_clock::now();
+            if (be_exe.launch_pad_piece(be_task->kernel_offset, be_task->block_offset, blocks, occ, q.stream) != Status::Succ) {
+                err_ = be_exe.error();
+                break;
+            }
+            PadPiece& pp = pad_pieces[slot];
+            reef_event_record(pp.ev, q.stream);
+            pp.pending = true;
+            pp.sms = (blocks + occ - 1) / occ;
+            pp.queue = qi;
+            advance_padded(be_task.get(), &q, blocks, true, nullptr);
+            dkp_next_queue = (qi + 1) % nq;
+            break;
+        }
+        kernel_sel_count++;
+        kernel_sel_latency_sum += ns_since(sel_start);
+    }
+}
+
 // reference: scheduler.cpp:477-683.  Per real-time kernel: pick a best-effort queue whose head kernel can
-// share the GPU (occupancy) and whose one-wave latency fits inside the real-time kernel (profile), size its
-// block count from the SMs the real-time kernel leaves free, launch both through reef_dispatch, and advance
-// the best-effort task's (kernel_offset, block_offset).  Queues are tried round-robin (the reference always
-// starts at queue 0, scheduler.cpp:533, which starves the later clients under a busy real-time client).
-// When both models consist of logical-block kernels only, the two kernels share ONE persistent dispatcher
-// grid on the real-time stream; as soon as a tensor-core cluster kernel is involved the best-effort blocks
-// are launched beside the real-time kernel on the best-effort queue's own stream.
+// share the grid (occupancy) and whose one-wave latency fits inside the real-time kernel (profile), size its
+// block count from the SMs the real-time kernel leaves free, launch ONE persistent dispatcher grid for both,
+// and advance the best-effort task's (kernel_offset, block_offset).  Used when every kernel on both sides is a
+// logical-block family.  Queues are tried round-robin (the reference always starts at queue 0,
+// scheduler.cpp:533, which starves the later clients under a busy real-time client).
 void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
     auto& rt_exe = rt_task->model->executor;
     std::vector<std::shared_ptr<Task>> complete_be_tasks;
     auto current_time_point = std::chrono::system_clock::now();
     const uint32_t nq = be_queue_cnt.load();
+    const int64_t unit = rt_exe.profile() ? rt_exe.profile()->latency_unit_ns : 1000;
 
     for (size_t i = 0; i < rt_exe.num_kernels(); i++) {
         auto sel_start = sclock::now();
@@ -488,7 +643,6 @@ void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
         const int logical_layers = std::max(1, align_up<int>(rt_args.block_num, num_sms) / num_sms);
 
         Task* final_be_task = nullptr;
-        HybridExecutor::KernelArg* final_be_args = nullptr;
         TaskQueue* final_queue = nullptr;
         int final_occupancy = required_occupancy, final_be_block_num = 0, sm_partition = num_sms;
 
@@ -498,13 +652,12 @@ void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
             if (be_queue.empty()) continue;
             auto be_task = be_queue.front();
             auto& be_exe = be_task->model->executor;
-            if (be_task->kernel_offset >= (int)be_exe.num_kernels()) continue;   // fully issued already
+            if (be_task->kernel_offset >= (int)be_exe.num_kernels()) continue;
             HybridExecutor::KernelArg& be_args = be_exe.trans_args[be_task->kernel_offset];
 
-            // 1. occupancy both kernels can run at
+            // 1. occupancy both kernels can run at inside one grid
             int merged_occupancy = std::min(rt_args.resource.max_blocks_per_sm, be_args.resource.max_blocks_per_sm);
             if (merged_occupancy < required_occupancy) continue;
-
             // 2. latency profile decides the best-effort occupancy
             int be_occupancy = 0;
             for (int j = merged_occupancy - 1; j >= 0; j--) {
@@ -515,7 +668,6 @@ void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
                 }
             }
             if (be_occupancy == 0) continue;
-
             // 3. partition and block budget
             int part = align_up(rt_args.block_num, logical_layers) / logical_layers;
             if (part >= num_sms) continue;   // the real-time kernel fills every SM: nothing to pad
@@ -523,13 +675,11 @@ void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
             int be_iters = std::max(1, rt_latency / be_latency_per_iter);
             int blocks = (num_sms - part) * be_iters * be_occupancy;
             blocks = std::min(blocks, be_args.block_num - be_task->block_offset);
-            blocks -= blocks % be_args.granularity;   // cluster kernels advance by whole clusters
             if (blocks <= 0) continue;
 
             sm_partition = part;
             final_occupancy = std::max(required_occupancy, be_occupancy);
             final_be_block_num = blocks;
-            final_be_args = &be_args;
             final_be_task = be_task.get();
             final_queue = be_queues[qi].get();
             dkp_next_queue = (qi + 1) % nq;
@@ -538,56 +688,18 @@ void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
         kernel_sel_count++;
         kernel_sel_latency_sum += ns_since(sel_start);
 
-        bool side_launch = false;
         if (final_be_task == nullptr) {
             rt_exe.launch_dispatch((int)i, nullptr, 0, 0, 0, num_sms, required_occupancy, rt_queue->stream);
         } else {
-            auto& be_exe = final_be_task->model->executor;
-            side_launch = rt_exe.has_tensor_core_kernels() || be_exe.has_tensor_core_kernels();
             if (final_be_task->start.time_since_epoch().count() == 0) final_be_task->start = current_time_point;
-            rt_exe.launch_dispatch((int)i, &be_exe, final_be_task->kernel_offset, final_be_task->block_offset,
-                                   final_be_block_num, sm_partition, final_occupancy, rt_queue->stream,
-                                   side_launch ? final_queue->stream : nullptr);
-            n_padded_kernels++;
-            n_padded_blocks += final_be_block_num;
+            rt_exe.launch_dispatch((int)i, &final_be_task->model->executor, final_be_task->kernel_offset,
+                                   final_be_task->block_offset, final_be_block_num, sm_partition, final_occupancy,
+                                   rt_queue->stream, nullptr);
         }
-        current_time_point += std::chrono::nanoseconds((int64_t)rt_args.profile.total_latency *
-                                                       (rt_exe.profile() ? rt_exe.profile()->latency_unit_ns : 1000));
-
-        // 6. best-effort progress
+        current_time_point += std::chrono::nanoseconds((int64_t)rt_args.profile.total_latency * unit);
         if (final_be_task != nullptr) {
-            final_be_task->padding = true;
-            final_be_task->needs_recover = true;   // resuming on its own stream must re-arm the counters
-            final_be_task->block_offset += final_be_block_num;
-            if (final_be_task->block_offset >= final_be_args->block_num) {
-                final_be_task->block_offset = 0;
-                final_be_task->kernel_offset++;
-                final_be_task->launch_offset = final_be_task->kernel_offset;
-                const int n_be = (int)final_be_task->model->executor.num_kernels();
-                if (final_be_task->kernel_offset >= n_be) {
-                    final_be_task->padding_to_finish = true;
-                    if (side_launch) {
-                        // its last blocks are on the best-effort stream: the task completes when that stream
-                        // has drained, which the best-effort branch of the loop sees through the window
-                        reef_event_t ev;
-                        if (!final_queue->free_events.empty()) {
-                            ev = final_queue->free_events.back();
-                            final_queue->free_events.pop_back();
-                        } else {
-                            reef_event_create(&ev);
-                        }
-                        reef_event_record(ev, final_queue->stream);
-                        final_queue->inflight.push_back(InFlight{ev, n_be - 1});
-                        final_be_task->all_issued_by_padding = true;
-                        final_be_task->state.store(TaskState::Executing);
-                    } else {
-                        final_be_task->end = current_time_point;
-                        final_be_task->kernel_offset = 0;
-                        complete_be_tasks.push_back(be_queues[final_be_task->qid]->task_queue.front());
-                        be_queues[final_be_task->qid]->task_queue.pop();
-                    }
-                }
-            }
+            advance_padded(final_be_task, final_queue, final_be_block_num, false, &complete_be_tasks);
+            if (final_be_task->padding_to_finish) final_be_task->end = current_time_point;
         }
     }
     if (!complete_be_tasks.empty()) {

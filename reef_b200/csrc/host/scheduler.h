@@ -95,6 +95,13 @@ public:
     void set_be_stream_cap(int value) { be_stream_device_queue_cap = value < 1 ? 1 : value; }
     // real-time tasks that find no best-effort work replay a CUDA graph of the model (default on)
     void set_rt_graph(bool value) { rt_graph = value; }
+    // real-time kernels ahead of the estimated position whose SM footprint bounds a padded piece (default 2)
+    void set_pad_window(int value) { pad_window = value < 1 ? 1 : value; }
+    // padded pieces in flight at most (1..8) and SMs they may claim beyond the profile's free count
+    void set_pad_limits(int inflight, int overcommit_sms) {
+        pad_inflight_max = inflight < 1 ? 1 : (inflight > kMaxPadInflight ? kMaxPadInflight : inflight);
+        pad_overcommit_sms = overcommit_sms < 0 ? 0 : overcommit_sms;
+    }
     Status run();
     Status shutdown();
 
@@ -133,6 +140,10 @@ private:
     void preempt_reset();
     void preempt_wait();
     void dynamic_kernel_padding(std::shared_ptr<Task>& rt_task);
+    void timeline_padding(std::shared_ptr<Task>& rt_task);
+    bool side_padding_needed(executor::HybridExecutor& rt_exe);
+    void advance_padded(Task* be_task, TaskQueue* q, int blocks, bool side_launch,
+                        std::vector<std::shared_ptr<Task>>* complete);
     void retire(TaskQueue& q, Task& t);
     void finish_task(std::shared_ptr<Task>& t);
     bool any_be_waiting();
@@ -168,6 +179,18 @@ private:
     std::atomic<uint64_t> pending_tasks;
 
     uint32_t dkp_next_queue = 0;
+    // timeline padding: padded pieces in flight (completion event + SMs they may occupy)
+    static const int kMaxPadInflight = 8;
+    struct PadPiece {
+        reef_event_t ev = nullptr;
+        int sms = 0;
+        bool pending = false;
+        uint32_t queue = 0;
+    };
+    PadPiece pad_pieces[kMaxPadInflight];
+    int pad_inflight_max = 4;           // pieces in flight at most (each on a different best-effort stream)
+    int pad_overcommit_sms = 32;        // SMs pieces may claim beyond what the profile says is free
+    int pad_window = 2;                 // real-time kernels a padded piece may overlap (footprint look-ahead)
     uint64_t preempt_count, preempt_latency_sum, preempt_latency_max;
     uint64_t kernel_sel_count, kernel_sel_latency_sum;
     uint64_t n_rt_tasks, n_be_tasks, n_be_padded_finish, n_padded_kernels, n_padded_blocks;

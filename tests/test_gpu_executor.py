@@ -216,3 +216,25 @@ def test_preempted_and_rerun_is_bit_identical(gen, model, delays):
             assert np.array_equal(a, b), f"delay {d}us: storage {i} differs after {restarts} restarts (first {first})"
         print(model, "delay", d, "us -> restarts", restarts, "first incomplete kernel", first)
     assert hit > 0, "no delay landed inside the run; preemption was not exercised"
+
+
+def test_profiler_writes_reference_schema(gen, tmp_path):
+    """The measured profile parses with the reference-schema reader and has a positive latency for every
+    distinct kernel (reference: test.cpp:79-91 parser.parse_profile)."""
+    import ctypes as C
+    import shutil
+    from reef_b200 import profiler
+    base = gen("resnet18_64")
+    for ext in (".json", ".param"):
+        shutil.copy(base + ext, str(tmp_path / ("m" + ext)))
+    out = profiler.profile_model(str(tmp_path / "m"), iters=3)
+    j = json.load(open(base + ".json"))
+    prof = json.load(open(out))
+    assert prof["latency_unit_ns"] == 1 and prof["model_latency"] > 0
+    assert set(prof["kernel_latency"]) == {k["name"] for k in j["kernels"]}
+    n, ml, mn = C.c_size_t(), C.c_int(), C.c_int()
+    assert capi.host_lib().reef_profile_parse(out.encode(), C.byref(n), C.byref(ml), C.byref(mn)) == capi.SUCC
+    assert n.value == len(prof["kernel_latency"]) and mn.value > 0
+    # the executor accepts it
+    e = capi.HybridExecutor(0)
+    e.load_model_from_file(str(tmp_path / "m.json"), out)
