@@ -289,7 +289,7 @@ def main():
     e.set_input("data", x)
     prof = e.profile_kernels(20)
     names = [k["name"] for k in json.load(open(base + ".json"))["kernels"]]
-    conv = [(n, p) for n, p in zip(names, prof) if n.startswith("fused_nn_conv2d")]
+    conv = [(n, p) for n, p in zip(names, prof) if p["tensor_core"]]   # reef_conv_tc_kernel launches
     conv_us = sum(p["us"] for _, p in conv)
     conv_bytes = sum(p["bytes"] for _, p in conv)
     conv_flops = sum(p["flops"] for _, p in conv)
@@ -302,7 +302,8 @@ def main():
         traffic = json.load(open(tpath)).get("traffic_bytes_per_launch")
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "peak_kind": peak_kind,
-                "kernel": "conv2d family (%d launches of one ResNet-152 pass, timed in context with CUDA events)" % len(conv),
+                "kernel": "reef_conv_tc_kernel (tcgen05 TF32 convolution: %d launches of one ResNet-152 pass, "
+                          "timed in context with CUDA events between the kernels of whole passes)" % len(conv),
                 "algorithmic_bytes_per_pass": conv_bytes, "avg_launch_us": conv_us / max(1, len(conv)),
                 "conv_tflops": conv_flops / (conv_us * 1e-6) / 1e12, "conv_share_of_kernel_time": conv_us / all_us,
                 "model_kernel_time_us": all_us}
