@@ -166,6 +166,32 @@ REEF_API reef_status reef_dispatch(reef_kernel_t rt, void** rt_args,
                                    reef_dptr_t rt_ctrl, reef_dptr_t be_ctrl,
                                    reef_stream_t s, reef_stream_t be_stream);
 
+/* reef_dispatch for callers that must not allocate device memory.  No counterpart in the reference (its
+ * proxy kernels keep no state in global memory).
+ * Who needs it: the dispatcher keeps its ticket counters in 16 bytes of zeroed device memory that
+ * reef_dispatch expects the caller to own (rt_ctrl).  A scheduler loop that is in the middle of serving a
+ * real-time request, or code running inside a CUDA stream capture, cannot get such memory: cudaMalloc
+ * synchronises the whole device (it would stall the very request being served) and is not permitted while a
+ * capture is open.  This entry point keeps the counters in a file-scope static device array inside the
+ * library instead, so it calls no cudaMalloc / cudaFree and no other allocating routine.
+ * Limits and rules:
+ *  - REEF_STATIC_DISPATCH_LANES (64) lanes of 256 bytes = 16 KB of device memory, held by every GPU that loads
+ *    the library until the process exits; `lane` >= 64 is rejected with REEF_OUT_OF_RANGE and a message.
+ *  - All launches that name the same lane share its counters, and a lane keeps what the last launch left in
+ *    it: every call first clears the lane on `s` (stream-ordered 16-byte memset), so calls on one stream are
+ *    safe back to back, but two launches that use the same lane and can overlap on the GPU race on the
+ *    tickets.  Give concurrent streams different lanes.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *    current); make that first call before any stream capture begins.
+ *  - Logical-block kernels only (one persistent grid); a tensor-core cluster kernel on either side is
+ *    refused with REEF_FAIL.  Everything else is as in reef_dispatch's single-grid form. */
+#define REEF_STATIC_DISPATCH_LANES 64
+REEF_API reef_status reef_dispatch_static(reef_kernel_t rt, void** rt_args,
+                                          reef_kernel_t be, void** be_args,
+                                          int be_block_offset, int be_block_num,
+                                          int sm_partition, int occupancy,
+                                          reef_dptr_t be_task_slot, int lane, reef_stream_t s);
+
 /* GPUClearHostQueue / GPUResetCU (reference: hip_impl.h:21-22) have no CUDA equivalent: queued
  * launches are dropped by the host scheduler before they reach the stream and running blocks leave
  * at their next flag poll.  This call is the bounded replacement for the reference's wait loop

@@ -311,6 +311,16 @@ reef_status reef_dispatch(reef_kernel_t rt, void** rt_args, reef_kernel_t be, vo
                            (cudaStream_t)be_stream);
 }
 
+reef_status reef_dispatch_static(reef_kernel_t rt, void** rt_args, reef_kernel_t be, void** be_args, int be_off,
+                                 int be_num, int sm_partition, int occupancy, reef_dptr_t be_slot, int lane,
+                                 reef_stream_t s) {
+    int sms = 0;
+    int rc = reef_device_num_sms(&sms);
+    if (rc != REEF_SUCC) return rc;
+    return launch_dispatch_static(rt ? &rt->spec : nullptr, rt_args, be ? &be->spec : nullptr, be_args, be_off, be_num,
+                                  sm_partition, occupancy, sms, (int*)be_slot, lane, (cudaStream_t)s);
+}
+
 reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us) {
     auto t0 = std::chrono::steady_clock::now();
     for (;;) {

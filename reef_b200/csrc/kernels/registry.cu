@@ -633,6 +633,72 @@ int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, 
     return REEF_SUCC;
 }
 
+// ---- dispatcher without any allocation -------------------------------------------------------------
+// Ticket blocks for callers that must not allocate: one 256-byte lane per concurrent dispatcher launch, held
+// by every GPU that loads this library until the process exits (16 KB).  In host code the array's name is
+// only a stand-in for the device object; its device address comes from cudaGetSymbolAddress, once per device.
+constexpr int kStaticLanes = REEF_STATIC_DISPATCH_LANES;
+constexpr int kLaneInts = 64;   // 256 bytes apart: lanes never share a cache line
+static __device__ __align__(256) int g_static_dispatch_ctrl[kStaticLanes * kLaneInts];
+static int* g_static_ctrl_ptr[16] = {nullptr};
+
+int launch_dispatch_static(const KernelSpec* rt, void** rt_args, const KernelSpec* be, void** be_args, int be_off,
+                           int be_num, int sm_partition, int occupancy, int num_sms, int* be_slot, int lane,
+                           cudaStream_t st) {
+    if (lane < 0 || lane >= kStaticLanes) {
+        set_error("reef_dispatch_static: lane " + std::to_string(lane) + " is beyond the " +
+                  std::to_string(kStaticLanes) + " statically reserved lanes (REEF_STATIC_DISPATCH_LANES)");
+        return REEF_OUT_OF_RANGE;
+    }
+    if (rt == nullptr && be == nullptr) return REEF_FAIL;
+    if (be == nullptr) be_num = 0;
+    if ((rt != nullptr && rt->task.family == F_CONV_TC) || (be_num > 0 && be->task.family == F_CONV_TC)) {
+        set_error("reef_dispatch_static hosts logical-block kernels only (a tensor-core cluster kernel was given)");
+        return REEF_FAIL;
+    }
+    if (be_num > 0 && (be_off < 0 || be_off + be_num > be->task.nblocks)) {
+        set_error("best-effort block range outside the kernel");
+        return REEF_OUT_OF_RANGE;
+    }
+    int dev = 0;
+    if (check_cuda(cudaGetDevice(&dev), "cudaGetDevice") != REEF_SUCC) return REEF_FAIL;
+    if (dev < 0 || dev >= 16) {
+        set_error("reef_dispatch_static: device ordinal out of range");
+        return REEF_OUT_OF_RANGE;
+    }
+    if (g_static_ctrl_ptr[dev] == nullptr) {
+        // set-up, once per device, with that device current
+        void* p = nullptr;
+        int rc = check_cuda(cudaGetSymbolAddress(&p, g_static_dispatch_ctrl), "cudaGetSymbolAddress(static dispatch lanes)");
+        if (rc != REEF_SUCC) return rc;
+        g_static_ctrl_ptr[dev] = static_cast<int*>(p);
+    }
+    int* ctrl = g_static_ctrl_ptr[dev] + lane * kLaneInts;
+    // the lane keeps whatever the previous launch left (zero after a launch that drained): start from zero
+    int rc = check_cuda(cudaMemsetAsync(ctrl, 0, 16, st), "cudaMemsetAsync(static dispatch lane)");
+    if (rc != REEF_SUCC) return rc;
+    KTask trt, tbe;
+    uint32_t smem = 0;
+    if (rt != nullptr) {
+        fill_args(*rt, rt_args, &trt);
+        smem = rt->dyn_smem;
+    } else {
+        memset(&trt, 0, sizeof(trt));
+    }
+    if (be_num > 0) {
+        fill_args(*be, be_args, &tbe);
+        if (be->dyn_smem > smem) smem = be->dyn_smem;
+    } else {
+        memset(&tbe, 0, sizeof(tbe));
+    }
+    if (occupancy < 1) occupancy = 1;
+    int grid = num_sms * occupancy;
+    void* kargs[] = {&trt, &tbe, &be_off, &be_num, &sm_partition, (void*)&be_slot, (void*)&ctrl};
+    cudaError_t e = cudaLaunchKernel((const void*)k_dispatch, dim3(grid), dim3(kThreads), kargs, smem, st);
+    g_launches++;
+    return check_cuda(e, "cudaLaunchKernel(dispatch, static lane)");
+}
+
 int kernel_attrs(const KernelSpec& s, reef_kernel_attrs_t* out) {
     cudaFuncAttributes fa;
     int threads = s.block[0] * s.block[1] * s.block[2];

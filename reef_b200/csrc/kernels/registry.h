@@ -46,6 +46,9 @@ int launch_be(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cudaSt
 int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, void** be_args, int be_off,
                     int be_num, int sm_partition, int occupancy, int num_sms, int* be_slot, int* ctrl, int* be_ctrl,
                     cudaStream_t st, cudaStream_t be_st);
+int launch_dispatch_static(const KernelSpec* rt, void** rt_args, const KernelSpec* be, void** be_args, int be_off,
+                           int be_num, int sm_partition, int occupancy, int num_sms, int* be_slot, int lane,
+                           cudaStream_t st);
 int kernel_attrs(const KernelSpec& s, reef_kernel_attrs_t* out);
 int prepare_kernel(const KernelSpec& s, void** args);
 int dispatch_occupancy(uint32_t smem, int* occ);
