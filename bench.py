@@ -318,17 +318,16 @@ def main():
     value = total_inf / region_s
     ms_per_step = 1000.0 * region_s / max(1, rt_r["completed"])
     e2e_value = e2e_total
+    from reef_b200 import replicas
+    sums, maxes = replicas.aggregate(dist, {"value": value, "e2e": e2e_value, "launches": float(launches)},
+                                     {"ms_per_step": ms_per_step, "rt_p99_ms": extra["rt_p99_ms"],
+                                      "rt_alone_p99_ms": extra["rt_alone_p99_ms"]},
+                                     device="cuda" if dist is not None else None)
+    value, e2e_value, launches = sums["value"], sums["e2e"], int(sums["launches"])
+    ms_per_step = maxes["ms_per_step"]
     if dist is not None:
-        t = torch.tensor([value, e2e_value, ms_per_step, float(launches)], dtype=torch.float64, device="cuda")
-        tsum = t.clone()
-        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        value, e2e_value, launches = float(tsum[0]), float(tsum[1]), int(tsum[3])
-        ms_per_step = float(tmax[2])
-        p99 = torch.tensor([extra["rt_p99_ms"], extra["rt_alone_p99_ms"]], dtype=torch.float64, device="cuda")
-        dist.all_reduce(p99, op=dist.ReduceOp.MAX)
-        extra["rt_p99_ms_max_over_ranks"], extra["rt_alone_p99_ms_max_over_ranks"] = float(p99[0]), float(p99[1])
+        extra["rt_p99_ms_max_over_ranks"] = maxes["rt_p99_ms"]
+        extra["rt_alone_p99_ms_max_over_ranks"] = maxes["rt_alone_p99_ms"]
 
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
