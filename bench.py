@@ -117,6 +117,7 @@ def run_reference_arm(args, rank, world):
     x = np.random.default_rng(2001).normal(0, 1, 3 * 224 * 224).astype(np.float32)
     o = oracle.OracleExecutor(base + ".json", base + ".param")
     o.set_input("data", x)
+    oracle.set_threads(os.cpu_count() or 1)   # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every host core
     cores = oracle.num_threads()
     for _ in range(max(1, min(args.warmup, 3))):
         o.execute()
@@ -332,6 +333,7 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         from oracle import oracle
+        oracle.set_threads(os.cpu_count() or 1)
         o = oracle.OracleExecutor(base + ".json", base + ".param")
         o.set_input("data", x)
         o.execute()

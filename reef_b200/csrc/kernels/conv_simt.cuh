@@ -167,6 +167,13 @@ __device__ __forceinline__ bool body_conv_simt(const KTask& t, int vb, unsigned 
             } else {
                 v.x += sh.x; v.y += sh.y; v.z += sh.z; v.w += sh.w;
             }
+            if (p.ep & EP_GELU) {
+                // exact-erf GELU (reference: resource/bert/bert.cu:167-173)
+                v.x = v.x * (0.5f * erff(v.x * 0.70710678118654752440f) + 0.5f);
+                v.y = v.y * (0.5f * erff(v.y * 0.70710678118654752440f) + 0.5f);
+                v.z = v.z * (0.5f * erff(v.z * 0.70710678118654752440f) + 0.5f);
+                v.w = v.w * (0.5f * erff(v.w * 0.70710678118654752440f) + 0.5f);
+            }
             if (p.ep & EP_RELU) {
                 v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f);
                 v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);

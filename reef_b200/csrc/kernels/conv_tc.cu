@@ -196,6 +196,7 @@ int tc_build_params(const ConvP& p, const TcPlan& pl, void* const* a, TcParams* 
     if (p.ep & EP_BIAS) P->ep |= TC_EP_BIAS;
     if (p.ep & EP_GB) P->ep |= TC_EP_GB;
     if (p.ep & EP_RELU) P->ep |= TC_EP_RELU;
+    if (p.ep & EP_GELU) P->ep |= TC_EP_GELU;
     if (p.round_tf32) P->ep |= TC_EP_ROUND;
     P->b_bytes = pl.b_bytes;
     P->cb_magic = (unsigned)((0x100000000ull + (unsigned long long)pl.cblocks - 1) / (unsigned long long)pl.cblocks);

@@ -151,12 +151,18 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-enum : int { TC_EP_RES = 1, TC_EP_BIAS = 2, TC_EP_GB = 4, TC_EP_RELU = 8, TC_EP_ROUND = 16 };
+enum : int { TC_EP_RES = 1, TC_EP_BIAS = 2, TC_EP_GB = 4, TC_EP_RELU = 8, TC_EP_ROUND = 16, TC_EP_GELU = 32 };
 
 // Branch-free form of (+residual) (+bias | *gamma+beta) (ReLU): r = 0, sc = 1, sh = 0, lo = -inf stand in for
 // the absent terms (v + 0 and fma(v, 1, b) are exact, so this equals the conditional form bit for bit).
-__device__ __forceinline__ float tc_epilogue(float v, float r, float sc, float sh, float lo, bool rnd) {
-    v = fmaxf(fmaf(v + r, sc, sh), lo);
+__device__ __forceinline__ float tc_epilogue(float v, float r, float sc, float sh, float lo, bool rnd, bool gelu = false) {
+    if (gelu) {
+        // matmul + bias -> exact-erf GELU -> (+residual)   (reference: resource/bert/bert.cu:167-173)
+        v = v + sh;
+        v = v * (0.5f * erff(v * 0.70710678118654752440f) + 0.5f) + r;
+    } else {
+        v = fmaxf(fmaf(v + r, sc, sh), lo);
+    }
     if (rnd) {
         // The tensor core reads only the upper 19 bits of an fp32 operand (truncation, a bias toward zero).
         // Rounding the stored activation to the nearest TF32 value makes the consumer's truncation exact.
@@ -404,6 +410,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
         const float lo = (P.ep & TC_EP_RELU) ? 0.f : -__int_as_float(0x7f800000);
         const bool has_res = (P.ep & TC_EP_RES) != 0;
         const bool rnd = (P.ep & TC_EP_ROUND) != 0;
+        const bool gelu = (P.ep & TC_EP_GELU) != 0;
         // Four pixel rows per warp are in flight at a time (all partial and residual loads issued before the
         // first use): with one or two warps per scheduler the loop is latency-bound, not bandwidth-bound.
         if (ok && cvalid) {
@@ -425,10 +432,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
                         const int j = jbase + 8 * u;
                         if (j < je) {
                             float4 o;
-                            o.x = tc_epilogue(v[u].x, rv[u].x, sc.x, sh.x, lo, rnd);
-                            o.y = tc_epilogue(v[u].y, rv[u].y, sc.y, sh.y, lo, rnd);
-                            o.z = tc_epilogue(v[u].z, rv[u].z, sc.z, sh.z, lo, rnd);
-                            o.w = tc_epilogue(v[u].w, rv[u].w, sc.w, sh.w, lo, rnd);
+                            o.x = tc_epilogue(v[u].x, rv[u].x, sc.x, sh.x, lo, rnd, gelu);
+                            o.y = tc_epilogue(v[u].y, rv[u].y, sc.y, sh.y, lo, rnd, gelu);
+                            o.z = tc_epilogue(v[u].z, rv[u].z, sc.z, sh.z, lo, rnd, gelu);
+                            o.w = tc_epilogue(v[u].w, rv[u].w, sc.w, sh.w, lo, rnd, gelu);
                             *reinterpret_cast<float4*>(P.out + (size_t)(pix0 + j) * P.ocs + P.ooff + co) = o;
                         }
                     }
@@ -462,10 +469,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
                             for (int q = 0; q < TC_MAX_SPLITS; q++)   // fixed rank order: deterministic sum
                                 if (q < S) { v.x += part[u][q].x; v.y += part[u][q].y; v.z += part[u][q].z; v.w += part[u][q].w; }
                             float4 o;
-                            o.x = tc_epilogue(v.x, rv[u].x, sc.x, sh.x, lo, rnd);
-                            o.y = tc_epilogue(v.y, rv[u].y, sc.y, sh.y, lo, rnd);
-                            o.z = tc_epilogue(v.z, rv[u].z, sc.z, sh.z, lo, rnd);
-                            o.w = tc_epilogue(v.w, rv[u].w, sc.w, sh.w, lo, rnd);
+                            o.x = tc_epilogue(v.x, rv[u].x, sc.x, sh.x, lo, rnd, gelu);
+                            o.y = tc_epilogue(v.y, rv[u].y, sc.y, sh.y, lo, rnd, gelu);
+                            o.z = tc_epilogue(v.z, rv[u].z, sc.z, sh.z, lo, rnd, gelu);
+                            o.w = tc_epilogue(v.w, rv[u].w, sc.w, sh.w, lo, rnd, gelu);
                             *reinterpret_cast<float4*>(P.out + (size_t)(pix0 + jb + jr) * P.ocs + P.ooff + co) = o;
                         }
                     }

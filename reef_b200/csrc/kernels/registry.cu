@@ -11,6 +11,7 @@
 #include <map>
 #include <string>
 
+#include "bert.cuh"
 #include "conv_simt.cuh"
 #include "conv_tc_params.h"
 #include "simple.cuh"
@@ -175,6 +176,75 @@ static int build_spec(const std::string& name, KernelSpec* s) {
         s->bytes = 8.0 * p.rows * p.n;
         return REEF_SUCC;
     }
+    if (op == "reef_embedding") {
+        int sN, h, vocab;
+        if (!a.need("s", &sN) || !a.need("h", &h) || !a.need("vocab", &vocab) || (h & 3)) goto bad;
+        t.p.raw[0] = sN; t.p.raw[1] = h; t.p.raw[2] = vocab;
+        t.family = F_EMBEDDING;
+        t.nblocks = ceil_div(sN * (h / 4), kThreads * 4);
+        s->nargs = 4;
+        s->bytes = 4.0 * 3.0 * sN * h + 8.0 * sN;
+        return REEF_SUCC;
+    }
+    if (op == "reef_layernorm" || op == "reef_add_layernorm") {
+        int rows, h;
+        if (!a.need("rows", &rows) || !a.need("h", &h) || (h % 128) != 0 || h > 1024) goto bad;
+        t.p.raw[0] = rows; t.p.raw[1] = h; t.p.raw[2] = op == "reef_add_layernorm";
+        t.family = F_LAYERNORM;
+        t.nblocks = ceil_div(rows, kLnRowsPerBlock);
+        s->nargs = t.p.raw[2] ? 5 : 4;
+        s->bytes = 4.0 * ((2.0 + t.p.raw[2]) * rows * h + 2.0 * h);
+        return REEF_SUCC;
+    }
+    if (op == "reef_attention") {
+        int sN, heads, d;
+        if (!a.need("s", &sN) || !a.need("heads", &heads) || !a.need("d", &d) || d != kAttD) goto bad;
+        t.p.raw[0] = sN; t.p.raw[1] = heads; t.p.raw[2] = d; t.p.raw[3] = (int)a.get("mask", 0);
+        t.family = F_ATTENTION;
+        t.nblocks = heads * ceil_div(sN, kAttRows);
+        s->dyn_smem = kAttSmem;
+        s->nargs = t.p.raw[3] ? 3 : 2;
+        s->flops = 4.0 * heads * (double)sN * sN * d;
+        s->bytes = 4.0 * 4.0 * sN * heads * d;
+        return REEF_SUCC;
+    }
+    if (op.rfind("reef_matmul_nt", 0) == 0) {
+        // C[m][n] = sum_k A[m][k] * B[n][k] (+bias[n]) (GELU) (+residual[m][n])  (reference: bert.cu:206-271):
+        // a 1x1 convolution over m "pixels": A = channels-last activations, B = weights [n][k]
+        ConvP& p = t.p.conv;
+        std::string tail = op.substr(strlen("reef_matmul_nt"));
+        int m, n, k;
+        if (!a.need("m", &m) || !a.need("n", &n) || !a.need("k", &k)) goto bad;
+        p.ep = 0;
+        p.i_res = p.i_bias = p.i_gamma = p.i_beta = -1;
+        int nargs = 3;
+        if (tail.find("_bias") != std::string::npos) { p.ep |= EP_BIAS; p.i_bias = nargs++; }
+        if (tail.find("_gelu") != std::string::npos) p.ep |= EP_GELU;
+        if (tail.find("_residual") != std::string::npos) { p.ep |= EP_RES; p.i_res = nargs++; }
+        p.ci = k; p.hi = 1; p.wi = m; p.co = n; p.kh = p.kw = 1; p.sh = p.sw = 1; p.ph = p.pw = 0;
+        p.ho = 1; p.wo = m; p.nchw = 0; p.ics = k; p.ioff = 0; p.ocs = n; p.ooff = 0;
+        p.ktot = k; p.ptot = m;
+        if ((n & 3) || (k & 3)) goto bad;
+        s->nargs = nargs;
+        s->flops = 2.0 * m * (double)n * k;
+        s->bytes = 4.0 * ((double)m * k + (double)n * k + (double)m * n * ((p.ep & EP_RES) ? 2.0 : 1.0) + n);
+        if ((int)a.get("v", 0) == 1) {
+            p.round_tf32 = (int)a.get("rt", 0);   // outputs feed LayerNorm / attention in fp32: no TF32 rounding
+            if (tc_plan(p, &s->tc) != REEF_SUCC) goto bad;
+            t.family = F_CONV_TC;
+            t.nblocks = s->tc.splits * s->tc.n_tiles * s->tc.m_tiles;
+            s->dyn_smem = (uint32_t)s->tc.smem;
+            s->block[0] = TC_THREADS;
+            s->tensor_core = 1;
+            return REEF_SUCC;
+        }
+        t.family = F_CONV_SIMT;
+        p.tiles_p = ceil_div(p.ptot, CBM);
+        p.tiles_c = ceil_div(p.co, CBN);
+        t.nblocks = p.tiles_p * p.tiles_c;
+        s->dyn_smem = kConvSimtSmem;
+        return REEF_SUCC;
+    }
     if (op.rfind("fused_nn_conv2d", 0) == 0) {
         ConvP& p = t.p.conv;
         std::string tail = op.substr(strlen("fused_nn_conv2d"));
@@ -284,6 +354,9 @@ __device__ __forceinline__ bool run_body(const KTask& t, int vb, unsigned char* 
     if (F == F_COPY) return body_copy(t, vb, smem, flag);
     if (F == F_DENSE) return body_dense(t, vb, smem, flag);
     if (F == F_SOFTMAX) return body_softmax(t, vb, smem, flag);
+    if (F == F_EMBEDDING) return body_embedding(t, vb, smem, flag);
+    if (F == F_LAYERNORM) return body_layernorm(t, vb, smem, flag);
+    if (F == F_ATTENTION) return body_attention(t, vb, smem, flag);
     return true;
 }
 
@@ -300,6 +373,9 @@ __device__ __forceinline__ bool run_any(const KTask& t, int vb, unsigned char* s
         case F_COPY: return run_body<F_COPY>(t, vb, smem, flag);
         case F_DENSE: return run_body<F_DENSE>(t, vb, smem, flag);
         case F_SOFTMAX: return run_body<F_SOFTMAX>(t, vb, smem, flag);
+        case F_EMBEDDING: return run_body<F_EMBEDDING>(t, vb, smem, flag);
+        case F_LAYERNORM: return run_body<F_LAYERNORM>(t, vb, smem, flag);
+        case F_ATTENTION: return run_body<F_ATTENTION>(t, vb, smem, flag);
         default: return true;
     }
 }
@@ -420,7 +496,7 @@ void add_launches(unsigned long long n) { g_launches += n; }
 
 #define FOR_EACH_FAMILY(X)                                                                      \
     X(F_MOCK_ADD) X(F_MOCK_MUL) X(F_FUSED_ADD_NCHW) X(F_BIAS_RELU) X(F_CONV_SIMT) X(F_MAX_POOL) \
-    X(F_AVG_POOL) X(F_GLOBAL_AVG_POOL) X(F_COPY) X(F_DENSE) X(F_SOFTMAX)
+    X(F_AVG_POOL) X(F_GLOBAL_AVG_POOL) X(F_COPY) X(F_DENSE) X(F_SOFTMAX) X(F_EMBEDDING) X(F_LAYERNORM) X(F_ATTENTION)
 
 static const void* plain_fn(int family) {
     switch (family) {

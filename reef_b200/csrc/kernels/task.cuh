@@ -29,13 +29,16 @@ enum Family : int {
     F_COPY,
     F_DENSE,
     F_SOFTMAX,
+    F_EMBEDDING,
+    F_LAYERNORM,
+    F_ATTENTION,
     F_COUNT,
     // families with their own __global__ kernel (not hosted by the 256-thread logical-block wrappers)
     F_CONV_TC = 100
 };
 
 // epilogue / option bits
-enum : int { EP_RES = 1, EP_BIAS = 2, EP_GB = 4, EP_RELU = 8 };
+enum : int { EP_RES = 1, EP_BIAS = 2, EP_GB = 4, EP_RELU = 8, EP_GELU = 16 };
 
 struct ConvP {
     int ci, hi, wi, co, kh, kw, sh, sw, ph, pw, ho, wo;

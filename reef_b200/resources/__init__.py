@@ -11,7 +11,10 @@ import os
 
 from .graph import Graph, kname, parse_kname, read_param_file, write_param_file  # noqa: F401
 from .mocked import build_mocked_kernel
+from .bert import build_bert
+from .densenet import build_densenet
 from .resnet import build_resnet
+from .vgg import build_vgg16
 
 DEFAULT_DIR = os.environ.get("REEF_RESOURCE_DIR", "/tmp/reef_b200_resources")
 
@@ -23,6 +26,13 @@ _BUILDERS = {
     # small variants for fast parity tests (same builders, 64x64 input like the reference's shipped resnet152)
     "resnet18_64": lambda **kw: build_resnet(18, name="resnet18_64", image=64, seed=1064, **kw),
     "resnet50_64": lambda **kw: build_resnet(50, name="resnet50_64", image=64, seed=5064, **kw),
+    "bert_base": lambda **kw: build_bert(**kw),
+    "bert_tiny": lambda **kw: build_bert(name="bert_tiny", layers=2, hidden=128, heads=2, ffn=256, vocab=1000, seq=48,
+                                         seed=5048, **kw),
+    "vgg16": lambda **kw: build_vgg16(**kw),
+    "vgg16_32": lambda **kw: build_vgg16(name="vgg16_32", image=32, fc=256, seed=4032, **kw),
+    "densenet201": lambda **kw: build_densenet(201, **kw),
+    "densenet121_64": lambda **kw: build_densenet(121, name="densenet121_64", image=64, seed=4064, **kw),
 }
 
 

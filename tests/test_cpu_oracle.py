@@ -105,3 +105,55 @@ def test_golden_resnet18_64(gen):
     logits = o.storage[j["kernels"][-1]["args"][0]]
     assert rel_err(logits, g["logits"]) < 1e-4
     assert rel_err(o.get_output(), g["probs"]) < 1e-4
+
+
+def test_oracle_bert_vs_torch(gen):
+    """BERT families (embedding, LayerNorm eps 1e-12, matmul+bias(+GELU)(+residual), attention) against an
+    independent float64 PyTorch encoder built from the same .param blobs."""
+    from reef_b200.resources.graph import read_param_file
+    base = gen("bert_tiny")
+    j = json.load(open(base + ".json"))
+    ids = np.random.default_rng(1).integers(0, 1000, 48).astype(np.int64)
+    o = oracle.OracleExecutor(base + ".json", base + ".param")
+    o.set_input("input0", ids)
+    o.execute()
+    P = read_param_file(base + ".param")
+    names = [s["name"] for s in j["storage"]]
+
+    def T(i):
+        return torch.from_numpy(P[names[i]].copy()).double()
+
+    it = iter(j["kernels"])
+    k = next(it)
+    x = T(k["args"][1]).reshape(1000, 128)[torch.from_numpy(ids)] + T(k["args"][3]).reshape(48, 128)
+
+    def ln(x, k):
+        return F.layer_norm(x, (128,), T(k["args"][2]), T(k["args"][3]), eps=1e-12)
+
+    x = ln(x, next(it))
+    for _ in range(2):
+        k = next(it)
+        qkv = x @ T(k["args"][1]).reshape(384, 128).T + T(k["args"][3])
+        next(it)
+        q, kk, v = [t.reshape(48, 2, 64).permute(1, 0, 2) for t in qkv.split(128, dim=1)]
+        ctx = (torch.softmax(q @ kk.transpose(1, 2) / 8.0, -1) @ v).permute(1, 0, 2).reshape(48, 128)
+        k = next(it)
+        a = ctx @ T(k["args"][1]).reshape(128, 128).T + T(k["args"][3]) + x
+        x1 = ln(a, next(it))
+        k = next(it)
+        h = x1 @ T(k["args"][1]).reshape(256, 128).T + T(k["args"][3])
+        h = h * (0.5 * torch.erf(h * 0.7071067811865476) + 0.5)
+        k = next(it)
+        x = ln(h @ T(k["args"][1]).reshape(128, 256).T + T(k["args"][3]) + x1, next(it))
+    assert rel_err(o.get_output(), x.reshape(-1).numpy()) < 1e-5
+
+
+@pytest.mark.parametrize("model,n", [("vgg16_32", 32), ("densenet121_64", 64)])
+def test_oracle_more_cnn_graphs_vs_torch(gen, model, n):
+    base = gen(model)
+    x = seeded_input(3 * n * n)
+    o = oracle.OracleExecutor(base + ".json", base + ".param")
+    o.set_input("data", x)
+    o.execute()
+    st, names = run_graph(base + ".json", base + ".param", {"data": x})
+    assert rel_err(o.get_output(), st[names.index("output")]) < 2e-5

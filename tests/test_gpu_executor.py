@@ -238,3 +238,47 @@ def test_profiler_writes_reference_schema(gen, tmp_path):
     # the executor accepts it
     e = capi.HybridExecutor(0)
     e.load_model_from_file(str(tmp_path / "m.json"), out)
+
+
+@pytest.mark.parametrize("model,inp,n", [("vgg16_32", "data", 3 * 32 * 32), ("densenet121_64", "data", 3 * 64 * 64),
+                                         ("bert_tiny", "input0", 48)])
+def test_more_models_layer_by_layer(gen, model, inp, n):
+    """VGG (conv+bias+ReLU, 2x2 max-pool, dense+ReLU), DenseNet (concat by channel offset, 2x2 avg-pool) and
+    BERT (embedding, LayerNorm, tensor-core matmul with bias/GELU/residual, attention), every buffer."""
+    base = gen(model)
+    j = json.load(open(base + ".json"))
+    x = seeded_input(n) if inp == "data" else np.random.default_rng(3).integers(0, 1000, n).astype(np.int64)
+    e = load_executor(base)
+    o = oracle.OracleExecutor(base + ".json", base + ".param")
+    e.set_input(inp, x)
+    o.set_input(inp, x)
+    e.execute()
+    o.execute()
+    tol = tol_for(base)
+    worst = compare_layers(e, o, j, lambda kname: tol)
+    print(model, "worst layer rel err", worst)
+    assert capi.device_error() == 0
+    raw = e.get_output()
+    for f in ("execute_graph", "execute_preemptable", "execute_dispatch"):
+        getattr(e, f)()
+        assert np.array_equal(e.get_output(), raw), f
+
+
+@pytest.mark.parametrize("model,inp", [("vgg16", "data"), ("densenet201", "data"), ("bert_base", "input0")])
+def test_more_models_full_size(gen, model, inp):
+    base = gen(model)
+    j = json.load(open(base + ".json"))
+    if inp == "data":
+        x = seeded_input(3 * 224 * 224, seed=12)
+    else:
+        x = np.random.default_rng(12).integers(0, 30522, 128).astype(np.int64)
+    e = load_executor(base)
+    o = oracle.OracleExecutor(base + ".json", base + ".param")
+    e.set_input(inp, x)
+    o.set_input(inp, x)
+    e.execute()
+    o.execute()
+    tol = tol_for(base)
+    err = rel_err(e.get_output(), o.get_output())
+    print(model, "output rel err", err, "tol", tol, "graph ms", e.time(1, 3, 10))
+    assert capi.device_error() == 0 and err < tol
