@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
             const uint32_t st = base + s * stage_bytes;
             const int kb = kb_begin + i;
             // tap and channel block of this K block; the per-tap sub-lattice and offsets come from a host table
-            const int tap = (int)__umulhi((unsigned)kb, P.cb_magic), cb = kb - tap * P.cblocks;
+            const int tap = P.cblocks == 1 ? kb : (int)__umulhi((unsigned)kb, P.cb_magic), cb = kb - tap * P.cblocks;   // 2^32/1 does not fit the magic
             if (P.spatial) {
                 tma_load_3d(st + TC_A_BYTES, &P.tm_x[P.tap_map[tap]], bar_full + 8 * s, cb * TC_BK, P.tap_qx[tap],
                             tile_n * P.rows + P.tap_qy[tap]);

@@ -13,6 +13,7 @@ from .graph import Graph, kname, parse_kname, read_param_file, write_param_file 
 from .mocked import build_mocked_kernel
 from .bert import build_bert
 from .densenet import build_densenet
+from .inception import build_inception_v3
 from .resnet import build_resnet
 from .vgg import build_vgg16
 
@@ -29,6 +30,8 @@ _BUILDERS = {
     "bert_base": lambda **kw: build_bert(**kw),
     "bert_tiny": lambda **kw: build_bert(name="bert_tiny", layers=2, hidden=128, heads=2, ffn=256, vocab=1000, seq=48,
                                          seed=5048, **kw),
+    "inception_v3": lambda **kw: build_inception_v3(**kw),
+    "inception_v3_139": lambda **kw: build_inception_v3(name="inception_v3_139", image=139, seed=4139, **kw),
     "vgg16": lambda **kw: build_vgg16(**kw),
     "vgg16_32": lambda **kw: build_vgg16(name="vgg16_32", image=32, fc=256, seed=4032, **kw),
     "densenet201": lambda **kw: build_densenet(201, **kw),

@@ -148,7 +148,7 @@ def test_oracle_bert_vs_torch(gen):
     assert rel_err(o.get_output(), x.reshape(-1).numpy()) < 1e-5
 
 
-@pytest.mark.parametrize("model,n", [("vgg16_32", 32), ("densenet121_64", 64)])
+@pytest.mark.parametrize("model,n", [("vgg16_32", 32), ("densenet121_64", 64), ("inception_v3_139", 139)])
 def test_oracle_more_cnn_graphs_vs_torch(gen, model, n):
     base = gen(model)
     x = seeded_input(3 * n * n)

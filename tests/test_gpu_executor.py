@@ -83,6 +83,7 @@ TC_CASES = [
     ("fused_nn_conv2d_nn_relu", 96, 17, 17, 160, 1, 7, 1, 0, 3),
     ("fused_nn_conv2d_add_nn_relu", 160, 9, 13, 72, 5, 5, 1, 2, 2),
     ("fused_nn_conv2d_add_nn_relu", 64, 15, 15, 96, 3, 3, 2, 0, 0),
+    ("fused_nn_conv2d_add_nn_relu", 32, 69, 69, 32, 3, 3, 1, 0, 0),      # one channel block per tap, prime output width
 ]
 
 
@@ -241,7 +242,7 @@ def test_profiler_writes_reference_schema(gen, tmp_path):
 
 
 @pytest.mark.parametrize("model,inp,n", [("vgg16_32", "data", 3 * 32 * 32), ("densenet121_64", "data", 3 * 64 * 64),
-                                         ("bert_tiny", "input0", 48)])
+                                         ("inception_v3_139", "data", 3 * 139 * 139), ("bert_tiny", "input0", 48)])
 def test_more_models_layer_by_layer(gen, model, inp, n):
     """VGG (conv+bias+ReLU, 2x2 max-pool, dense+ReLU), DenseNet (concat by channel offset, 2x2 avg-pool) and
     BERT (embedding, LayerNorm, tensor-core matmul with bias/GELU/residual, attention), every buffer."""
@@ -264,12 +265,13 @@ def test_more_models_layer_by_layer(gen, model, inp, n):
         assert np.array_equal(e.get_output(), raw), f
 
 
-@pytest.mark.parametrize("model,inp", [("vgg16", "data"), ("densenet201", "data"), ("bert_base", "input0")])
+@pytest.mark.parametrize("model,inp", [("vgg16", "data"), ("densenet201", "data"), ("inception_v3", "data"),
+                                       ("bert_base", "input0")])
 def test_more_models_full_size(gen, model, inp):
     base = gen(model)
     j = json.load(open(base + ".json"))
     if inp == "data":
-        x = seeded_input(3 * 224 * 224, seed=12)
+        x = seeded_input(j["storage"][0]["size"], seed=12)
     else:
         x = np.random.default_rng(12).integers(0, 30522, 128).astype(np.int64)
     e = load_executor(base)
