@@ -30,11 +30,29 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-METRIC = "resnet152_b1_inferences_per_s_rt_plus_4be"
 UNIT = "inf/s"
-WORKLOAD = "configs[2]: ResNet-152 b1 RT client back-to-back + 4 BE ResNet-152 b1 closed-loop clients, REEF mode"
-MODEL = "resnet152"
-N_BE = 4
+# BASELINE.json configs; "c2" is the configuration the headline metric is quoted on and the default
+WORKLOADS = {
+    "c2": dict(metric="resnet152_b1_inferences_per_s_rt_plus_4be", rt="resnet152", be=["resnet152"] * 4,
+               desc="configs[2]: ResNet-152 b1 RT client back-to-back + 4 BE ResNet-152 b1 closed-loop clients, REEF mode"),
+    "c3": dict(metric="inception_v3_b1_inferences_per_s_rt_plus_vgg16_densenet201_be", rt="inception_v3",
+               be=["vgg16", "densenet201"],
+               desc="configs[3]: RT Inception-v3 b1 (299x299) + BE VGG-16 b1 + BE DenseNet-201 b1, REEF mode (kernel padding mix)"),
+    "c4": dict(metric="bert_base_s128_inferences_per_s_rt_plus_4be_resnet50", rt="bert_base", be=["resnet50"] * 4,
+               desc="configs[4]: RT BERT-base b1 seq 128 + 4 BE ResNet-50 b1 per GPU, REEF mode"),
+}
+METRIC = WORKLOADS["c2"]["metric"]
+WORKLOAD = WORKLOADS["c2"]["desc"]
+MODEL = WORKLOADS["c2"]["rt"]
+
+
+def model_input(base, seed):
+    """(input storage name, seeded synthetic input) of the model at `base`: images ~ N(0,1), token ids uniform."""
+    st = json.load(open(base + ".json"))["storage"][0]
+    rng = np.random.default_rng(seed)
+    if st["stype"] == "int64":
+        return st["name"], rng.integers(0, 30522, st["size"]).astype(np.int64)
+    return st["name"], rng.normal(0, 1, st["size"]).astype(np.float32)
 
 
 def measured_peaks():
@@ -146,7 +164,10 @@ def main():
     ap.add_argument("--be-cap", type=int, default=int(os.environ.get("REEF_BE_CAP", "4")))
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--profile-out", default="")
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    n_be = len(wl["be"])
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -175,31 +196,36 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    models = sorted(set([wl["rt"]] + wl["be"]))
     if rank == 0:
-        d = resources.generate(MODEL)
-        # latency tables for the padding policy, measured on this GPU (the reference ships them per model)
         from reef_b200 import profiler
-        profiler.profile_model(os.path.join(d, MODEL), iters=10, device=local_rank)
+        for m in models:
+            d = resources.generate(m)
+            # latency tables for the padding policy, measured on this GPU (the reference ships them per model)
+            profiler.profile_model(os.path.join(d, m), iters=10, device=local_rank)
     barrier()
-    d = resources.generate(MODEL)
-    base = os.path.join(d, MODEL)
+    bases = {m: os.path.join(resources.generate(m), m) for m in models}
+    inputs = {m: model_input(bases[m], 2001 + rank) for m in models}
+    base = bases[wl["rt"]]
+    in_name, x = inputs[wl["rt"]]
     S = capi.REEFScheduler
-    x = np.random.default_rng(2001 + rank).normal(0, 1, 3 * 224 * 224).astype(np.float32)
 
-    def make_sched(n_be, rt=True):
+    def load(s, m, qtype):
+        b = bases[m]
+        mid = s.load_model_files(b + ".json", b + ".profile.json", b + ".param")
+        s.bind_model_queue(s.create_queue(qtype), mid)
+        s.set_input(mid, inputs[m][1], inputs[m][0])
+        return mid
+
+    def make_sched(n_be_clients, rt=True):
         s = S(S.REEF, local_rank)
         s.set_be_stream_cap(args.be_cap)
         s.run()
-        ids = {"rt": None, "be": []}
+        ids = {"rt": None, "be": [], "be_models": wl["be"][:n_be_clients]}
         if rt:
-            ids["rt"] = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
-            s.bind_model_queue(s.create_queue(S.RealTimeQueue), ids["rt"])
-            s.set_input(ids["rt"], x)
-        for _ in range(n_be):
-            m = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
-            s.bind_model_queue(s.create_queue(S.BestEffortQueue), m)
-            s.set_input(m, x)
-            ids["be"].append(m)
+            ids["rt"] = load(s, wl["rt"], S.RealTimeQueue)
+        for m in wl["be"][:n_be_clients]:
+            ids["be"].append(load(s, m, S.BestEffortQueue))
         return s, ids
 
     extra = {}
@@ -212,7 +238,7 @@ def main():
     s.shutdown(); s.close()
 
     # ---- phase B: BE alone ---------------------------------------------------------------------
-    s, ids = make_sched(N_BE, rt=False)
+    s, ids = make_sched(n_be, rt=False)
     be_req = max(20, args.steps // 8)
     rs = s.run_clients([dict(mid=m, max_requests=be_req, warmup=max(3, args.warmup // 8), want_output=False)
                         for m in ids["be"]])
@@ -220,7 +246,7 @@ def main():
     s.shutdown(); s.close()
 
     # ---- phase C (timed region of `value`): RT + 4 BE, inputs resident in HBM --------------------
-    s, ids = make_sched(N_BE)
+    s, ids = make_sched(n_be)
     clients = [dict(mid=ids["rt"], max_requests=args.steps, warmup=args.warmup, want_output=False)] + \
               [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
     sampler = ClockSampler(local_rank)
@@ -251,7 +277,7 @@ def main():
     s.shutdown(); s.close()
 
     # ---- phase D: preemption latency with drain (flag set -> BE streams idle -> counters read) ----
-    s, ids = make_sched(N_BE)
+    s, ids = make_sched(n_be)
     s.set_wait_sync(True)
     clients = [dict(mid=ids["rt"], max_requests=max(50, args.steps // 10), warmup=5, want_output=False, think_us=2000)] + \
               [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
@@ -263,22 +289,23 @@ def main():
     s.shutdown(); s.close()
 
     # ---- phase E (e2e): same workload through the request calls with pinned host buffers ---------
-    s, ids = make_sched(N_BE)
+    s, ids = make_sched(n_be)
     in_bytes = x.nbytes
     pins = []
     clients = []
-    for i, m in enumerate([ids["rt"]] + ids["be"]):
-        pin = pinned_array(capi, in_bytes)
-        pin[:] = x
+    for i, (mid, mname) in enumerate(zip([ids["rt"]] + ids["be"], [wl["rt"]] + ids["be_models"])):
+        nm, arr = inputs[mname]
+        pin = pinned_array(capi, arr.nbytes, arr.dtype)
+        pin[:] = arr
         pins.append(pin)
-        clients.append(dict(mid=m, max_requests=args.steps if i == 0 else 0, warmup=args.warmup if i == 0 else 0,
-                            input=pin, want_output=True))
+        clients.append(dict(mid=mid, max_requests=args.steps if i == 0 else 0, warmup=args.warmup if i == 0 else 0,
+                            input=pin, input_name=nm, want_output=True))
     barrier()
     rs = s.run_clients(clients)
     barrier()
     e2e_region = rs[0]["elapsed_s"]
     e2e_total = rs[0]["completed"] / e2e_region + sum(r["completed"] / r["elapsed_s"] for r in rs[1:] if r["elapsed_s"] > 0)
-    out_bytes = 4000
+    out_bytes = int(rs[0]["output"].nbytes)
     extra["e2e_rt_p50_ms"] = pct(rs[0]["latencies_ms"], 50)
     extra["e2e_rt_p99_ms"] = pct(rs[0]["latencies_ms"], 99)
     s.shutdown(); s.close()
@@ -287,7 +314,7 @@ def main():
     e = capi.HybridExecutor(local_rank)
     e.load_model_from_file(base + ".json", base + ".profile.json")
     e.load_param_from_file(base + ".param")
-    e.set_input("data", x)
+    e.set_input(in_name, x)
     prof = e.profile_kernels(20)
     names = [k["name"] for k in json.load(open(base + ".json"))["kernels"]]
     conv = [(n, p) for n, p in zip(names, prof) if p["tensor_core"]]   # reef_conv_tc_kernel launches
@@ -299,12 +326,12 @@ def main():
     achieved = conv_bytes / (conv_us * 1e-6) / 1e9
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "conv_traffic.json")
-    if os.path.exists(tpath):
+    if os.path.exists(tpath) and args.workload == "c2":
         traffic = json.load(open(tpath)).get("traffic_bytes_per_launch")
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "peak_kind": peak_kind,
-                "kernel": "reef_conv_tc_kernel (tcgen05 TF32 convolution: %d launches of one ResNet-152 pass, "
-                          "timed in context with CUDA events between the kernels of whole passes)" % len(conv),
+                "kernel": "reef_conv_tc_kernel (tcgen05 TF32 convolution/matmul: %d launches of one %s pass, "
+                          "timed in context with CUDA events between the kernels of whole passes)" % (len(conv), wl["rt"]),
                 "algorithmic_bytes_per_pass": conv_bytes, "avg_launch_us": conv_us / max(1, len(conv)),
                 "conv_tflops": conv_flops / (conv_us * 1e-6) / 1e12, "conv_share_of_kernel_time": conv_us / all_us,
                 "model_kernel_time_us": all_us}
@@ -335,7 +362,7 @@ def main():
         from oracle import oracle
         oracle.set_threads(os.cpu_count() or 1)
         o = oracle.OracleExecutor(base + ".json", base + ".param")
-        o.set_input("data", x)
+        o.set_input(in_name, x)
         o.execute()
         n_cpu = 0
         t0 = time.perf_counter()
@@ -344,14 +371,15 @@ def main():
             n_cpu += 1
         dt = time.perf_counter() - t0
         cpu = {"value": n_cpu / dt, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
-               "sample": f"{n_cpu} sequential ResNet-152 b1 inferences of the same schedule (plain-C oracle, OpenMP)"}
+               "sample": f"{n_cpu} sequential {wl['rt']} b1 inferences of the same schedule (plain-C oracle, OpenMP)"}
 
     if rank == 0:
-        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        line = {"metric": wl["metric"], "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": WORKLOAD, "inputs": "1x3x224x224 N(0,1)", "clients": "1 RT + 4 BE per GPU",
-                           "l2": "weights of one pass (240 MB per model, 5 replicas) exceed the 126 MB L2"},
+                "config": {"workload": wl["desc"], "inputs": "seeded synthetic: images N(0,1), token ids uniform",
+                           "clients": "1 RT + %d BE per GPU" % n_be,
+                           "l2": "every client owns a weight replica; the replicas streamed per pass exceed the 126 MB L2"},
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
                 "rt_be": extra}
