@@ -86,8 +86,12 @@ reef_status reef_free(reef_dptr_t ptr) {
     CK(cudaFree((void*)ptr));
     return REEF_SUCC;
 }
+// The synchronous forms return only when the bytes are in device memory.  cudaMemset and a cudaMemcpy from
+// pageable host memory may return while the device-side write is still in flight on the legacy stream, and
+// the executors launch on non-blocking streams, which the legacy stream does not order.
 reef_status reef_memset(reef_dptr_t ptr, int value, size_t bytes) {
     CK(cudaMemset((void*)ptr, value, bytes));
+    CK(cudaStreamSynchronize(cudaStreamLegacy));
     return REEF_SUCC;
 }
 reef_status reef_memset_async(reef_dptr_t ptr, int value, size_t bytes, reef_stream_t s) {
@@ -96,6 +100,7 @@ reef_status reef_memset_async(reef_dptr_t ptr, int value, size_t bytes, reef_str
 }
 reef_status reef_memcpy_h2d(reef_dptr_t dst, const void* src, size_t bytes) {
     CK(cudaMemcpy((void*)dst, src, bytes, cudaMemcpyHostToDevice));
+    CK(cudaStreamSynchronize(cudaStreamLegacy));
     return REEF_SUCC;
 }
 reef_status reef_memcpy_d2h(void* dst, reef_dptr_t src, size_t bytes) {
