@@ -270,13 +270,29 @@ def main():
     st = s.stats()
     extra.update({"rt_p50_ms": pct(rt_r["latencies_ms"], 50), "rt_p99_ms": pct(rt_r["latencies_ms"], 99),
                   "be_inf_s": be_inf_s, "rt_inf_s": rt_r["completed"] / region_s,
-                  "preempt_avg_us": st["preempt_ns_sum"] / max(1, st["preempt_count"]) / 1e3,
-                  "preempt_max_us": st["preempt_ns_max"] / 1e3, "preempt_count": st["preempt_count"],
+                  "preempt_count_back_to_back": st["preempt_count"],
                   "padded_kernels": st["padded_kernels"], "be_tasks_padded_to_finish": st["be_tasks_padded_to_finish"],
                   "device_event_ms_incl_warmup": ev0.elapsed_time(ev1), "be_stream_cap": args.be_cap})
     s.shutdown(); s.close()
 
-    # ---- phase D: preemption latency with drain (flag set -> BE streams idle -> counters read) ----
+    # ---- phase D1: reset-based preemption.  The RT client pauses 2 ms between requests, so the BE clients run
+    # at full speed on their own streams and every RT arrival preempts them (under a back-to-back RT client the
+    # BE tasks only advance as padding and there is nothing to preempt).  Latency = flag raised + tasks rolled
+    # back, as the scheduler measures it (reference: scheduler.cpp:305-346).
+    s, ids = make_sched(n_be)
+    clients = [dict(mid=ids["rt"], max_requests=max(100, args.steps // 3), warmup=5, want_output=False, think_us=2000)] + \
+              [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
+    rs = s.run_clients(clients)
+    st = s.stats()
+    extra["preempt_avg_us"] = st["preempt_ns_sum"] / max(1, st["preempt_count"]) / 1e3
+    extra["preempt_max_us"] = st["preempt_ns_max"] / 1e3
+    extra["preempt_count"] = st["preempt_count"]
+    extra["rt_after_preempt_p50_ms"] = pct(rs[0]["latencies_ms"], 50)
+    extra["rt_after_preempt_p99_ms"] = pct(rs[0]["latencies_ms"], 99)
+    extra["be_inf_s_rt_every_2ms"] = sum(r["completed"] / r["elapsed_s"] for r in rs[1:] if r["elapsed_s"] > 0)
+    s.shutdown(); s.close()
+
+    # ---- phase D2: preemption latency with drain (flag set -> BE streams idle -> counters read) ----
     s, ids = make_sched(n_be)
     s.set_wait_sync(True)
     clients = [dict(mid=ids["rt"], max_requests=max(50, args.steps // 10), warmup=5, want_output=False, think_us=2000)] + \

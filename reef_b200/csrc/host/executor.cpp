@@ -225,6 +225,7 @@ HybridExecutor::HybridExecutor() {}
 
 HybridExecutor::~HybridExecutor() {
     if (graph) reef_graph_destroy(graph);
+    for (auto g : pad_segments) reef_graph_destroy(g);
     if (own_flag && preempt_flag) reef_free(preempt_flag);
     if (task_slot_base) reef_free(task_slot_base);
     if (dispatch_ctrl) reef_free(dispatch_ctrl);
@@ -340,6 +341,45 @@ Status HybridExecutor::launch_pad_piece(int idx, int block_offset, int block_num
                            task_slot_base + (size_t)idx * 4, dispatch_ctrl, dispatch_ctrl, stream, stream);
     if (rc != REEF_SUCC) err_ = reef_last_error();
     GPU_RETURN_STATUS(rc);
+    return Status::Succ;
+}
+
+Status HybridExecutor::build_pad_segments() {
+    if (!pad_segments.empty()) return Status::Succ;
+    GPUStream_t cap = nullptr;
+    GPU_RETURN_STATUS(reef_stream_create(&cap, 0));
+    const int n = (int)num_kernels();
+    Status st = Status::Succ;
+    for (int k0 = 0; k0 < n && st == Status::Succ; k0 += kPadSegment) {
+        if (reef_graph_begin(cap) != REEF_SUCC) {
+            st = Status::Fail;
+            break;
+        }
+        for (int k = k0; k < std::min(n, k0 + kPadSegment) && st == Status::Succ; k++) {
+            const KernelArg& a = trans_args[k];
+            const int occ = a.resource.tensor_core ? 1 : std::max(1, std::min(2, a.resource.max_blocks_per_sm));
+            st = launch_pad_piece(k, 0, a.block_num, occ, cap);
+        }
+        reef_graph_t g = nullptr;
+        int rc = reef_graph_end(cap, &g);
+        if (rc != REEF_SUCC) {
+            err_ = reef_last_error();
+            st = Status::Fail;
+        }
+        if (st == Status::Succ) pad_segments.push_back(g);
+        else if (g) reef_graph_destroy(g);
+    }
+    reef_stream_destroy(cap);
+    if (st != Status::Succ) {
+        for (auto g : pad_segments) reef_graph_destroy(g);
+        pad_segments.clear();
+    }
+    return st;
+}
+
+Status HybridExecutor::launch_pad_segment(int seg, GPUStream_t stream) {
+    if (seg < 0 || seg >= (int)pad_segments.size()) RETURN_STATUS(Status::OutOfRange);
+    GPU_RETURN_STATUS(reef_graph_launch(pad_segments[seg], stream));
     return Status::Succ;
 }
 

@@ -116,6 +116,13 @@ public:
                            int sm_partition, int occupancy, GPUStream_t stream, GPUStream_t be_stream = nullptr);
     // best-effort logical blocks [offset, offset+num) of kernel idx alone, non-preemptible, counted into the task slot
     Status launch_pad_piece(int idx, int block_offset, int block_num, int occupancy, GPUStream_t stream);
+    // Padding segments: the kernel list cut into runs of kPadSegment kernels, each run captured once as a CUDA
+    // graph of whole-kernel pieces (one launch and one completion event for the run; inside it the kernels keep
+    // their programmatic dependencies).  Segment g covers kernels [g*kPadSegment, (g+1)*kPadSegment).
+    static const int kPadSegment = 4;
+    Status build_pad_segments();
+    bool has_pad_segments() const { return !pad_segments.empty(); }
+    Status launch_pad_segment(int seg, GPUStream_t stream);
     bool has_tensor_core_kernels() const { return has_tc; }
     // CUDA graph of the whole kernel list on `stream` (captured lazily on first use)
     Status execute_graph(GPUStream_t stream);
@@ -148,6 +155,7 @@ protected:
     bool has_tc = false;
     std::shared_ptr<ModelProfile> model_profile;
     reef_graph_t graph = nullptr;
+    std::vector<reef_graph_t> pad_segments;
     GPUStream_t graph_stream = nullptr;
 };
 

@@ -47,26 +47,43 @@ REEFScheduler::REEFScheduler(ScheduleMode _mode, int _device)
         num_sms = 0;   // run()/load_model() refuse to work
     }
     be_stream_device_queue_cap = mode == WaitPreempt ? 1024 : 2;
-    for (auto& pp : pad_pieces) reef_event_create(&pp.ev);
-    if (const char* v = getenv("REEF_PAD_INFLIGHT")) set_pad_limits(atoi(v), pad_overcommit_sms);
-    if (const char* v = getenv("REEF_PAD_OVERCOMMIT")) set_pad_limits(pad_inflight_max, atoi(v));
+    if (const char* v = getenv("REEF_PAD_DEPTH")) set_pad_limits(atoi(v), pad_overcommit, pad_quantum);
+    if (const char* v = getenv("REEF_PAD_OVERCOMMIT")) set_pad_limits(pad_depth, atoi(v), pad_quantum);
+    if (const char* v = getenv("REEF_PAD_QUANTUM")) set_pad_limits(pad_depth, pad_overcommit, atoi(v));
     if (const char* v = getenv("REEF_PAD_WINDOW")) set_pad_window(atoi(v));
+    if (const char* v = getenv("REEF_RT_GRACE_US")) set_rt_grace_us(atoi(v));
+    if (const char* v = getenv("REEF_PAD_TARGET")) set_pad_slowdown_target(atof(v));
 }
 
 REEFScheduler::~REEFScheduler() {
     if (scheduler && scheduler->joinable()) shutdown();
+    if (getenv("REEF_PAD_TRACE") && pad_trace.calls) {
+        const PadTrace& t = pad_trace;
+        fprintf(stderr,
+                "[reef] timeline padding: %llu windows avg %.1f us (graph launch %.1f us), per window: %.1f iterations, "
+                "%.1f pieces (launch %.2f us, turnaround %.1f us), skipped: no slot %.1f, no SMs %.1f, no queue %.1f, tail %.1f\n",
+                (unsigned long long)t.calls, t.window_ns / 1e3 / t.calls, t.graph_launch_ns / 1e3 / t.calls,
+                (double)t.iters / t.calls, (double)t.launched / t.calls, t.launched ? t.launch_ns / 1e3 / t.launched : 0.0,
+                t.retired ? t.turnaround_ns / 1e3 / t.retired : 0.0, (double)t.no_slot / t.calls, (double)t.no_sms / t.calls,
+                (double)t.no_queue / t.calls, (double)t.tail / t.calls);
+        fprintf(stderr, "[reef]   per window: segments %.1f, single pieces %.1f; queue visits skipped: empty %.1f, draining %.1f, "
+                "depth full %.1f, fully issued %.1f, no fit %.1f\n", (double)t.segments / t.calls, (double)t.singles / t.calls,
+                (double)t.q_empty / t.calls, (double)t.q_draining / t.calls, (double)t.q_full / t.calls,
+                (double)t.q_issued / t.calls, (double)t.q_nofit / t.calls);
+        fprintf(stderr, "[reef]   slowdown controller: target %.3f, smoothed ratio %.3f, rate %.1f kernels per window\n", pad_target,
+                pad_ratio_ema, pad_rate);
+    }
     reef_gpu_init(device);
     reef_device_sync();
     model_pool.clear();
     for (auto& q : be_queues)
         if (q) {
             for (auto& f : q->inflight) reef_event_destroy(f.ev);
+            for (auto& po : q->pad_out) reef_event_destroy(po.ev);
             for (auto e : q->free_events) reef_event_destroy(e);
             if (q->stream) reef_stream_destroy(q->stream);
         }
     if (rt_queue && rt_queue->stream) reef_stream_destroy(rt_queue->stream);
-    for (auto& pp : pad_pieces)
-        if (pp.ev) reef_event_destroy(pp.ev);
     if (preempt_stream) reef_stream_destroy(preempt_stream);
     if (preempt_flag) reef_free(preempt_flag);
 }
@@ -146,6 +163,15 @@ Status REEFScheduler::bind_model_queue(const QueueID& qid, const ModelID& mid) {
     if (model_pool_size.load() <= mid) return Status::OutOfRange;
     if (be_queue_cnt.load() <= qid && qid != rt_queue_id) return Status::OutOfRange;
     model_pool[mid]->qid = qid;
+    if (mode == ScheduleMode::REEF && qid != rt_queue_id) {
+        // best-effort model under dynamic kernel padding: capture its padding segments now, not inside a
+        // real-time window
+        reef_gpu_init(device);
+        if (model_pool[mid]->executor.build_pad_segments() != Status::Succ) {
+            err_ = "padding segments: " + model_pool[mid]->executor.error();
+            return Status::Fail;
+        }
+    }
     return Status::Succ;
 }
 
@@ -289,10 +315,21 @@ void REEFScheduler::finish_task(std::shared_ptr<Task>& t) {
 void REEFScheduler::loop_body() {
     for (;;) {
         while (!rt_queue->task_queue.empty()) {
-            preempt_be_tasks();
             auto rt_task = rt_queue->task_queue.front();
             rt_queue->task_queue.pop();
-            execute_rt_task(rt_task);
+            execute_rt_task(rt_task);   // preempts the best-effort tasks first (or right after its graph launch)
+            last_rt_finish = sclock::now();
+            rt_recent = true;
+        }
+        // A closed-loop real-time client submits its next request a few microseconds after the previous one
+        // completes.  Best-effort work started in that gap would be preempted at once, and every launch made
+        // for it delays the moment the new request is seen, so the queue is polled for a short grace period
+        // before best-effort work is resumed.
+        if (rt_recent && rt_grace_us > 0) {
+            while (rt_queue->task_queue.empty() && ns_since(last_rt_finish) < (uint64_t)rt_grace_us * 1000ull && !_shutdown.load()) {
+            }
+            if (!rt_queue->task_queue.empty()) continue;
+            rt_recent = false;
         }
         bool interrupted = false;
         uint32_t nq = be_queue_cnt.load();
@@ -456,16 +493,27 @@ void REEFScheduler::execute_rt_task(std::shared_ptr<Task>& task) {
     task->state.store(TaskState::Executing);
     task->start = std::chrono::system_clock::now();
     auto& exe = task->model->executor;
+    if (mode == ScheduleMode::REEF && any_be_waiting() && side_padding_needed(exe)) {
+        // the graph goes out first; the best-effort streams are preempted while it starts up
+        timeline_padding(task);
+        reef_stream_sync(rt_queue->stream);
+        task->end = std::chrono::system_clock::now();
+        n_rt_tasks++;
+        finish_task(task);
+        return;
+    }
+    preempt_be_tasks();
     if (mode == ScheduleMode::REEF && any_be_waiting()) {
-        if (side_padding_needed(exe)) timeline_padding(task);
-        else dynamic_kernel_padding(task);
+        dynamic_kernel_padding(task);
         reef_stream_sync(rt_queue->stream);
     } else if (rt_graph) {
+        auto t0 = sclock::now();
         if (exe.execute_graph(rt_queue->stream) != Status::Succ) {
             err_ = "real-time graph launch failed: " + exe.error();
             fprintf(stderr, "[reef] %s\n", err_.c_str());
         }
         reef_stream_sync(rt_queue->stream);
+        task->model->add_alone_sample((double)ns_since(t0));
     } else {
         exe.execute(rt_queue->stream);
     }
@@ -525,25 +573,38 @@ bool REEFScheduler::side_padding_needed(HybridExecutor& rt_exe) {
 
 // Dynamic kernel padding when a tensor-core (cluster) kernel is involved on either side.  Such kernels are
 // not hosted by the logical-block dispatcher, so the padding is done in space and time by separate launches:
-//  * the real-time task replays its CUDA graph on the high-priority stream (full speed, no per-kernel host work);
-//  * while it runs, this thread issues best-effort PIECES — block ranges of the head kernel of a best-effort
-//    queue, round-robin over the queues — on that queue's own low-priority stream, one piece in flight at a time;
-//  * a piece is sized from the SMs the real-time kernels of the next `pad_window` positions leave free
-//    (position = elapsed time mapped onto the measured latency profile, reference policy scheduler.cpp:566-595
-//    restated for a free-running real-time stream), whole clusters only.
+//  * the real-time task replays its CUDA graph on the high-priority stream (full speed, no per-kernel host
+//    work).  Its kernels release their successor only after their own dependency wait, so at most two grids
+//    of the chain are resident: the running one and the prologue of the next;
+//  * while it runs, this thread issues best-effort PIECES (block ranges of a queue's head kernel, whole
+//    kernels where they fit) on that queue's own low-priority stream, up to `pad_depth` per stream so that the
+//    stream never idles for a launch round trip.  Pieces of one stream run one after the other;
+//  * space is accounted in SM slots (two tensor-core CTAs fit one SM): the streams with pieces out may
+//    together occupy what the real-time kernels of the next `pad_window` positions leave free (position =
+//    elapsed time mapped onto the measured latency profile; reference policy scheduler.cpp:566-595 restated
+//    for a free-running real-time stream);
+//  * a queue that has issued `pad_quantum` pieces drains and yields, so every best-effort client advances.
 // Pieces are launched in the plain flavour (they do not poll the preempt flag; they are short and sized to the
-// idle SMs) and count into the task's completion slots.
+// free slots) and count into the task's completion slots.
+static int64_t abs_ns() {
+    return std::chrono::duration_cast<std::chrono::nanoseconds>(sclock::now().time_since_epoch()).count();
+}
+static int slots_of(const HybridExecutor::KernelArg& a, int blocks) {
+    // a slot is half an SM: one tensor-core CTA, or four 256-thread logical blocks
+    return a.resource.tensor_core ? blocks : (blocks + 3) / 4;
+}
+
 void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
     auto& rt_exe = rt_task->model->executor;
     const size_t n_rt = rt_exe.num_kernels();
     const uint32_t nq = be_queue_cnt.load();
-    // cumulative profile time and SM footprint per real-time kernel
+    const int total_slots = 2 * num_sms;
+    // cumulative profile time and slot footprint per real-time kernel (kernel k running + prologue of k+1)
     std::vector<double> cum(n_rt + 1, 0.0);
-    std::vector<int> part(n_rt, 0);
+    std::vector<int> part(n_rt + 1, 0);
     for (size_t k = 0; k < n_rt; k++) {
         const HybridExecutor::KernelArg& a = rt_exe.trans_args[k];
-        const int layers = std::max(1, align_up<int>(a.block_num, num_sms) / num_sms);
-        part[k] = std::min(num_sms, align_up(a.block_num, layers) / layers);
+        part[k] = std::min(total_slots, slots_of(a, a.block_num));
         cum[k + 1] = cum[k] + std::max(1, a.profile.total_latency);
     }
     const double unit = rt_exe.profile() ? rt_exe.profile()->latency_unit_ns : 1000;
@@ -557,68 +618,184 @@ void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
         fprintf(stderr, "[reef] %s\n", err_.c_str());
         return;
     }
+    pad_trace.calls++;
+    pad_trace.graph_launch_ns += ns_since(t0);
+    preempt_be_tasks();   // flag up, tasks rolled back to what is known complete; pieces below are not preemptible
+    Model& rt_model = *rt_task->model;
+    // Probe windows refresh the baseline: two unpadded windows in a row (the first lets the pieces still out
+    // drain, the second is measured), early on and then once per kPadProbePeriod windows.
+    const uint32_t wi = rt_model.pad_windows++;
+    const uint32_t phase = wi < 16 ? wi % 8 : wi % kPadProbePeriod;
+    const bool drain_only = pad_target > 0 && phase == 6;
+    const bool probe = pad_target > 0 && phase == 7;
     size_t pos = 0;
+    int issued = 0;       // best-effort kernels issued in this window (rate limit)
     for (;;) {
         int busy = 0;
         if (reef_stream_query(rt_queue->stream, &busy) != REEF_SUCC || !busy) break;
-        // retire finished pieces; count what is still out
-        int inflight = 0, sms_out = 0, slot = -1;
-        uint32_t busy_queues = 0;
-        for (int p = 0; p < pad_inflight_max; p++) {
-            PadPiece& pp = pad_pieces[p];
-            if (pp.pending) {
+        pad_trace.iters++;
+        // retire finished pieces; slots still claimed = per stream the widest piece it has out
+        int slots_out = 0, active = 0;
+        for (uint32_t i = 0; i < nq; i++) {
+            auto& q = *be_queues[i];
+            while (!q.pad_out.empty()) {
                 int pending = 1;
-                if (reef_event_query(pp.ev, &pending) == REEF_SUCC && !pending) pp.pending = false;
+                if (reef_event_query(q.pad_out.front().ev, &pending) != REEF_SUCC || pending) break;
+                pad_trace.retired++;
+                pad_trace.turnaround_ns += abs_ns() - q.pad_out.front().t_launch;
+                q.free_events.push_back(q.pad_out.front().ev);
+                q.pad_out.pop_front();
             }
-            if (pp.pending) {
-                inflight++;
-                sms_out += pp.sms;
-                busy_queues |= 1u << pp.queue;
-            } else if (slot < 0) {
-                slot = p;
+            if (q.pad_out.empty()) {
+                q.pad_draining = false;
+                continue;
             }
+            int widest = 0;
+            for (auto& po : q.pad_out) widest = std::max(widest, po.slots);
+            slots_out += widest;
+            active++;
         }
-        if (slot < 0) continue;
         // estimated position of the real-time stream
         const double now_ns = (double)ns_since(t0);
         while (pos < n_rt && cum[pos + 1] * scale <= now_ns) pos++;
-        if (pos >= n_rt) continue;   // in the tail: let the task finish
-        int part_w = 0;
-        for (size_t k = pos; k < std::min(n_rt, pos + (size_t)pad_window); k++) part_w = std::max(part_w, part[k]);
-        const int free_sms = num_sms - part_w + pad_overcommit_sms - sms_out;
-        if (free_sms <= 0) continue;
+        if (pos >= n_rt) pos = n_rt - 1;   // the replay runs behind the profile: keep padding beside its last kernels
+        int rt_slots = 0;
+        for (size_t k = pos; k < std::min(n_rt, pos + (size_t)pad_window); k++) rt_slots = std::max(rt_slots, part[k] + part[k + 1]);
+        const int free_slots = total_slots - std::min(total_slots, rt_slots) + pad_overcommit - slots_out;
+
+        // rate limit: kernels allowed so far in this window (a small burst lets a whole segment through)
+        const int G = HybridExecutor::kPadSegment;
+        const bool limited = pad_target > 0;
+        const double allowed = limited ? pad_rate * std::min(1.0, now_ns / model_ns) + G : 1e18;
+        if (probe || drain_only || issued + 1 > allowed) { pad_trace.no_slot++; continue; }
 
         auto sel_start = sclock::now();
-        for (uint32_t n = 0; n < nq; n++) {
+        bool launched = false;
+        for (uint32_t n = 0; n < nq && !launched; n++) {
             const uint32_t qi = (dkp_next_queue + n) % nq;
-            if (busy_queues & (1u << qi)) continue;   // one piece per best-effort stream: pieces of a task stay ordered
             auto& q = *be_queues[qi];
-            if (q.task_queue.empty()) continue;
+            if (q.task_queue.empty()) { pad_trace.q_empty++; continue; }
+            if (q.pad_draining) { pad_trace.q_draining++; continue; }
+            if ((int)q.pad_out.size() >= pad_depth) { pad_trace.q_full++; continue; }
             auto be_task = q.task_queue.front();
             auto& be_exe = be_task->model->executor;
-            if (be_task->kernel_offset >= (int)be_exe.num_kernels()) continue;   // fully issued, draining
+            if (be_task->kernel_offset >= (int)be_exe.num_kernels()) {
+                // fully issued by padding: complete it here as soon as its stream has drained, so that its client
+                // can submit the next request while the real-time window is still open
+                if (be_task->all_issued_by_padding && be_task->get_state() == TaskState::Executing) {
+                    retire(q, *be_task);
+                    if (q.inflight.empty()) {
+                        be_task->end = std::chrono::system_clock::now();
+                        n_be_padded_finish++;
+                        be_task->state.store(TaskState::Finish);
+                        be_task->kernel_offset = 0;
+                        be_task->block_offset = 0;
+                        q.task_queue.pop();
+                        n_be_tasks++;
+                        finish_task(be_task);
+                    }
+                }
+                pad_trace.q_issued++;
+                continue;
+            }
             HybridExecutor::KernelArg& be_args = be_exe.trans_args[be_task->kernel_offset];
             int occ = 1;
             if (!be_args.resource.tensor_core) occ = std::max(1, std::min(2, be_args.resource.max_blocks_per_sm));
-            int blocks = std::min(free_sms * occ, be_args.block_num - be_task->block_offset);
-            blocks -= blocks % be_args.granularity;
-            if (blocks <= 0) continue;
+            const int remaining = be_args.block_num - be_task->block_offset;
+            int widest = 0;
+            for (auto& po : q.pad_out) widest = std::max(widest, po.slots);
+            // slots this stream may use: what it already claims plus what is free
+            const int avail = widest + free_slots;
+            int blocks = remaining;
+            // a whole segment (one graph launch, one event) when the task stands at a segment boundary
+            if (be_exe.has_pad_segments() && be_task->block_offset == 0 && be_task->kernel_offset % G == 0 &&
+                issued + G <= allowed + G - 1) {
+                const int k0 = be_task->kernel_offset, k1 = std::min((int)be_exe.num_kernels(), k0 + G);
+                int seg_slots = 0;
+                for (int k = k0; k < k1; k++) seg_slots = std::max(seg_slots, slots_of(be_exe.trans_args[k], be_exe.trans_args[k].block_num));
+                if (seg_slots <= avail) {
+                    if (be_task->start.time_since_epoch().count() == 0) be_task->start = std::chrono::system_clock::now();
+                    if (be_exe.launch_pad_segment(k0 / G, q.stream) != Status::Succ) {
+                        err_ = be_exe.error();
+                        break;
+                    }
+                    reef_event_t ev;
+                    if (!q.free_events.empty()) {
+                        ev = q.free_events.back();
+                        q.free_events.pop_back();
+                    } else {
+                        reef_event_create(&ev);
+                    }
+                    reef_event_record(ev, q.stream);
+                    if (q.pad_out.empty()) {
+                        q.pad_quantum_left = pad_quantum;
+                        dkp_next_queue = (qi + 1) % nq;
+                    }
+                    q.pad_out.push_back(PadOut{ev, seg_slots, abs_ns()});
+                    q.pad_quantum_left -= k1 - k0;
+                    if (q.pad_quantum_left <= 0) q.pad_draining = true;
+                    launched = true;
+                    issued += k1 - k0;
+                    pad_trace.segments++;
+                    for (int k = k0; k < k1; k++) advance_padded(be_task.get(), &q, be_exe.trans_args[k].block_num, true, nullptr);
+                    continue;
+                }
+            }
+            if (slots_of(be_args, blocks) > avail) {
+                // the kernel does not fit whole: a partial piece only when nothing else is out (progress)
+                if (active > 0 || avail <= 0) { pad_trace.q_nofit++; continue; }
+                blocks = be_args.resource.tensor_core ? avail : avail * 4;
+                blocks -= blocks % be_args.granularity;
+                if (blocks <= 0) continue;
+            }
             if (be_task->start.time_since_epoch().count() == 0) be_task->start = std::chrono::system_clock::now();
             if (be_exe.launch_pad_piece(be_task->kernel_offset, be_task->block_offset, blocks, occ, q.stream) != Status::Succ) {
                 err_ = be_exe.error();
                 break;
             }
-            PadPiece& pp = pad_pieces[slot];
-            reef_event_record(pp.ev, q.stream);
-            pp.pending = true;
-            pp.sms = (blocks + occ - 1) / occ;
-            pp.queue = qi;
+            reef_event_t ev;
+            if (!q.free_events.empty()) {
+                ev = q.free_events.back();
+                q.free_events.pop_back();
+            } else {
+                reef_event_create(&ev);
+            }
+            reef_event_record(ev, q.stream);
+            if (q.pad_out.empty()) {
+                q.pad_quantum_left = pad_quantum;   // takes a place: the next free place goes to a later queue
+                dkp_next_queue = (qi + 1) % nq;
+            }
+            q.pad_out.push_back(PadOut{ev, slots_of(be_args, blocks), abs_ns()});
+            if (--q.pad_quantum_left <= 0) q.pad_draining = true;
+            launched = true;
+            issued++;
+            pad_trace.singles++;
             advance_padded(be_task.get(), &q, blocks, true, nullptr);
-            dkp_next_queue = (qi + 1) % nq;
-            break;
         }
         kernel_sel_count++;
         kernel_sel_latency_sum += ns_since(sel_start);
+        if (launched) {
+            pad_trace.launched++;
+            pad_trace.launch_ns += ns_since(sel_start);
+        } else if (free_slots <= 0) {
+            pad_trace.no_sms++;
+        } else {
+            pad_trace.no_queue++;
+        }
+    }
+    const uint64_t window_ns = ns_since(t0);
+    pad_trace.window_ns += window_ns;
+    if (probe) {
+        rt_model.add_alone_sample((double)window_ns);
+    } else if (drain_only) {
+    } else if (pad_target > 0 && model_ns > 0) {
+        // slowdown controller: one multiplicative step per window on the kernel rate
+        const double baseline = rt_model.alone_ns() > 0.0 ? rt_model.alone_ns() : 1.02 * model_ns;
+        const double ratio = (double)window_ns / baseline;
+        pad_ratio_ema = pad_ratio_ema == 0.0 ? ratio : 0.8 * pad_ratio_ema + 0.2 * ratio;
+        if (pad_ratio_ema > 1.0 + pad_target) pad_rate *= 0.97;
+        else pad_rate *= 1.015;
+        pad_rate = std::max(4.0, std::min(4096.0, pad_rate));
     }
 }
 
@@ -728,8 +905,9 @@ void REEFScheduler::execute_be_task(std::shared_ptr<Task>& task, std::shared_ptr
             reef_stream_sync(preempt_stream);
         }
         if (task->needs_recover) {
-            // leftovers of the preempted launches have left the stream long ago; bounded wait all the same
-            reef_preempt_wait(tqueue->stream, 200000);
+            // Leftovers of preempted launches and padded pieces may still be on the stream.  Nothing waits for
+            // them: the counter reset and the relaunch below are ordered behind them by the stream, and every
+            // buffer from the resume point on is recomputed in order.
             for (auto& f : tqueue->inflight) tqueue->free_events.push_back(f.ev);
             tqueue->inflight.clear();
             task->needs_recover = false;

@@ -95,13 +95,26 @@ public:
     void set_be_stream_cap(int value) { be_stream_device_queue_cap = value < 1 ? 1 : value; }
     // real-time tasks that find no best-effort work replay a CUDA graph of the model (default on)
     void set_rt_graph(bool value) { rt_graph = value; }
-    // real-time kernels ahead of the estimated position whose SM footprint bounds a padded piece (default 2)
+    // Timeline padding (tensor-core models).  Unit = one SM slot: an SM holds two tensor-core CTAs.
+    //  window      real-time kernels ahead of the estimated position whose footprint bounds the padding
+    //  depth       padded pieces queued per best-effort stream (hides the launch-to-completion latency)
+    //  overcommit  slots best-effort pieces may claim beyond what the real-time kernels leave free
+    //  quantum     pieces after which a best-effort queue drains and yields its place to the next queue
     void set_pad_window(int value) { pad_window = value < 1 ? 1 : value; }
-    // padded pieces in flight at most (1..8) and SMs they may claim beyond the profile's free count
-    void set_pad_limits(int inflight, int overcommit_sms) {
-        pad_inflight_max = inflight < 1 ? 1 : (inflight > kMaxPadInflight ? kMaxPadInflight : inflight);
-        pad_overcommit_sms = overcommit_sms < 0 ? 0 : overcommit_sms;
+    void set_pad_limits(int depth, int overcommit_slots, int quantum) {
+        pad_depth = depth < 1 ? 1 : depth;
+        pad_overcommit = overcommit_slots;
+        pad_quantum = quantum < 1 ? 1 : quantum;
     }
+    // Padding is throttled so that a padded real-time task takes at most (1 + value) times the model latency of
+    // its profile (measured alone).  What a best-effort kernel costs the real-time chain is close to a fixed
+    // time per kernel launch on the device, whatever its size, so the throttle is a rate: at most `pad_rate`
+    // best-effort kernels per real-time window, spread evenly over it; after every window the rate moves a step
+    // down when the smoothed ratio is above the target and a step up when it is below.  0 switches the
+    // controller off (no rate limit).
+    void set_pad_slowdown_target(double value) { pad_target = value < 0 ? 0 : value; }
+    // after a real-time task, poll its queue this long before best-effort work is resumed (0: not at all)
+    void set_rt_grace_us(int value) { rt_grace_us = value < 0 ? 0 : value; }
     Status run();
     Status shutdown();
 
@@ -119,16 +132,39 @@ private:
     struct Model {
         executor::HybridExecutor executor;
         QueueID qid;
+        // real-time models: host-observed duration of an unpadded graph replay (ns), the baseline of the padding
+        // slowdown controller = the smallest of the last four samples (anything that disturbs a sample makes it
+        // longer).  Sampled by every replay that runs without best-effort work and by unpadded probe windows.
+        double alone_samples[4] = {0, 0, 0, 0};
+        uint32_t alone_count = 0;
+        uint32_t pad_windows = 0;
+        void add_alone_sample(double ns) { alone_samples[alone_count++ % 4] = ns; }
+        double alone_ns() const {
+            double m = 0.0;
+            for (double v : alone_samples)
+                if (v > 0.0 && (m == 0.0 || v < m)) m = v;
+            return m;
+        }
     };
+    static const uint32_t kPadProbePeriod = 64;
     struct InFlight {
         reef_event_t ev;
         int kernel;
+    };
+    struct PadOut {
+        reef_event_t ev;
+        int slots;
+        int64_t t_launch;
     };
     struct TaskQueue {
         ThreadSafeQueue<std::shared_ptr<Task>> task_queue;
         executor::GPUStream_t stream = nullptr;
         std::deque<InFlight> inflight;
         std::vector<reef_event_t> free_events;
+        // timeline padding: pieces of this queue's head task on its stream, not yet seen complete
+        std::deque<PadOut> pad_out;
+        int pad_quantum_left = 0;
+        bool pad_draining = false;
     };
 
     Status create_task_queue(std::shared_ptr<TaskQueue>& ret, bool rt);
@@ -179,18 +215,22 @@ private:
     std::atomic<uint64_t> pending_tasks;
 
     uint32_t dkp_next_queue = 0;
-    // timeline padding: padded pieces in flight (completion event + SMs they may occupy)
-    static const int kMaxPadInflight = 8;
-    struct PadPiece {
-        reef_event_t ev = nullptr;
-        int sms = 0;
-        bool pending = false;
-        uint32_t queue = 0;
-    };
-    PadPiece pad_pieces[kMaxPadInflight];
-    int pad_inflight_max = 4;           // pieces in flight at most (each on a different best-effort stream)
-    int pad_overcommit_sms = 32;        // SMs pieces may claim beyond what the profile says is free
-    int pad_window = 2;                 // real-time kernels a padded piece may overlap (footprint look-ahead)
+    int rt_grace_us = 30;
+    bool rt_recent = false;
+    std::chrono::steady_clock::time_point last_rt_finish;
+    int pad_depth = 3;
+    int pad_overcommit = 0;
+    int pad_window = 8;
+    int pad_quantum = 24;
+    double pad_target = 0.07;
+    double pad_ratio_ema = 0.0;
+    double pad_rate = 100.0;            // best-effort kernels per real-time window (controller state)
+    // loop statistics of timeline_padding, printed at destruction when REEF_PAD_TRACE is set
+    struct PadTrace {
+        uint64_t calls = 0, iters = 0, no_slot = 0, tail = 0, no_sms = 0, no_queue = 0, launched = 0;
+        uint64_t launch_ns = 0, turnaround_ns = 0, retired = 0, graph_launch_ns = 0, window_ns = 0;
+        uint64_t q_empty = 0, q_draining = 0, q_full = 0, q_issued = 0, q_nofit = 0, segments = 0, singles = 0;
+    } pad_trace;
     uint64_t preempt_count, preempt_latency_sum, preempt_latency_max;
     uint64_t kernel_sel_count, kernel_sel_latency_sum;
     uint64_t n_rt_tasks, n_be_tasks, n_be_padded_finish, n_padded_kernels, n_padded_blocks;

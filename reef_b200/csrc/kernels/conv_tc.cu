@@ -16,8 +16,19 @@ static int ceil_div_i(int a, int b) { return (a + b - 1) / b; }
 static int tc_plan_cap(const ConvP& p, int cap, TcPlan* pl) {
     memset(pl, 0, sizeof(*pl));
     pl->spatial = (p.kh * p.kw > 1 || p.sh > 1 || p.ph || p.pw) ? 1 : 0;
-    if (pl->spatial) {
-        if (p.wo > cap) return REEF_NOT_FOUND;
+    pl->xsplit = 1;
+    pl->xw = p.wo;
+    if (pl->spatial && p.wo > cap) {
+        // rows wider than a tile: cut every row into xsplit equal pieces
+        int xs = ceil_div_i(p.wo, cap);
+        while (xs <= p.wo && p.wo % xs != 0) xs++;
+        if (xs > p.wo || p.wo / xs < 8) return REEF_NOT_FOUND;
+        pl->xsplit = xs;
+        pl->xw = p.wo / xs;
+        pl->rows = 1;
+        pl->n_valid = pl->xw;
+        pl->n_tiles = p.ho * xs;
+    } else if (pl->spatial) {
         int best = 1;
         const int rmax = cap / p.wo;
         const int lim = rmax < p.ho ? rmax : p.ho;
@@ -51,21 +62,23 @@ static int tc_plan_cap(const ConvP& p, int cap, TcPlan* pl) {
         if (pl->splits == s || s == 1) break;
     }
     pl->b_bytes = pl->n_valid * 128;
-    // shared memory: the stage ring is reused by the epilogue for the staged accumulator tile (pixel rows
-    // rounded up to 32, 512 bytes each) and, with a K split, the exchange area recv[rank][cpc_max][128]
-    // ring depth: the whole K range of a CTA in flight when it fits (a batch-1 layer is bound by load latency)
+    // Shared memory: at most TC_SMEM_CAP per CTA, so that two CTAs fit one SM (a real-time kernel beside the
+    // early-launched prologue of its successor, or beside a best-effort kernel).  The stage ring is reused by
+    // the epilogue for the staged accumulator tile (one 512-byte row per pixel) and, with a K split, the
+    // exchange area recv[S-1][cpc_max][128].
+    const int budget = TC_SMEM_CAP - 1024 - 256;   // alignment slack and control words
     const int stage_bytes = TC_A_BYTES + pl->n_mma * 128;
     pl->stages = pl->kb_per_split < TC_MAX_STAGES ? pl->kb_per_split : TC_MAX_STAGES;
-    while (pl->stages > 2 && pl->stages * stage_bytes > 200 * 1024) pl->stages--;
+    while (pl->stages > 1 && pl->stages * stage_bytes > budget) pl->stages--;
+    if (pl->stages * stage_bytes > budget || (pl->stages < 2 && pl->kb_per_split > 1)) return REEF_NOT_FOUND;
     const int ring = pl->stages * stage_bytes;
-    const int n32 = ((pl->n_valid + 31) / 32) * 32;
     pl->cpc_max = ceil_div_i(pl->n_valid, pl->splits);
-    pl->recv_offset_floats = n32 * TC_BM;
-    const int epi = n32 * 512 + (pl->splits > 1 ? pl->splits * pl->cpc_max * 512 : 0);
+    pl->recv_offset_floats = pl->n_valid * TC_BM;
+    const int epi = pl->n_valid * 512 + (pl->splits > 1 ? (pl->splits - 1) * pl->cpc_max * 512 : 0);
+    if (epi > budget) return REEF_NOT_FOUND;
     pl->region_bytes = ring > epi ? ring : epi;
     pl->region_bytes = ((pl->region_bytes + 127) / 128) * 128;
     pl->smem = 1024 + pl->region_bytes + 256;   // alignment slack + data region + control words
-    if (pl->smem > 225 * 1024) return REEF_NOT_FOUND;
     return REEF_SUCC;
 }
 
@@ -77,7 +90,7 @@ int tc_plan(const ConvP& p, TcPlan* pl) {
     if (p.nchw || (p.ci % TC_BK) != 0 || p.sh != p.sw || (p.sh != 1 && p.sh != 2)) return REEF_NOT_FOUND;
     if ((p.ics & 3) || (p.ioff & 3) || (p.ocs & 3) || (p.ooff & 3) || (p.co & 3)) return REEF_NOT_FOUND;
     if (p.kh * p.kw > 64) return REEF_NOT_FOUND;
-    static const int caps[] = {224, 160, 112, 64, 32};
+    static const int caps[] = {208, 160, 112, 96, 64, 32};
     TcPlan best;
     int best_ctas = 0;
     for (int cap : caps) {
@@ -168,7 +181,7 @@ int tc_build_params(const ConvP& p, const TcPlan& pl, void* const* a, TcParams* 
                 const float* base = in + p.ioff + ((size_t)ry * p.wi + rx) * p.ics;
                 cuuint64_t dims[3] = {(cuuint64_t)p.ci, (cuuint64_t)nx, (cuuint64_t)ny};
                 cuuint64_t strides[2] = {(cuuint64_t)s * p.ics * 4, (cuuint64_t)s * p.wi * p.ics * 4};
-                cuuint32_t box[3] = {TC_BK, (cuuint32_t)p.wo, (cuuint32_t)pl.rows};
+                cuuint32_t box[3] = {TC_BK, (cuuint32_t)pl.xw, (cuuint32_t)pl.rows};
                 rc = encode(&P->tm_x[ry * s + rx], base, 3, dims, strides, box);
                 if (rc != REEF_SUCC) return rc;
             }
@@ -187,7 +200,7 @@ int tc_build_params(const ConvP& p, const TcPlan& pl, void* const* a, TcParams* 
     rc = tc_error_word(&P->error_word);
     if (rc != REEF_SUCC) return rc;
     P->co = p.co; P->ptot = p.ptot; P->ocs = p.ocs; P->ooff = p.ooff;
-    P->spatial = pl.spatial; P->wo = p.wo; P->rows = pl.rows;
+    P->spatial = pl.spatial; P->wo = p.wo; P->rows = pl.rows; P->xsplit = pl.xsplit; P->xw = pl.xw;
     P->n_valid = pl.n_valid; P->n_mma = pl.n_mma; P->tmem_cols = pl.tmem_cols;
     P->kh = p.kh; P->kw = p.kw; P->stride = p.sh; P->ph = p.ph; P->pw = p.pw;
     P->cblocks = pl.cblocks; P->kb_total = pl.kb_total; P->kb_per_split = pl.kb_per_split; P->splits = pl.splits;
@@ -257,6 +270,9 @@ int tc_prepare_device() {
     if (dev >= 0 && dev < 16 && !g_attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute((const void*)reef_conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              226 * 1024);
+        if (e == cudaSuccess)   // the whole unified L1/shared array as shared memory, so that two CTAs are resident
+            e = cudaFuncSetAttribute((const void*)reef_conv_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) {
             set_error(std::string("cudaFuncSetAttribute(conv_tc): ") + cudaGetErrorString(e));
             return REEF_FAIL;
@@ -305,7 +321,13 @@ int tc_launch(const TcParams& P0, const TcPlan& pl, cudaStream_t st, const int* 
         attrs[na].val.clusterDim.z = 1;
         na++;
     }
-    if (g_use_pdl) {
+    static int pad_pdl = -1;
+    if (pad_pdl < 0) {
+        const char* v = getenv("REEF_PAD_PDL");
+        pad_pdl = (v && v[0] == '0') ? 0 : 1;
+    }
+    const bool piece = flag == nullptr && slot != nullptr;   // a padded best-effort piece
+    if (g_use_pdl && (!piece || pad_pdl)) {
         attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attrs[na].val.programmaticStreamSerializationAllowed = 1;
         na++;
@@ -326,8 +348,9 @@ int tc_func_attrs(const TcPlan& pl, cudaFuncAttributes* fa, int* occ) {
         set_error(std::string("cudaFuncGetAttributes(conv_tc): ") + cudaGetErrorString(e));
         return REEF_FAIL;
     }
-    *occ = 1;   // 180 KB of shared memory: one CTA per SM
-    (void)pl;
+    // shared memory (plus the 1 KB the hardware reserves per CTA) and 124 registers x 256 threads: two at most
+    const int by_smem = (228 * 1024) / (pl.smem + 1024);
+    *occ = by_smem < 1 ? 1 : (by_smem > 2 ? 2 : by_smem);
     return REEF_SUCC;
 }
 

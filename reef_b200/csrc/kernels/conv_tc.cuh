@@ -177,7 +177,52 @@ __device__ __forceinline__ void tc_stamp(const TcParams& P, int slot) {
     if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) P.trace[slot] = clock64();
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __grid_constant__ TcParams P) {
+// Finishes the pixel rows [jb, je) a cluster rank owns after a K split: sums the partials of ranks 0..S-1 in
+// rank order (a fixed order: bit-reproducible), applies the epilogue and stores 512-byte rows.  RB rows per warp
+// are in flight at a time, RB * SMAX 128-bit loads per lane (16: the kernel is built for two CTAs per SM, so
+// a thread has 128 registers).
+template <int RB, int SMAX>
+__device__ __forceinline__ void tc_finish_split(const TcParams& P, const float* stage, const float* recv, int S, int split,
+                                                int jb, int je, int warp, int cbase, int co, int pix0, float4 sc, float4 sh,
+                                                float lo, bool rnd, bool gelu, bool has_res) {
+    const float* src[SMAX];
+#pragma unroll
+    for (int q = 0; q < SMAX; q++)
+        src[q] = (q == split) ? stage + (size_t)jb * TC_BM + cbase
+                              : recv + (size_t)(q < S ? (q < split ? q : q - 1) : 0) * P.cpc_max * TC_BM + cbase;
+    for (int jbase = warp; jbase < je - jb; jbase += 8 * RB) {
+        float4 part[RB][SMAX], rv[RB];
+#pragma unroll
+        for (int u = 0; u < RB; u++) {
+            const int jr = jbase + 8 * u;   // row within this rank's slice
+            rv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (jr < je - jb) {
+#pragma unroll
+                for (int q = 0; q < SMAX; q++)
+                    if (q < S) part[u][q] = *reinterpret_cast<const float4*>(src[q] + (size_t)jr * TC_BM);
+                if (has_res) rv[u] = __ldg(reinterpret_cast<const float4*>(P.res + (size_t)(pix0 + jb + jr) * P.co + co));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < RB; u++) {
+            const int jr = jbase + 8 * u;
+            if (jr < je - jb) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < SMAX; q++)   // fixed rank order: deterministic sum
+                    if (q < S) { v.x += part[u][q].x; v.y += part[u][q].y; v.z += part[u][q].z; v.w += part[u][q].w; }
+                float4 o;
+                o.x = tc_epilogue(v.x, rv[u].x, sc.x, sh.x, lo, rnd, gelu);
+                o.y = tc_epilogue(v.y, rv[u].y, sc.y, sh.y, lo, rnd, gelu);
+                o.z = tc_epilogue(v.z, rv[u].z, sc.z, sh.z, lo, rnd, gelu);
+                o.w = tc_epilogue(v.w, rv[u].w, sc.w, sh.w, lo, rnd, gelu);
+                *reinterpret_cast<float4*>(P.out + (size_t)(pix0 + jb + jr) * P.ocs + P.ooff + co) = o;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __grid_constant__ TcParams P) {
     extern __shared__ __align__(16) unsigned char tc_smem_raw[];
     // stage buffers need 1024-byte alignment (swizzle atom); carve barriers behind them
     const uint32_t raw = smem_u32(tc_smem_raw);
@@ -203,7 +248,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
     const int kb_end = min(kb_begin + P.kb_per_split, P.kb_total);
     const int nkb = kb_end - kb_begin;
 
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may begin its prologue
     if (tid == 0) {
         for (int s = 0; s < NS; s++) {
             mbar_init(bar_full + 8 * s, 1);
@@ -233,7 +277,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
     // K-split exchange barrier: armed now, so that peers may send as soon as their own tile is staged.  The
     // cluster barrier below (cheap here: all CTAs of a cluster start together, and it overlaps the first loads'
     // latency) guarantees every peer's barrier is initialised and armed before any remote completion.
-    const int pix0 = P.spatial ? (tile % P.n_tiles) * P.rows * P.wo : (tile % P.n_tiles) * P.n_valid;
+    // spatial tiles: tile_n -> (row group ty, row piece tx); tx > 0 only where a row is wider than a tile
+    const int tile_y = P.xsplit > 1 ? tile_n / P.xsplit : tile_n, tile_x = P.xsplit > 1 ? tile_n - tile_y * P.xsplit : 0;
+    const int pix0 = P.spatial ? tile_y * P.rows * P.wo + tile_x * P.xw : tile_n * P.n_valid;
     const int n_lim = min(P.n_valid, P.ptot - pix0);   // columns of this tile that are real pixels
     const int cpc = (n_lim + S - 1) / S;               // pixel rows one rank finishes
     const int jb = min(split * cpc, n_lim), je = min(jb + cpc, n_lim);
@@ -271,8 +317,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
             // tap and channel block of this K block; the per-tap sub-lattice and offsets come from a host table
             const int tap = P.cblocks == 1 ? kb : (int)__umulhi((unsigned)kb, P.cb_magic), cb = kb - tap * P.cblocks;   // 2^32/1 does not fit the magic
             if (P.spatial) {
-                tma_load_3d(st + TC_A_BYTES, &P.tm_x[P.tap_map[tap]], bar_full + 8 * s, cb * TC_BK, P.tap_qx[tap],
-                            tile_n * P.rows + P.tap_qy[tap]);
+                tma_load_3d(st + TC_A_BYTES, &P.tm_x[P.tap_map[tap]], bar_full + 8 * s, cb * TC_BK,
+                            tile_x * P.xw + P.tap_qx[tap], tile_y * P.rows + P.tap_qy[tap]);
             } else {
                 tma_load_2d(st + TC_A_BYTES, &P.tm_x[0], bar_full + 8 * s, cb * TC_BK, tile_n * P.n_valid);
             }
@@ -286,6 +332,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
                 tma_load_2d(base + lane * stage_bytes, &P.tm_w, bar_full + 8 * lane, (kb_begin + lane) * TC_BK, m0);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
+            // Only now may the next kernel of the stream begin its prologue (set-up, weight loads).  Released
+            // any earlier, a chain of these kernels runs ahead without bound and parks its blocks on every SM;
+            // in this order at most two grids of a chain are resident and the other SM slots stay free for
+            // best-effort kernels.  One thread per CTA executing the instruction counts for the CTA.
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             if (lane < first) load_b(lane);
             if (lane == 0) tc_stamp(P, 2);   // ring filled (loads issued)
         }
@@ -356,7 +407,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
                 tmem_ld32_nowait(taddr + j0, r);
                 tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 32; j++) stage[(j0 + j) * TC_BM + row] = __uint_as_float(r[j]);
+                for (int j = 0; j < 32; j++)
+                    if (j0 + j < n_lim) stage[(j0 + j) * TC_BM + row] = __uint_as_float(r[j]);
             }
         }
         if (tid == 0) tc_stamp(P, 7);   // accumulator tile staged in shared memory
@@ -364,7 +416,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
         // by each peer with ONE bulk shared-memory-to-shared-memory copy per peer (the copy engine moves the
         // bytes and completes the owner's mbarrier); remote loads from distributed shared memory proved an
         // order of magnitude slower here.  Owners then read only their own shared memory.
-        float* recv = stage + P.recv_offset_floats;    // recv[rank][cpc_max][128]
+        float* recv = stage + P.recv_offset_floats;    // recv[slot][cpc_max][128]; sender q uses slot q - (q > owner)
         if (S > 1) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staged tile -> visible to the copy engine
             __syncthreads();      // the whole tile is staged
@@ -376,7 +428,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
                     const int qb = min(q * cpc, n_lim), qe = min(qb + cpc, n_lim);
                     const uint32_t bytes = (uint32_t)((qe - qb) * TC_BM * 4);
                     if (bytes == 0) continue;
-                    const uint32_t dst = mapa_shared(smem_u32(recv + (size_t)split * P.cpc_max * TC_BM), (uint32_t)q);
+                    const int slot = split < q ? split : split - 1;   // the owner keeps no slot for itself
+                    const uint32_t dst = mapa_shared(smem_u32(recv + (size_t)slot * P.cpc_max * TC_BM), (uint32_t)q);
                     const uint32_t rbar = mapa_shared(bar_red, (uint32_t)q);
                     asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                                  ::"r"(dst), "r"(smem_u32(stage + (size_t)qb * TC_BM)), "r"(bytes), "r"(rbar)
@@ -442,41 +495,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) reef_conv_tc_kernel(const __gri
                 }
             } else {
                 // partial of rank q for row j: own rows come from the staged tile, the others from recv[q]
-                const float* src[TC_MAX_SPLITS];
-#pragma unroll
-                for (int q = 0; q < TC_MAX_SPLITS; q++)
-                    src[q] = (q == split) ? stage + (size_t)jb * TC_BM + cbase
-                                          : recv + (size_t)(q < S ? q : 0) * P.cpc_max * TC_BM + cbase;
-                for (int jbase = warp; jbase < je - jb; jbase += 8 * RB) {
-                    float4 part[RB][TC_MAX_SPLITS], rv[RB];
-#pragma unroll
-                    for (int u = 0; u < RB; u++) {
-                        const int jr = jbase + 8 * u;   // row within this rank's slice
-                        rv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (jr < je - jb) {
-#pragma unroll
-                            for (int q = 0; q < TC_MAX_SPLITS; q++)
-                                if (q < S) part[u][q] = *reinterpret_cast<const float4*>(src[q] + (size_t)jr * TC_BM);
-                            if (has_res) rv[u] = __ldg(reinterpret_cast<const float4*>(P.res + (size_t)(pix0 + jb + jr) * P.co + co));
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < RB; u++) {
-                        const int jr = jbase + 8 * u;
-                        if (jr < je - jb) {
-                            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                            for (int q = 0; q < TC_MAX_SPLITS; q++)   // fixed rank order: deterministic sum
-                                if (q < S) { v.x += part[u][q].x; v.y += part[u][q].y; v.z += part[u][q].z; v.w += part[u][q].w; }
-                            float4 o;
-                            o.x = tc_epilogue(v.x, rv[u].x, sc.x, sh.x, lo, rnd, gelu);
-                            o.y = tc_epilogue(v.y, rv[u].y, sc.y, sh.y, lo, rnd, gelu);
-                            o.z = tc_epilogue(v.z, rv[u].z, sc.z, sh.z, lo, rnd, gelu);
-                            o.w = tc_epilogue(v.w, rv[u].w, sc.w, sh.w, lo, rnd, gelu);
-                            *reinterpret_cast<float4*>(P.out + (size_t)(pix0 + jb + jr) * P.ocs + P.ooff + co) = o;
-                        }
-                    }
-                }
+                if (S <= 4)
+                    tc_finish_split<4, 4>(P, stage, recv, S, split, jb, je, warp, cbase, co, pix0, sc, sh, lo, rnd, gelu, has_res);
+                else
+                    tc_finish_split<2, TC_MAX_SPLITS>(P, stage, recv, S, split, jb, je, warp, cbase, co, pix0, sc, sh, lo, rnd,
+                                                      gelu, has_res);
             }
         }
         if (S > 1) cluster_wait();      // barrier #2

@@ -12,6 +12,8 @@ constexpr int TC_BK = 32;             // fp32 elements per K block = 128 bytes
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 4;
 constexpr int TC_THREADS = 256;
 constexpr int TC_MAX_SPLITS = 8;
+// Dynamic shared memory of one CTA at most: two CTAs (each + 1 KB the hardware reserves) fit the 228 KB of an SM
+constexpr int TC_SMEM_CAP = 112 * 1024;
 
 struct TcParams {
     CUtensorMap tm_w;        // weights  dims (K, Cout), box (32, 128)
@@ -29,6 +31,7 @@ struct TcParams {
     int ocs, ooff;
     int spatial;             // 0: flat [P][C] view, tile = n_valid consecutive pixels; 1: tile = rows x Wo
     int wo, rows;            // spatial: output width, rows per tile
+    int xsplit, xw;          // spatial: a row is cut into xsplit tiles of xw pixels (rows == 1), else xsplit == 1
     int n_valid;             // pixels per tile
     int n_mma;               // UMMA N (multiple of 16, >= n_valid)
     int tmem_cols;           // power of two >= n_mma

@@ -382,11 +382,14 @@ __device__ __forceinline__ bool run_any(const KTask& t, int vb, unsigned char* s
 
 extern __shared__ __align__(16) unsigned char reef_dyn_smem[];
 
-// Programmatic dependent launch: the next kernel may start its prologue at once (launch_dependents) and this
-// one waits for its predecessor's results before touching memory (wait is a no-op for an ordinary launch).
+// Programmatic dependent launch: this kernel waits for its predecessor's results before touching memory (a
+// no-op for an ordinary launch) and only then lets its successor start its prologue.  Releasing the successor
+// before the wait would let a chain of kernels run ahead without bound: every grid's blocks would become
+// resident, release the next grid and park at their wait, until the SMs are full of parked blocks and a
+// best-effort kernel on another stream finds no room.  In this order at most two grids of a chain are resident.
 __device__ __forceinline__ void pdl_prologue() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 template <int F>

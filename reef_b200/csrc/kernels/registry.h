@@ -19,6 +19,7 @@ struct TcPlan {
     int n_tiles, m_tiles, cblocks, kb_total, kb_per_split, splits;
     int b_bytes, smem;
     int region_bytes, recv_offset_floats, cpc_max, stages;
+    int xsplit, xw;
 };
 
 struct TcCache;   // tensor maps of one kernel call, rebuilt when its pointers change
