@@ -55,6 +55,10 @@ REEF_HOST_API int reef_executor_execute_preempt_resume(reef_executor_t e, int de
 REEF_HOST_API int reef_executor_task_slots(reef_executor_t e, int* slots, int* block_nums, size_t n);
 /* Average milliseconds of `iters` executions after `warmup` (mode: 0 raw launches, 1 graph, 2 best-effort). */
 REEF_HOST_API int reef_executor_time(reef_executor_t e, int mode, int warmup, int iters, float* avg_ms);
+/* Average milliseconds of one replay of a CUDA graph holding only the model's tensor-core kernels, in schedule
+ * order (CUDA events around `iters` replays after `warmup`); *launches = kernels in that graph.  NotFound when
+ * the schedule has none.  No reference counterpart (measurement aid for the roofline of the dominant kernel). */
+REEF_HOST_API int reef_executor_time_tensor_core(reef_executor_t e, int warmup, int iters, float* avg_ms, int* launches);
 /* Per-kernel device time in microseconds (CUDA events around each launch), n = num_kernels entries;
  * also returns algorithmic flops/bytes and the tensor-core marker per kernel when the arrays are given. */
 REEF_HOST_API int reef_executor_profile_kernels(reef_executor_t e, int iters, float* us, double* flops, double* bytes,

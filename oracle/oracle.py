@@ -80,6 +80,15 @@ def run_kernel(name: str, bufs: list, acc64: bool = False) -> None:
     elif op == "fused_add_nn_relu":
         L.reef_oracle_fused_add_nn_relu(_p(bufs[0]), _p(bufs[1]), _p(bufs[2]), i32(a["c"]), i32(a["n"]),
                                         i32(a.get("ics", a["c"])), i32(a.get("ioff", 0)))
+    elif op == "reef_conv2d_add_preact":
+        # one launch in the product; here the two reference kernels it stands for, one after the other
+        # (fused_nn_conv2d_add, then fused_add_nn_relu of the next unit): bufs = in, weight, out, residual, bias2, out2
+        conv_name = "fused_nn_conv2d_add__" + name.split("__", 1)[1]
+        run_kernel(conv_name, bufs[:4], acc64)
+        L.reef_oracle_fused_add_nn_relu(_p(bufs[5]), _p(bufs[2]), _p(bufs[4]), i32(a["co"]),
+                                        i32(((a["hi"] + 2 * a["ph"] - a["kh"]) // a["sh"] + 1) *
+                                            ((a["wi"] + 2 * a["pw"] - a["kw"]) // a["sw"] + 1)),
+                                        i32(a["co"]), i32(0))
     elif op.startswith("fused_nn_conv2d"):
         tail = op[len("fused_nn_conv2d"):]
         relu = tail.endswith("_nn_relu")

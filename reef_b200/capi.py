@@ -214,6 +214,14 @@ class HybridExecutor:
                "reef_executor_time", self._err())
         return ms.value
 
+    def time_tensor_core(self, warmup: int = 3, iters: int = 20):
+        """(ms per replay, launches) of a graph with only the tensor-core kernels of the schedule."""
+        ms = C.c_float()
+        n = C.c_int()
+        _check(self._lib.reef_executor_time_tensor_core(self._h, C.c_int(warmup), C.c_int(iters), C.byref(ms), C.byref(n)),
+               "time_tensor_core", self._err())
+        return float(ms.value), int(n.value)
+
     def profile_kernels(self, iters: int = 20):
         n = self.num_kernels()
         us = (C.c_float * n)()

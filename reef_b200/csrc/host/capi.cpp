@@ -146,6 +146,41 @@ int reef_executor_time(reef_executor_t e, int mode, int warmup, int iters, float
     reef_event_destroy(b);
     return rc;
 }
+int reef_executor_time_tensor_core(reef_executor_t e, int warmup, int iters, float* avg_ms, int* launches) {
+    // a CUDA graph of the tensor-core kernels alone, in schedule order (they keep their programmatic
+    // dependencies on one another; the kernels between them are left out, so their inputs are stale, which
+    // does not change what a launch costs)
+    auto& exe = e->exe;
+    int n = 0;
+    for (size_t i = 0; i < exe.num_kernels(); i++) n += exe.trans_args[i].resource.tensor_core ? 1 : 0;
+    if (launches) *launches = n;
+    if (n == 0) return NotFound;
+    reef_graph_t g = nullptr;
+    if (reef_graph_begin(exe.stream()) != REEF_SUCC) return Fail;
+    Status st = Succ;
+    for (size_t i = 0; i < exe.num_kernels() && st == Succ; i++)
+        if (exe.trans_args[i].resource.tensor_core) st = (Status)exe.execute_kernel_async((int)i);
+    int rc = reef_graph_end(exe.stream(), &g);
+    if (st != Succ || rc != REEF_SUCC) {
+        if (g) reef_graph_destroy(g);
+        return Fail;
+    }
+    reef_event_t a, b;
+    if (reef_event_create(&a) != REEF_SUCC || reef_event_create(&b) != REEF_SUCC) return Fail;
+    for (int i = 0; i < warmup && rc == REEF_SUCC; i++) rc = reef_graph_launch(g, exe.stream());
+    reef_stream_sync(exe.stream());
+    reef_event_record(a, exe.stream());
+    for (int i = 0; i < iters && rc == REEF_SUCC; i++) rc = reef_graph_launch(g, exe.stream());
+    reef_event_record(b, exe.stream());
+    reef_event_sync(b);
+    float ms = 0;
+    reef_event_elapsed_ms(a, b, &ms);
+    *avg_ms = ms / (float)std::max(1, iters);
+    reef_event_destroy(a);
+    reef_event_destroy(b);
+    reef_graph_destroy(g);
+    return rc == REEF_SUCC ? Succ : Fail;
+}
 int reef_executor_profile_kernels(reef_executor_t e, int iters, float* us, double* flops, double* bytes,
                                   int* tensor_core, int* blocks, int* max_blocks_per_sm, size_t n) {
     if (n < e->exe.num_kernels()) return OutOfRange;

@@ -197,6 +197,8 @@ int tc_build_params(const ConvP& p, const TcPlan& pl, void* const* a, TcParams* 
     P->bias = (p.ep & EP_BIAS) ? (const float*)a[p.i_bias] : nullptr;
     P->gamma = (p.ep & EP_GB) ? (const float*)a[p.i_gamma] : nullptr;
     P->beta = (p.ep & EP_GB) ? (const float*)a[p.i_beta] : nullptr;
+    P->out2 = (p.ep & EP_DUAL) ? (float*)a[p.i_out2] : nullptr;
+    P->bias2 = (p.ep & EP_DUAL) ? (const float*)a[p.i_bias2] : nullptr;
     rc = tc_error_word(&P->error_word);
     if (rc != REEF_SUCC) return rc;
     P->co = p.co; P->ptot = p.ptot; P->ocs = p.ocs; P->ooff = p.ooff;

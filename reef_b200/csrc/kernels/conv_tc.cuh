@@ -173,6 +173,20 @@ __device__ __forceinline__ float tc_epilogue(float v, float r, float sc, float s
     return v;
 }
 
+// second output of the dual epilogue: relu(o + b2), rounded like the first when the layer rounds
+__device__ __forceinline__ float4 tc_preact(float4 o, float4 b2, bool rnd) {
+    float4 r;
+    r.x = fmaxf(o.x + b2.x, 0.f); r.y = fmaxf(o.y + b2.y, 0.f); r.z = fmaxf(o.z + b2.z, 0.f); r.w = fmaxf(o.w + b2.w, 0.f);
+    if (rnd) {
+        uint32_t u;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(r.x)); r.x = __uint_as_float(u);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(r.y)); r.y = __uint_as_float(u);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(r.z)); r.z = __uint_as_float(u);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(r.w)); r.w = __uint_as_float(u);
+    }
+    return r;
+}
+
 __device__ __forceinline__ void tc_stamp(const TcParams& P, int slot) {
     if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) P.trace[slot] = clock64();
 }
@@ -184,7 +198,7 @@ __device__ __forceinline__ void tc_stamp(const TcParams& P, int slot) {
 template <int RB, int SMAX>
 __device__ __forceinline__ void tc_finish_split(const TcParams& P, const float* stage, const float* recv, int S, int split,
                                                 int jb, int je, int warp, int cbase, int co, int pix0, float4 sc, float4 sh,
-                                                float lo, bool rnd, bool gelu, bool has_res) {
+                                                float lo, bool rnd, bool gelu, bool has_res, float4 b2) {
     const float* src[SMAX];
 #pragma unroll
     for (int q = 0; q < SMAX; q++)
@@ -217,6 +231,7 @@ __device__ __forceinline__ void tc_finish_split(const TcParams& P, const float* 
                 o.z = tc_epilogue(v.z, rv[u].z, sc.z, sh.z, lo, rnd, gelu);
                 o.w = tc_epilogue(v.w, rv[u].w, sc.w, sh.w, lo, rnd, gelu);
                 *reinterpret_cast<float4*>(P.out + (size_t)(pix0 + jb + jr) * P.ocs + P.ooff + co) = o;
+                if (P.out2 != nullptr) *reinterpret_cast<float4*>(P.out2 + (size_t)(pix0 + jb + jr) * P.co + co) = tc_preact(o, b2, rnd);
             }
         }
     }
@@ -422,12 +437,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             __syncthreads();      // the whole tile is staged
             cluster_wait();       // barrier #1: all peers are past their main loops (and their barriers are armed)
             if (tid == 0) tc_stamp(P, 3);
-            if (tid == 0) {
-                for (int q = 0; q < S; q++) {
-                    if (q == split) continue;
-                    const int qb = min(q * cpc, n_lim), qe = min(qb + cpc, n_lim);
-                    const uint32_t bytes = (uint32_t)((qe - qb) * TC_BM * 4);
-                    if (bytes == 0) continue;
+            if (tid < S && tid != split) {   // one thread per peer: the copies are issued side by side
+                const int q = tid;
+                const int qb = min(q * cpc, n_lim), qe = min(qb + cpc, n_lim);
+                const uint32_t bytes = (uint32_t)((qe - qb) * TC_BM * 4);
+                if (bytes != 0) {
                     const int slot = split < q ? split : split - 1;   // the owner keeps no slot for itself
                     const uint32_t dst = mapa_shared(smem_u32(recv + (size_t)slot * P.cpc_max * TC_BM), (uint32_t)q);
                     const uint32_t rbar = mapa_shared(bar_red, (uint32_t)q);
@@ -460,6 +474,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
                 sh = *reinterpret_cast<const float4*>(P.bias + co);
             }
         }
+        float4 b2 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (cvalid && P.bias2 != nullptr) b2 = *reinterpret_cast<const float4*>(P.bias2 + co);
         const float lo = (P.ep & TC_EP_RELU) ? 0.f : -__int_as_float(0x7f800000);
         const bool has_res = (P.ep & TC_EP_RES) != 0;
         const bool rnd = (P.ep & TC_EP_ROUND) != 0;
@@ -490,16 +506,17 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
                             o.z = tc_epilogue(v[u].z, rv[u].z, sc.z, sh.z, lo, rnd, gelu);
                             o.w = tc_epilogue(v[u].w, rv[u].w, sc.w, sh.w, lo, rnd, gelu);
                             *reinterpret_cast<float4*>(P.out + (size_t)(pix0 + j) * P.ocs + P.ooff + co) = o;
+                            if (P.out2 != nullptr) *reinterpret_cast<float4*>(P.out2 + (size_t)(pix0 + j) * P.co + co) = tc_preact(o, b2, rnd);
                         }
                     }
                 }
             } else {
                 // partial of rank q for row j: own rows come from the staged tile, the others from recv[q]
                 if (S <= 4)
-                    tc_finish_split<4, 4>(P, stage, recv, S, split, jb, je, warp, cbase, co, pix0, sc, sh, lo, rnd, gelu, has_res);
+                    tc_finish_split<4, 4>(P, stage, recv, S, split, jb, je, warp, cbase, co, pix0, sc, sh, lo, rnd, gelu, has_res, b2);
                 else
                     tc_finish_split<2, TC_MAX_SPLITS>(P, stage, recv, S, split, jb, je, warp, cbase, co, pix0, sc, sh, lo, rnd,
-                                                      gelu, has_res);
+                                                      gelu, has_res, b2);
             }
         }
         if (S > 1) cluster_wait();      // barrier #2

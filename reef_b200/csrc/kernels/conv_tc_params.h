@@ -23,6 +23,8 @@ struct TcParams {
     const float* bias;
     const float* gamma;
     const float* beta;
+    float* out2;             // second output [P][Cout] = relu(out + bias2), else nullptr
+    const float* bias2;
     const int* preempt_flag; // best-effort flavour, else nullptr
     int* task_slot;
     int* error_word;         // device word set non-zero when a bounded wait expired

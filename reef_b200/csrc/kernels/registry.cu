@@ -216,7 +216,7 @@ static int build_spec(const std::string& name, KernelSpec* s) {
         int m, n, k;
         if (!a.need("m", &m) || !a.need("n", &n) || !a.need("k", &k)) goto bad;
         p.ep = 0;
-        p.i_res = p.i_bias = p.i_gamma = p.i_beta = -1;
+        p.i_res = p.i_bias = p.i_gamma = p.i_beta = p.i_bias2 = p.i_out2 = -1;
         int nargs = 3;
         if (tail.find("_bias") != std::string::npos) { p.ep |= EP_BIAS; p.i_bias = nargs++; }
         if (tail.find("_gelu") != std::string::npos) p.ep |= EP_GELU;
@@ -245,11 +245,15 @@ static int build_spec(const std::string& name, KernelSpec* s) {
         s->dyn_smem = kConvSimtSmem;
         return REEF_SUCC;
     }
-    if (op.rfind("fused_nn_conv2d", 0) == 0) {
+    // reef_conv2d_add_preact: conv + residual written to `out`, and relu(out + bias2) written to `out2` by the
+    // same epilogue: the reference's fused_nn_conv2d_add followed by the next unit's fused_add_nn_relu
+    // (resource/resnet152/resnet152.cu:340-363 and :2-12) in one launch.  args: in, weight, out, residual, bias2, out2.
+    if (op == "reef_conv2d_add_preact" || op.rfind("fused_nn_conv2d", 0) == 0) {
+        const bool preact = op == "reef_conv2d_add_preact";
         ConvP& p = t.p.conv;
-        std::string tail = op.substr(strlen("fused_nn_conv2d"));
+        std::string tail = preact ? std::string("_add") : op.substr(strlen("fused_nn_conv2d"));
         p.ep = 0;
-        p.i_res = p.i_bias = p.i_gamma = p.i_beta = -1;
+        p.i_res = p.i_bias = p.i_gamma = p.i_beta = p.i_bias2 = p.i_out2 = -1;
         bool relu = false;
         const std::string r = "_nn_relu";
         if (tail.size() >= r.size() && tail.compare(tail.size() - r.size(), r.size(), r) == 0) {
@@ -272,6 +276,12 @@ static int build_spec(const std::string& name, KernelSpec* s) {
             return REEF_NOT_FOUND;
         }
         if (relu) p.ep |= EP_RELU;
+        if (preact) {
+            p.ep |= EP_DUAL;
+            p.i_bias2 = 4;
+            p.i_out2 = 5;
+            nargs = 6;
+        }
         if (!a.need("ci", &p.ci) || !a.need("hi", &p.hi) || !a.need("wi", &p.wi) || !a.need("co", &p.co) ||
             !a.need("kh", &p.kh) || !a.need("kw", &p.kw) || !a.need("sh", &p.sh) || !a.need("sw", &p.sw) ||
             !a.need("ph", &p.ph) || !a.need("pw", &p.pw))
@@ -290,7 +300,12 @@ static int build_spec(const std::string& name, KernelSpec* s) {
         s->flops = 2.0 * p.co * (double)p.ktot * p.ptot;
         s->bytes = 4.0 * ((double)p.ci * p.hi * p.wi + (double)p.co * p.ktot + (double)p.co * p.ptot *
                           ((p.ep & EP_RES) ? 2.0 : 1.0) + p.co * ((p.ep & EP_GB) ? 2.0 : ((p.ep & EP_BIAS) ? 1.0 : 0.0)));
+        if (preact) s->bytes += 4.0 * ((double)p.co * p.ptot + p.co);
         int impl = (int)a.get("v", 0);
+        if (preact && (impl != 1 || p.ocs != p.co || p.ooff != 0)) {
+            set_error("reef_conv2d_add_preact exists as the tensor-core variant (_v1) with a dense output only: " + name);
+            return REEF_NOT_FOUND;
+        }
         if (impl == 0) {
             t.family = F_CONV_SIMT;
             p.tiles_p = ceil_div(p.ptot, CBM);

@@ -38,7 +38,7 @@ enum Family : int {
 };
 
 // epilogue / option bits
-enum : int { EP_RES = 1, EP_BIAS = 2, EP_GB = 4, EP_RELU = 8, EP_GELU = 16 };
+enum : int { EP_RES = 1, EP_BIAS = 2, EP_GB = 4, EP_RELU = 8, EP_GELU = 16, EP_DUAL = 32 };
 
 struct ConvP {
     int ci, hi, wi, co, kh, kw, sh, sw, ph, pw, ho, wo;
@@ -48,6 +48,7 @@ struct ConvP {
     int ep;                  // EP_* bits
     int i_res, i_bias, i_gamma, i_beta;   // positions in the arg list, -1 when absent
     int round_tf32;          // tensor-core variant: store activations rounded to the nearest TF32 value
+    int i_bias2, i_out2;     // EP_DUAL: second output out2 = relu(out + bias2) (the next unit's pre-activation)
 };
 
 struct PoolP {

@@ -91,7 +91,11 @@ class Builder:
     def conv(self, x: Tensor, co: int, k, stride=1, pad=0, *, weight=None,
              out_scale=None, in_scale=None, bias=None, relu=False,
              residual: Tensor | None = None, gamma_beta=None,
-             out: Tensor | None = None, nchw_in=False, w_gain: float = 1.0) -> Tensor:
+             out: Tensor | None = None, nchw_in=False, w_gain: float = 1.0, preact_bias=None):
+        """One convolution kernel.  With ``preact_bias`` (residual convolutions only) the next unit's
+        pre-activation relu(out + preact_bias) is produced as well and (out, act) is returned: by the same
+        launch where the tensor-core variant exists (reef_conv2d_add_preact), else by a fused_add_nn_relu
+        kernel behind the convolution, as in the reference's graphs."""
         kh, kw = (k, k) if isinstance(k, int) else k
         sh, sw = (stride, stride) if isinstance(stride, int) else stride
         ph, pw = (pad, pad) if isinstance(pad, int) else pad
@@ -133,6 +137,14 @@ class Builder:
         if out.cstride != co or out.coff:
             attrs["ocs"] = out.cstride
             attrs["ooff"] = out.coff
+        if preact_bias is not None:
+            assert op == "fused_nn_conv2d_add" and out.cstride == co and not out.coff
+            if self.pick_conv_impl("reef_conv2d_add_preact", attrs) == 1:
+                act = self.new_act(ho, wo, co)
+                args[1] = self.g.param(round_tf32(wgt))
+                args += [self.g.param(preact_bias), act.idx]
+                self.g.kernel(kname("reef_conv2d_add_preact", **attrs, v=1), args)
+                return out, act
         impl = self.pick_conv_impl(op, attrs)
         if impl:
             attrs["v"] = impl
@@ -142,6 +154,8 @@ class Builder:
             wgt = round_tf32(wgt)
         args[1] = self.g.param(wgt)
         self.g.kernel(kname(op, **attrs), args)
+        if preact_bias is not None:
+            return out, self.bias_relu(out, preact_bias)
         return out
 
     def pick_conv_impl(self, op, attrs) -> int:

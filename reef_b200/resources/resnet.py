@@ -65,7 +65,7 @@ def build_resnet(depth: int, *, name: str | None = None, image: int = 224, class
                 if last_unit:
                     sf, tf = b.bn(co)
                     final.update(gamma_beta=(sf, tf), relu=True)
-                x_new = b.conv(t, co, 3, 1, 1, w_gain=RES_BRANCH_GAIN, **final)
+                last = (t, co, 3, 1, 1)
             else:
                 mid = co // 4
                 s2, t2 = b.bn(mid)
@@ -77,11 +77,16 @@ def build_resnet(depth: int, *, name: str | None = None, image: int = 224, class
                 if last_unit:
                     sf, tf = b.bn(co)
                     final.update(gamma_beta=(sf, tf), relu=True)
-                x_new = b.conv(t_b, co, 1, 1, 0, w_gain=RES_BRANCH_GAIN, **final)
-            x_raw = x_new
-            if not last_unit:
+                last = (t_b, co, 1, 1, 0)
+            # the unit's last convolution adds the shortcut; the next unit's pre-activation relu(x + t/s) rides
+            # on its epilogue where the tensor-core variant exists (weights are drawn before that unit's BN, so
+            # both schedules hold the same model)
+            wgt = b.he_conv(co, last[2], last[2], last[0].c)
+            if last_unit:
+                x_raw = b.conv(*last, weight=wgt, w_gain=RES_BRANCH_GAIN, **final)
+            else:
                 s_n, t_n = b.bn(co)
-                act = b.bias_relu(x_raw, t_n / s_n)
+                x_raw, act = b.conv(*last, weight=wgt, w_gain=RES_BRANCH_GAIN, preact_bias=t_n / s_n, **final)
                 act_scale = s_n
 
     pooled = b.global_avg_pool(x_raw)

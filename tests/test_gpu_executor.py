@@ -93,6 +93,37 @@ def test_conv_tensor_core_parity(tmp_path, case):
     _conv_case(tmp_path, case, "_v1", TF32_TOL)
 
 
+@pytest.mark.parametrize("shape", [(256, 14, 14, 1024, 1), (64, 9, 11, 96, 3), (512, 7, 7, 2048, 1), (128, 28, 28, 128, 3)])
+def test_conv_preact_dual_output(tmp_path, shape):
+    """reef_conv2d_add_preact: conv + residual -> out, relu(out + bias2) -> out2 in one launch, against the
+    oracle's two reference kernels (fused_nn_conv2d_add, then fused_add_nn_relu), every flavour bit-identical."""
+    from gpu_util import TF32_TOL, all_storage
+    ci, hi, wi, co, k = shape
+    pad = k // 2
+    name = f"reef_conv2d_add_preact__ci{ci}_hi{hi}_wi{wi}_co{co}_kh{k}_kw{k}_sh1_sw1_ph{pad}_pw{pad}_v1"
+    specs = [("in", ci * hi * wi), ("param", co * k * k * ci), ("out", hi * wi * co), ("in", hi * wi * co),
+             ("param", co), ("out", hi * wi * co)]
+    base, inputs = single_kernel_model(tmp_path, "one", name, specs)
+    j = json.load(open(base + ".json"))
+    e = load_executor(base)
+    o = oracle.OracleExecutor(base + ".json", base + ".param")
+    for kk, v in inputs.items():
+        e.set_input(kk, v)
+        o.set_input(kk, v)
+    e.execute()
+    o.execute()
+    got = all_storage(e, j)
+    for idx in (2, 5):
+        err = rel_err(got[idx], o.storage[idx])
+        print(name, "storage", idx, "rel err", err)
+        assert err < TF32_TOL
+    assert capi.device_error() == 0
+    for f in ("execute_preemptable", "execute_dispatch", "execute_graph"):
+        getattr(e, f)()
+        again = all_storage(e, j)
+        assert np.array_equal(again[2], got[2]) and np.array_equal(again[5], got[5]), f
+
+
 @pytest.mark.parametrize("case", CONV_CASES, ids=[c[0][9:] + f"_{c[1]}x{c[4]}k{c[5]}{c[6]}s{c[7]}" for c in CONV_CASES])
 def test_conv_kernel_parity(tmp_path, case):
     _conv_case(tmp_path, case, "", FP32_TOL)

@@ -47,8 +47,8 @@ def run_graph(json_path: str, param_path: str | None, inputs: dict, double: bool
             ics, ioff = a.get("ics", a["c"]), a.get("ioff", 0)
             x = T(args[1]).reshape(a["n"], ics)[:, ioff:ioff + a["c"]]
             put(args[0], torch.relu(x + T(args[2])[None, :]))
-        elif op.startswith("fused_nn_conv2d"):
-            tail = op[len("fused_nn_conv2d"):]
+        elif op.startswith("fused_nn_conv2d") or op == "reef_conv2d_add_preact":
+            tail = "_add" if op == "reef_conv2d_add_preact" else op[len("fused_nn_conv2d"):]
             relu = tail.endswith("_nn_relu")
             if relu:
                 tail = tail[:-8]
@@ -77,6 +77,8 @@ def run_graph(json_path: str, param_path: str | None, inputs: dict, double: bool
             buf = T(args[2]).reshape(ho * wo, ocs).clone()
             buf[:, ooff:ooff + co] = y.reshape(ho * wo, co)
             put(args[2], buf)
+            if op == "reef_conv2d_add_preact":   # second output: the next unit's pre-activation
+                put(args[5], torch.relu(y.reshape(ho * wo, co) + T(args[4])[None, :]))
         elif op in ("fused_nn_max_pool2d", "fused_nn_max_pool2d_add_nn_relu", "fused_nn_avg_pool2d"):
             c, hi, wi = a["c"], a["hi"], a["wi"]
             ics, ioff = a.get("ics", c), a.get("ioff", 0)
