@@ -308,6 +308,11 @@ class REEFScheduler:
                                                name.encode()), "get_output")
         return out
 
+    def get_output_into(self, mid: int, out: np.ndarray, name: str = "output"):
+        """Copy the named tensor into ``out`` (a contiguous array of exactly the tensor's size in bytes)."""
+        _check(self._lib.reef_sched_get_output(self._h, C.c_uint32(mid), _buf(out), C.c_size_t(out.nbytes),
+                                               name.encode()), "get_output")
+
     def new_task(self, mid: int) -> int:
         tid = C.c_uint32()
         _check(self._lib.reef_sched_new_task(self._h, C.c_uint32(mid), C.byref(tid)), "new_task")
