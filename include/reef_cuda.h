@@ -105,6 +105,10 @@ REEF_API reef_status reef_module_get_kernel(reef_module_t mod, const char* name,
  * "launch_params" (reference: model.cpp:35-37) and the dynamic shared memory in bytes as stored in
  * "shared_memory".  Needs no GPU; the resource generator calls it so json and registry agree. */
 REEF_API reef_status reef_kernel_plan(const char* name, uint32_t dims[6], uint32_t* dyn_smem, int* num_args);
+/* Algorithmic work of one launch of a kernel name: floating-point operations and bytes that must move
+ * (weights + inputs + outputs (+ residual, + second output) + per-channel parameters), and whether the name
+ * selects the tensor-core kernel.  Needs no GPU; no reference counterpart (roofline bookkeeping). */
+REEF_API reef_status reef_kernel_cost(const char* name, double* flops, double* bytes, int* tensor_core);
 
 /* Binds a kernel handle to its device pointers ahead of the first launch (no reference counterpart): builds
  * the TMA tensor maps of tensor-core kernels and does every one-time allocation or attribute call, so

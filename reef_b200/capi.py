@@ -95,6 +95,13 @@ def kernel_plan(name: str):
     return list(dims), int(smem.value), int(nargs.value)
 
 
+def kernel_cost(name: str):
+    """(flops, bytes, tensor_core) of one launch of a kernel name; needs no GPU."""
+    fl, by, tc = C.c_double(), C.c_double(), C.c_int()
+    _check(cuda_lib().reef_kernel_cost(name.encode(), C.byref(fl), C.byref(by), C.byref(tc)), f"reef_kernel_cost({name})")
+    return fl.value, by.value, tc.value
+
+
 def plan_fn(name: str):
     d, s, _ = kernel_plan(name)
     return d, s

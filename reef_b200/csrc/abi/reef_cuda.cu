@@ -286,6 +286,15 @@ reef_status reef_kernel_plan(const char* name, uint32_t dims[6], uint32_t* dyn_s
     if (num_args) *num_args = s.nargs;
     return REEF_SUCC;
 }
+reef_status reef_kernel_cost(const char* name, double* flops, double* bytes, int* tensor_core) {
+    KernelSpec s;
+    int rc = plan_kernel(name, &s);
+    if (rc != REEF_SUCC) return (reef_status)rc;
+    if (flops) *flops = s.flops;
+    if (bytes) *bytes = s.bytes;
+    if (tensor_core) *tensor_core = s.tensor_core;
+    return REEF_SUCC;
+}
 reef_status reef_kernel_prepare(reef_kernel_t k, void** args) {
     if (!k || !args) return REEF_FAIL;
     return prepare_kernel(k->spec, args);

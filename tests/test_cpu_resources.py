@@ -132,3 +132,13 @@ def test_product_fails_loudly_without_gpu(libs):
         pytest.skip("a GPU is present")
     with pytest.raises(capi.ReefError):
         capi.HybridExecutor(0)
+
+
+def test_model_totals_match_the_published_architectures(libs, tmp_path):
+    """flops.py: ResNet-18 3.65 GFLOP / 46.8 MB of weights, ResNet-50 7.72 GFLOP / 102 MB at 224x224, batch 1."""
+    from reef_b200 import flops
+    t18 = flops.model_totals("resnet18", str(tmp_path))["totals"]
+    assert abs(t18["flops"] / 1e9 - 3.65) < 0.05 and abs(t18["weight_bytes"] / 1e6 - 46.8) < 0.5
+    t50 = flops.model_totals("resnet50", str(tmp_path))["totals"]
+    assert abs(t50["flops"] / 1e9 - 7.72) < 0.05 and abs(t50["weight_bytes"] / 1e6 - 102.1) < 0.5
+    assert t50["tensor_core_kernels"] == 52 and t50["hbm_floor_us_nominal"] > t50["tf32_floor_us_nominal"]
