@@ -98,7 +98,9 @@ public:
     // Timeline padding (tensor-core models).  Unit = one SM slot: an SM holds two tensor-core CTAs.
     //  window      real-time kernels ahead of the estimated position whose footprint bounds the padding
     //  depth       padded pieces queued per best-effort stream (hides the launch-to-completion latency)
-    //  overcommit  slots best-effort pieces may claim beyond what the real-time kernels leave free
+    //  overcommit  slots best-effort pieces may claim beyond what the real-time kernels leave free (default 100:
+    //              the parked prologue of the next real-time kernel is counted as a full footprint, but it
+    //              only needs its slots by the time the running kernel ends)
     //  quantum     pieces after which a best-effort queue drains and yields its place to the next queue
     void set_pad_window(int value) { pad_window = value < 1 ? 1 : value; }
     void set_pad_limits(int depth, int overcommit_slots, int quantum) {
@@ -219,10 +221,10 @@ private:
     bool rt_recent = false;
     std::chrono::steady_clock::time_point last_rt_finish;
     int pad_depth = 3;
-    int pad_overcommit = 0;
+    int pad_overcommit = 100;
     int pad_window = 8;
     int pad_quantum = 24;
-    double pad_target = 0.07;
+    double pad_target = 0.065;
     double pad_ratio_ema = 0.0;
     double pad_rate = 100.0;            // best-effort kernels per real-time window (controller state)
     // loop statistics of timeline_padding, printed at destruction when REEF_PAD_TRACE is set

@@ -54,7 +54,11 @@ static int tc_plan_cap(const ConvP& p, int cap, TcPlan* pl) {
     // split K over a cluster until about 128 CTAs are in flight, keeping >= 2 K blocks per CTA
     const int base = pl->m_tiles * pl->n_tiles;
     int s = 1;
-    while (s < TC_MAX_SPLITS && base * s * 2 <= 128 && pl->kb_total >= 2 * (s * 2)) s *= 2;
+    if (p.plan_splits > 0) {
+        while (s < p.plan_splits && s < TC_MAX_SPLITS && pl->kb_total >= s * 2) s *= 2;
+    } else {
+        while (s < TC_MAX_SPLITS && base * s * 2 <= 128 && pl->kb_total >= 2 * (s * 2)) s *= 2;
+    }
     // every rank must own at least one K block and the cluster size stays a power of two
     for (;; s /= 2) {
         pl->kb_per_split = ceil_div_i(pl->kb_total, s);
@@ -83,14 +87,22 @@ static int tc_plan_cap(const ConvP& p, int cap, TcPlan* pl) {
 }
 
 // ---- planning (needs no GPU) --------------------------------------------------------------------
-// Tile caps are tried from large to small; the first plan that fits shared memory and puts at least 48
-// CTAs in flight wins, else the feasible plan with the most CTAs (a batch-1 layer is latency-bound: more
-// CTAs shorten every CTA's load stream, at the price of re-reading weights from L2).
+// Default plan (names without a tuned plan): tile caps are tried from large to small; the first plan that fits
+// shared memory and puts at least 48 CTAs in flight wins, else the feasible plan with the most CTAs.  A batch-1
+// layer is bound by what one SM can pull from L2 (about 85 GB/s per CTA measured): more CTAs shorten every
+// CTA's load stream, at the price of re-reading weights from L2; where the balance lies depends on the shape
+// (ResNet's 14x14 layers are fastest at 112-128 CTAs, BERT's 128-token matmuls at 48-96), so the resource
+// generator writes measured plans into the kernel names (tp = tile cap, ts = K splits; reef_b200/tune.py).
 int tc_plan(const ConvP& p, TcPlan* pl) {
     if (p.nchw || (p.ci % TC_BK) != 0 || p.sh != p.sw || (p.sh != 1 && p.sh != 2)) return REEF_NOT_FOUND;
     if ((p.ics & 3) || (p.ioff & 3) || (p.ocs & 3) || (p.ooff & 3) || (p.co & 3)) return REEF_NOT_FOUND;
     if (p.kh * p.kw > 64) return REEF_NOT_FOUND;
-    static const int caps[] = {208, 160, 112, 96, 64, 32};
+    if (p.plan_cap > 0) {
+        // tile cap fixed by the kernel name (a tuned plan): that candidate or nothing
+        if (p.plan_cap < 8 || p.plan_cap > 208) return REEF_NOT_FOUND;
+        return tc_plan_cap(p, p.plan_cap, pl);
+    }
+    static const int caps[] = {208, 160, 112, 96, 64, 48, 32};
     TcPlan best;
     int best_ctas = 0;
     for (int cap : caps) {

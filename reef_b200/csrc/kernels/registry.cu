@@ -230,6 +230,8 @@ static int build_spec(const std::string& name, KernelSpec* s) {
         s->bytes = 4.0 * ((double)m * k + (double)n * k + (double)m * n * ((p.ep & EP_RES) ? 2.0 : 1.0) + n);
         if ((int)a.get("v", 0) == 1) {
             p.round_tf32 = (int)a.get("rt", 0);   // outputs feed LayerNorm / attention in fp32: no TF32 rounding
+            p.plan_cap = (int)a.get("tp", 0);
+            p.plan_splits = (int)a.get("ts", 0);
             if (tc_plan(p, &s->tc) != REEF_SUCC) goto bad;
             t.family = F_CONV_TC;
             t.nblocks = s->tc.splits * s->tc.n_tiles * s->tc.m_tiles;
@@ -317,6 +319,8 @@ static int build_spec(const std::string& name, KernelSpec* s) {
         if (impl == 1) {
             // tcgen05 TF32 implicit GEMM; "rt0" in the name keeps full fp32 bits in the stored activations
             p.round_tf32 = (int)a.get("rt", 1);
+            p.plan_cap = (int)a.get("tp", 0);       // tuned plan carried by the name: tile cap and K splits
+            p.plan_splits = (int)a.get("ts", 0);
             if (tc_plan(p, &s->tc) != REEF_SUCC) {
                 set_error("shape not supported by the tensor-core convolution: " + name);
                 return REEF_NOT_FOUND;
@@ -533,6 +537,23 @@ static const void* be_fn(int family) {
     }
 }
 
+// One-time, per device: every kernel asks for the same split of the SM's unified L1/shared array as the
+// tensor-core kernel (all of it as shared memory).  CTAs of kernels with different carve-outs cannot share an
+// SM: behind a tensor-core kernel that fills every SM, a kernel with another preference had to wait for whole
+// SMs to drain and be reconfigured (BERT-base replay 0.92 -> 1.13 ms with 216-CTA matmul plans).
+static bool g_carveout_set[16] = {false};
+static void prepare_carveout() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16 || g_carveout_set[dev]) return;
+    for (int f = 0; f < F_COUNT; f++) {
+        cudaFuncSetAttribute(plain_fn(f), cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(be_fn(f), cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    }
+    cudaFuncSetAttribute((const void*)k_dispatch, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaGetLastError();
+    g_carveout_set[dev] = true;
+}
+
 // Launch with the programmatic-stream-serialization attribute (REEF_PDL=0 turns it off): the kernel may be
 // scheduled while its predecessor in the stream still runs; all kernels here wait in their prologue.
 static cudaError_t launch_pdl(const void* fn, dim3 grid, dim3 block, void** kargs, uint32_t smem, cudaStream_t st) {
@@ -590,6 +611,7 @@ static int bind_tc(const KernelSpec& s, void** args) {
 }
 
 int prepare_kernel(const KernelSpec& s, void** args) {
+    prepare_carveout();
     if (s.task.family == F_CONV_TC) return bind_tc(s, args);
     return REEF_SUCC;
 }

@@ -49,6 +49,7 @@ struct ConvP {
     int i_res, i_bias, i_gamma, i_beta;   // positions in the arg list, -1 when absent
     int round_tf32;          // tensor-core variant: store activations rounded to the nearest TF32 value
     int i_bias2, i_out2;     // EP_DUAL: second output out2 = relu(out + bias2) (the next unit's pre-activation)
+    int plan_cap, plan_splits;   // tensor-core variant: tile cap / K splits fixed by the name (tp, ts), 0 = planner's choice
 };
 
 struct PoolP {

@@ -46,7 +46,8 @@ def _generator_stamp() -> str:
     import hashlib
     h = hashlib.sha256()
     here = os.path.dirname(os.path.abspath(__file__))
-    for f in sorted(glob.glob(os.path.join(here, "*.py"))):
+    h.update(os.environ.get("REEF_UNTUNED", "").encode())
+    for f in sorted(glob.glob(os.path.join(here, "*.py")) + glob.glob(os.path.join(here, "tuned_plans.json"))):
         with open(f, "rb") as fh:
             h.update(fh.read())
     stamp = os.path.join(os.path.dirname(here), "libreef_cuda.so.stamp")

@@ -20,7 +20,7 @@ from __future__ import annotations
 
 import numpy as np
 
-from .graph import Graph, kname
+from .graph import Graph, kname, tuned_plan
 from .layers import round_tf32
 
 
@@ -45,6 +45,7 @@ class _B:
             try:
                 capi.kernel_plan(kname(op, **attrs, v=1))
                 attrs["v"] = 1
+                attrs.update(tuned_plan(kname(op, **attrs)))
                 w = round_tf32(w)
             except capi.ReefError:
                 pass

@@ -40,6 +40,30 @@ def kname(op: str, **attrs: int) -> str:
     return op + "__" + "_".join(f"{k}{int(v)}" for k, v in attrs.items())
 
 
+_TUNED = None
+
+
+def tuned_plan(name: str) -> dict:
+    """Measured launch plan of a tensor-core kernel name ({} when the shape was never tuned): ``tp`` = pixel-tile
+    cap, ``ts`` = K splits, as written by ``python -m reef_b200.tune`` into ``tuned_plans.json`` beside this file.
+    The generators append them to the kernel name, so the plan is part of the schedule a ``<model>.json`` records."""
+    global _TUNED
+    if _TUNED is None:
+        import json
+        import os
+        path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tuned_plans.json")
+        _TUNED = json.load(open(path))["plans"] if os.path.exists(path) else {}
+    if os_environ_untuned():
+        return {}
+    hit = _TUNED.get(name)
+    return dict(tp=int(hit[0]), ts=int(hit[1])) if hit else {}
+
+
+def os_environ_untuned() -> bool:
+    import os
+    return os.environ.get("REEF_UNTUNED", "") not in ("", "0")
+
+
 def parse_kname(name: str):
     """Inverse of :func:`kname` -> (op, {key: int})."""
     if "__" not in name:

@@ -34,7 +34,7 @@ from __future__ import annotations
 
 import numpy as np
 
-from .graph import Graph, Tensor, kname
+from .graph import Graph, Tensor, kname, tuned_plan
 
 BN_EPS = 2e-5
 
@@ -143,7 +143,8 @@ class Builder:
                 act = self.new_act(ho, wo, co)
                 args[1] = self.g.param(round_tf32(wgt))
                 args += [self.g.param(preact_bias), act.idx]
-                self.g.kernel(kname("reef_conv2d_add_preact", **attrs, v=1), args)
+                full = kname("reef_conv2d_add_preact", **attrs, v=1)
+                self.g.kernel(kname("reef_conv2d_add_preact", **attrs, v=1, **tuned_plan(full)), args)
                 return out, act
         impl = self.pick_conv_impl(op, attrs)
         if impl:
@@ -152,6 +153,7 @@ class Builder:
             # already rounded to the nearest TF32 value, so the model in the .param file is exactly the
             # model the hardware multiplies with (and the oracle reads the same bytes)
             wgt = round_tf32(wgt)
+            attrs.update(tuned_plan(kname(op, **attrs)))
         args[1] = self.g.param(wgt)
         self.g.kernel(kname(op, **attrs), args)
         if preact_bias is not None:

@@ -172,3 +172,39 @@ def test_closed_loop_clients_rt_with_be(gen):
         assert r["completed"] > 0 and rel_err(r["output"], want) < FP32_TOL
     s.shutdown()
     s.close()
+
+
+def test_padding_segments_keep_best_effort_results_exact(gen, monkeypatch):
+    """Four best-effort ResNet-152 clients advance only as padding under a back-to-back real-time client
+    (padding segments, several pieces per stream, tasks completed inside the window): every client finishes
+    requests, most of them entirely by padding, and every output is bit-identical to an unpadded run."""
+    monkeypatch.setenv("REEF_PAD_TARGET", "0.5")      # a generous slowdown budget: pad as much as fits
+    base = gen("resnet152")
+    x = seeded_input(3 * 224 * 224, seed=21)
+    e = capi.HybridExecutor(0)
+    e.load_model_from_file(base + ".json", base + ".profile.json")
+    e.load_param_from_file(base + ".param")
+    e.set_input("data", x)
+    e.execute()
+    want = e.get_output().copy()
+    e.close()
+    s = S(S.REEF)
+    s.run()
+    rt = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
+    s.bind_model_queue(s.create_queue(S.RealTimeQueue), rt)
+    bes = []
+    for _ in range(4):
+        m = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
+        s.bind_model_queue(s.create_queue(S.BestEffortQueue), m)
+        bes.append(m)
+    res = s.run_clients([dict(mid=rt, max_requests=150, warmup=10, input=x)] +
+                        [dict(mid=m, max_requests=0, input=x) for m in bes])
+    st = s.stats()
+    print("padding stats", st, "be completed", [r["completed"] for r in res[1:]])
+    assert capi.device_error() == 0
+    assert np.array_equal(res[0]["output"], want)
+    for r in res[1:]:
+        assert r["completed"] > 0 and np.array_equal(r["output"], want)
+    assert st["padded_kernels"] > 1000 and st["be_tasks_padded_to_finish"] > 0
+    s.shutdown()
+    s.close()
