@@ -49,7 +49,7 @@ static int tc_plan_cap(const ConvP& p, int cap, TcPlan* pl) {
     pl->tmem_cols = 32;
     while (pl->tmem_cols < pl->n_mma) pl->tmem_cols *= 2;
     pl->m_tiles = ceil_div_i(p.co, TC_BM);
-    pl->cblocks = p.ci / TC_BK;
+    pl->cblocks = ceil_div_i(p.ci, TC_BK);   // a ragged last channel block reads zeros beyond Cin (TMA out-of-bounds fill)
     pl->kb_total = p.kh * p.kw * pl->cblocks;
     // split K over a cluster until about 128 CTAs are in flight, keeping >= 2 K blocks per CTA
     const int base = pl->m_tiles * pl->n_tiles;
@@ -94,7 +94,7 @@ static int tc_plan_cap(const ConvP& p, int cap, TcPlan* pl) {
 // (ResNet's 14x14 layers are fastest at 112-128 CTAs, BERT's 128-token matmuls at 48-96), so the resource
 // generator writes measured plans into the kernel names (tp = tile cap, ts = K splits; reef_b200/tune.py).
 int tc_plan(const ConvP& p, TcPlan* pl) {
-    if (p.nchw || (p.ci % TC_BK) != 0 || p.sh != p.sw || (p.sh != 1 && p.sh != 2)) return REEF_NOT_FOUND;
+    if (p.nchw || (p.ci & 3) || p.ci < 16 || p.sh != p.sw || (p.sh != 1 && p.sh != 2)) return REEF_NOT_FOUND;
     if ((p.ics & 3) || (p.ioff & 3) || (p.ocs & 3) || (p.ooff & 3) || (p.co & 3)) return REEF_NOT_FOUND;
     if (p.kh * p.kw > 64) return REEF_NOT_FOUND;
     if (p.plan_cap > 0) {
@@ -178,10 +178,12 @@ int tc_build_params(const ConvP& p, const TcPlan& pl, void* const* a, TcParams* 
     const float* in = (const float*)a[0];
     const float* wgt = (const float*)a[1];
     {
-        cuuint64_t dims[2] = {(cuuint64_t)p.ktot, (cuuint64_t)p.co};
-        cuuint64_t strides[1] = {(cuuint64_t)p.ktot * 4};
-        cuuint32_t box[2] = {TC_BK, TC_BM};
-        rc = encode(&P->tm_w, wgt, 2, dims, strides, box);
+        // weights [Cout][tap][Cin] as a 3-d map (Cin, taps, Cout): a box is 32 channels of one tap for 128 output
+        // channels, and channels beyond Cin (Cin not a multiple of 32) come back as zeros
+        cuuint64_t dims[3] = {(cuuint64_t)p.ci, (cuuint64_t)(p.kh * p.kw), (cuuint64_t)p.co};
+        cuuint64_t strides[2] = {(cuuint64_t)p.ci * 4, (cuuint64_t)p.ktot * 4};
+        cuuint32_t box[3] = {TC_BK, 1, TC_BM};
+        rc = encode(&P->tm_w, wgt, 3, dims, strides, box);
         if (rc != REEF_SUCC) return rc;
     }
     if (pl.spatial) {

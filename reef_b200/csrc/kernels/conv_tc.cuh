@@ -325,12 +325,18 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         // ---------------- TMA producer, part 1: fill the ring (no waits) ----------------
         const uint32_t tx = TC_A_BYTES + (uint32_t)P.b_bytes;
         const int first = nkb < NS ? nkb : NS;
+        // tap and channel block of a K block (2^32/1 does not fit the magic: one channel block per tap is a copy)
+        auto tap_of = [&](int kb) { return P.cblocks == 1 ? kb : (int)__umulhi((unsigned)kb, P.cb_magic); };
+        auto load_a = [&](int i) {   // weights: 32 channels of one tap for this tile's 128 output channels
+            const int s = i % NS, kb = kb_begin + i, tap = tap_of(kb), cb = kb - tap * P.cblocks;
+            tma_load_3d(base + s * stage_bytes, &P.tm_w, bar_full + 8 * s, cb * TC_BK, tap, m0);
+        };
         auto load_b = [&](int i) {
             const int s = i % NS;
             const uint32_t st = base + s * stage_bytes;
             const int kb = kb_begin + i;
-            // tap and channel block of this K block; the per-tap sub-lattice and offsets come from a host table
-            const int tap = P.cblocks == 1 ? kb : (int)__umulhi((unsigned)kb, P.cb_magic), cb = kb - tap * P.cblocks;   // 2^32/1 does not fit the magic
+            // the per-tap sub-lattice and offsets come from a host table
+            const int tap = tap_of(kb), cb = kb - tap * P.cblocks;
             if (P.spatial) {
                 tma_load_3d(st + TC_A_BYTES, &P.tm_x[P.tap_map[tap]], bar_full + 8 * s, cb * TC_BK,
                             tile_x * P.xw + P.tap_qx[tap], tile_y * P.rows + P.tap_qy[tap]);
@@ -344,7 +350,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             // on the previous kernel: they are requested before the dependency wait, activations after it.
             if (lane < first) {
                 mbar_expect_tx(bar_full + 8 * lane, tx);
-                tma_load_2d(base + lane * stage_bytes, &P.tm_w, bar_full + 8 * lane, (kb_begin + lane) * TC_BK, m0);
+                load_a(lane);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             // Only now may the next kernel of the stream begin its prologue (set-up, weight loads).  Released
@@ -365,7 +371,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
                 ok = mbar_wait(bar_empty + 8 * s, ((i / NS) - 1) & 1);
                 if (!ok) break;
                 mbar_expect_tx(bar_full + 8 * s, tx);
-                tma_load_2d(base + s * stage_bytes, &P.tm_w, bar_full + 8 * s, (kb_begin + i) * TC_BK, m0);
+                load_a(i);
                 load_b(i);
             }
             if (!ok) s_flags[1] = 1;

@@ -16,7 +16,7 @@ constexpr int TC_MAX_SPLITS = 8;
 constexpr int TC_SMEM_CAP = 112 * 1024;
 
 struct TcParams {
-    CUtensorMap tm_w;        // weights  dims (K, Cout), box (32, 128)
+    CUtensorMap tm_w;        // weights  dims (Cin, taps, Cout), box (32, 1, 128)
     CUtensorMap tm_x[4];     // activations, one per stride sub-lattice (ry*s + rx)
     float* out;
     const float* res;

@@ -84,6 +84,9 @@ TC_CASES = [
     ("fused_nn_conv2d_add_nn_relu", 160, 9, 13, 72, 5, 5, 1, 2, 2),
     ("fused_nn_conv2d_add_nn_relu", 64, 15, 15, 96, 3, 3, 2, 0, 0),
     ("fused_nn_conv2d_add_nn_relu", 32, 69, 69, 32, 3, 3, 1, 0, 0),      # one channel block per tap, prime output width
+    ("fused_nn_conv2d_add_nn_relu", 48, 35, 35, 64, 5, 5, 1, 2, 2),      # Cin not a multiple of 32: ragged last channel block
+    ("fused_nn_conv2d_add_nn_relu", 80, 19, 19, 192, 3, 3, 1, 0, 0),
+    ("fused_nn_conv2d_add", 20, 12, 12, 40, 1, 1, 1, 0, 0),              # a single ragged channel block
 ]
 
 
