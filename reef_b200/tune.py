@@ -31,6 +31,21 @@ SPLITS = (1, 2, 4, 8)
 DEFAULT_OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "resources", "tuned_plans.json")
 
 
+NOTE = ("written by python -m reef_b200.tune on one B200: plans = kernel name -> [tile cap tp, K splits ts], kept only "
+        "where the whole-model replay gets faster; measured_us = kernel name -> [default plan, best plan] microseconds "
+        "per launch on its own; models_ms = model -> [replay ms with default plans, with the kept plans, plans kept, "
+        "plans tried]")
+
+
+def _write_table(table: dict, path: str):
+    """One entry per line, sorted, so that a re-tune shows up as a readable diff."""
+    def block(name):
+        items = sorted(table.get(name, {}).items())
+        return f' "{name}": {{\n' + ",\n".join(f'  "{k}": {json.dumps(v)}' for k, v in items) + "\n }"
+    with open(path, "w") as f:
+        f.write('{\n "note": ' + json.dumps(NOTE) + ",\n" + ",\n".join(block(n) for n in ("models_ms", "plans", "measured_us")) + "\n}\n")
+
+
 def _arg_sizes(op: str, a: dict):
     """(input size, weight size, output size, [(role, size) of the remaining arguments]) in floats."""
     if op.startswith("reef_matmul_nt"):
@@ -132,8 +147,7 @@ def tune_models(models, out_path: str = DEFAULT_OUT, variant: str = ""):
             table["measured_us"][n] = [round(default_us, 3), round(us, 3)]
             if attrs:
                 table["plans"][n] = [attrs["tp"], attrs["ts"]]
-            with open(out_path, "w") as f:
-                json.dump(table, f, indent=0, sort_keys=True)
+            _write_table(table, out_path)
     return table
 
 
@@ -190,8 +204,7 @@ def verify_models(models, out_path: str = DEFAULT_OUT):
     del os.environ["REEF_UNTUNED"]
     table["plans"] = keep
     table["models_ms"] = report
-    with open(out_path, "w") as f:
-        json.dump(table, f, indent=0, sort_keys=True)
+    _write_table(table, out_path)
     return table
 
 
