@@ -198,7 +198,7 @@ __device__ __forceinline__ void tc_stamp(const TcParams& P, int slot) {
 template <int RB, int SMAX>
 __device__ __forceinline__ void tc_finish_split(const TcParams& P, const float* stage, const float* recv, int S, int split,
                                                 int jb, int je, int warp, int cbase, int co, int pix0, float4 sc, float4 sh,
-                                                float lo, bool rnd, bool gelu, bool has_res, float4 b2) {
+                                                float lo, bool rnd, bool gelu, bool has_res, float4 b2, const float4* rpre) {
     const float* src[SMAX];
 #pragma unroll
     for (int q = 0; q < SMAX; q++)
@@ -214,7 +214,7 @@ __device__ __forceinline__ void tc_finish_split(const TcParams& P, const float* 
 #pragma unroll
                 for (int q = 0; q < SMAX; q++)
                     if (q < S) part[u][q] = *reinterpret_cast<const float4*>(src[q] + (size_t)jr * TC_BM);
-                if (has_res) rv[u] = __ldg(reinterpret_cast<const float4*>(P.res + (size_t)(pix0 + jb + jr) * P.co + co));
+                if (has_res) rv[u] = (u < 2 && jbase == warp) ? rpre[u & 1] : __ldg(reinterpret_cast<const float4*>(P.res + (size_t)(pix0 + jb + jr) * P.co + co));
             }
         }
 #pragma unroll
@@ -363,6 +363,27 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         }
         __syncwarp();
 
+        // epilogue parameters of this lane's 4 output channels: model constants, requested right after the first loads so
+        // that their latency is long gone when the accumulator is ready
+        const int cbase = lane * 4;
+        const int co = m0 + cbase;
+        const bool cvalid = co < P.co;
+        float4 sc = make_float4(1.f, 1.f, 1.f, 1.f), sh = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 b2 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (cvalid) {
+            if (P.ep & TC_EP_GB) {
+                sc = __ldg(reinterpret_cast<const float4*>(P.gamma + co));
+                sh = __ldg(reinterpret_cast<const float4*>(P.beta + co));
+            } else if (P.ep & TC_EP_BIAS) {
+                sh = __ldg(reinterpret_cast<const float4*>(P.bias + co));
+            }
+            if (P.bias2 != nullptr) b2 = __ldg(reinterpret_cast<const float4*>(P.bias2 + co));
+        }
+        const float lo = (P.ep & TC_EP_RELU) ? 0.f : -__int_as_float(0x7f800000);
+        const bool has_res = (P.ep & TC_EP_RES) != 0;
+        const bool rnd = (P.ep & TC_EP_ROUND) != 0;
+        const bool gelu = (P.ep & TC_EP_GELU) != 0;
+
         if (warp == 0 && lane == 0) {
             // ---------------- TMA producer, part 2: refill stages as the MMAs release them ----------------
             bool ok = true;
@@ -398,6 +419,16 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         }
         __syncwarp();   // lanes 1..31 of the two role warps park here instead of spinning beside their lane 0
         if (warp != 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+        // the first two residual rows of this warp's pass over its pixel rows (rows jb + warp + 8u): requested now, used
+        // after the exchange
+        float4 rpre[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            rpre[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int jr = warp + 8 * u;
+            if (has_res && cvalid && jr < je - jb)
+                rpre[u] = __ldg(reinterpret_cast<const float4*>(P.res + (size_t)(pix0 + jb + jr) * P.co + co));
+        }
 
         // ---------------- epilogue: all eight warps ----------------
         bool ok = mbar_wait(bar_acc, 0);
@@ -468,24 +499,6 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         }
 
         if (tid == 0) tc_stamp(P, 8);   // exchange complete
-        const int cbase = lane * 4;                    // 4 channels of this lane
-        const int co = m0 + cbase;
-        const bool cvalid = co < P.co;
-        float4 sc = make_float4(1.f, 1.f, 1.f, 1.f), sh = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (cvalid) {
-            if (P.ep & TC_EP_GB) {
-                sc = *reinterpret_cast<const float4*>(P.gamma + co);
-                sh = *reinterpret_cast<const float4*>(P.beta + co);
-            } else if (P.ep & TC_EP_BIAS) {
-                sh = *reinterpret_cast<const float4*>(P.bias + co);
-            }
-        }
-        float4 b2 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (cvalid && P.bias2 != nullptr) b2 = *reinterpret_cast<const float4*>(P.bias2 + co);
-        const float lo = (P.ep & TC_EP_RELU) ? 0.f : -__int_as_float(0x7f800000);
-        const bool has_res = (P.ep & TC_EP_RES) != 0;
-        const bool rnd = (P.ep & TC_EP_ROUND) != 0;
-        const bool gelu = (P.ep & TC_EP_GELU) != 0;
         // Four pixel rows per warp are in flight at a time (all partial and residual loads issued before the
         // first use): with one or two warps per scheduler the loop is latency-bound, not bandwidth-bound.
         if (ok && cvalid) {
@@ -499,7 +512,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
                         rv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                         if (j < je) {
                             v[u] = *reinterpret_cast<const float4*>(stage + j * TC_BM + cbase);
-                            if (has_res) rv[u] = __ldg(reinterpret_cast<const float4*>(P.res + (size_t)(pix0 + j) * P.co + co));
+                            if (has_res) rv[u] = (u < 2 && jbase == jb + warp) ? rpre[u & 1] : __ldg(reinterpret_cast<const float4*>(P.res + (size_t)(pix0 + j) * P.co + co));
                         }
                     }
 #pragma unroll
@@ -519,10 +532,10 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             } else {
                 // partial of rank q for row j: own rows come from the staged tile, the others from recv[q]
                 if (S <= 4)
-                    tc_finish_split<4, 4>(P, stage, recv, S, split, jb, je, warp, cbase, co, pix0, sc, sh, lo, rnd, gelu, has_res, b2);
+                    tc_finish_split<4, 4>(P, stage, recv, S, split, jb, je, warp, cbase, co, pix0, sc, sh, lo, rnd, gelu, has_res, b2, rpre);
                 else
                     tc_finish_split<2, TC_MAX_SPLITS>(P, stage, recv, S, split, jb, je, warp, cbase, co, pix0, sc, sh, lo, rnd,
-                                                      gelu, has_res, b2);
+                                                      gelu, has_res, b2, rpre);
             }
         }
         if (S > 1) cluster_wait();      // barrier #2
