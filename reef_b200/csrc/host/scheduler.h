@@ -224,7 +224,7 @@ private:
     int pad_overcommit = 100;
     int pad_window = 8;
     int pad_quantum = 24;
-    double pad_target = 0.065;
+    double pad_target = 0.075;
     double pad_ratio_ema = 0.0;
     double pad_rate = 100.0;            // best-effort kernels per real-time window (controller state)
     // loop statistics of timeline_padding, printed at destruction when REEF_PAD_TRACE is set
