@@ -108,12 +108,13 @@ public:
         pad_overcommit = overcommit_slots;
         pad_quantum = quantum < 1 ? 1 : quantum;
     }
-    // Padding is throttled so that a padded real-time task takes at most (1 + value) times the model latency of
-    // its profile (measured alone).  What a best-effort kernel costs the real-time chain is close to a fixed
-    // time per kernel launch on the device, whatever its size, so the throttle is a rate: at most `pad_rate`
-    // best-effort kernels per real-time window, spread evenly over it; after every window the rate moves a step
-    // down when the smoothed ratio is above the target and a step up when it is below.  0 switches the
-    // controller off (no rate limit).
+    // Padding is throttled so that the slow tail of padded real-time tasks stays within (1 + value) times the
+    // task's latency alone: the controlled quantity is the 4th largest of the last 32 window-time / baseline
+    // ratios (about the 90th percentile; the 99th sits roughly one percent above it).  What a best-effort kernel
+    // costs the real-time chain is close to a fixed time per kernel launch on the device, whatever its size, so
+    // the throttle is a rate: at most `pad_rate` best-effort kernels per real-time window, spread evenly over
+    // it; after every window the rate moves a step down when the statistic is above the target and a smaller
+    // step up when it is below.  0 switches the controller off (no rate limit).
     void set_pad_slowdown_target(double value) { pad_target = value < 0 ? 0 : value; }
     // after a real-time task, poll its queue this long before best-effort work is resumed (0: not at all)
     void set_rt_grace_us(int value) { rt_grace_us = value < 0 ? 0 : value; }
@@ -224,8 +225,11 @@ private:
     int pad_overcommit = 100;
     int pad_window = 8;
     int pad_quantum = 24;
-    double pad_target = 0.075;
+    double pad_target = 0.09;
     double pad_ratio_ema = 0.0;
+    static const int kPadHistory = 32;
+    double pad_ratios[kPadHistory] = {0};   // window time / baseline of the last padded windows
+    uint32_t pad_ratio_count = 0;
     double pad_rate = 100.0;            // best-effort kernels per real-time window (controller state)
     // loop statistics of timeline_padding, printed at destruction when REEF_PAD_TRACE is set
     struct PadTrace {
