@@ -225,7 +225,7 @@ private:
     int pad_overcommit = 100;
     int pad_window = 8;
     int pad_quantum = 24;
-    double pad_target = 0.09;
+    double pad_target = 0.08;
     double pad_ratio_ema = 0.0;
     static const int kPadHistory = 32;
     double pad_ratios[kPadHistory] = {0};   // window time / baseline of the last padded windows
