@@ -802,7 +802,8 @@ void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
             for (int k = 0; k < 4; k++)
                 if (v > top[k]) std::swap(v, top[k]);
         }
-        const double tail = n >= 4 ? top[3] : top[0];
+        static const bool use_mean = getenv("REEF_PAD_MEAN") != nullptr;   // experiment: regulate the smoothed mean instead
+        const double tail = use_mean ? pad_ratio_ema : (n >= 4 ? top[3] : top[0]);
         if (tail > 1.0 + pad_target) pad_rate *= 0.97;
         else pad_rate *= 1.015;
         pad_rate = std::max(4.0, std::min(4096.0, pad_rate));

@@ -142,3 +142,36 @@ def test_model_totals_match_the_published_architectures(libs, tmp_path):
     t50 = flops.model_totals("resnet50", str(tmp_path))["totals"]
     assert abs(t50["flops"] / 1e9 - 7.72) < 0.05 and abs(t50["weight_bytes"] / 1e6 - 102.1) < 0.5
     assert t50["tensor_core_kernels"] == 52 and t50["hbm_floor_us_nominal"] > t50["tf32_floor_us_nominal"]
+
+
+def test_tuned_plan_table_is_consistent(libs):
+    """Every measured plan in the table resolves in the registry, keeps the family's argument count, and is what
+    the generator writes into the schedule; REEF_UNTUNED keeps the bare names."""
+    import json
+    import os
+    from reef_b200 import capi, resources, tune
+    from reef_b200.resources.graph import tuned_plan
+    path = os.path.join(os.path.dirname(resources.__file__), "tuned_plans.json")
+    table = json.load(open(path))
+    assert table["plans"], "the committed table holds the measured plans"
+    for name, (tp, ts) in table["plans"].items():
+        assert name in table["measured_us"] and table["measured_us"][name][1] <= table["measured_us"][name][0]
+        d0, _, n0 = capi.kernel_plan(name)
+        d1, smem, n1 = capi.kernel_plan(f"{name}_tp{tp}_ts{ts}")
+        assert n0 == n1 and smem <= 112 * 1024 and d1[3] == 256
+        assert tuned_plan(name) == dict(tp=tp, ts=ts)
+    # candidates(): the default plan first, then distinct (grid, shared memory) alternatives within 24..300 CTAs
+    c = tune.candidates("fused_nn_conv2d_add_nn_relu__ci256_hi14_wi14_co256_kh3_kw3_sh1_sw1_ph1_pw1_v1")
+    assert c[0][0] is None and len(c) > 4 and len({(g, s) for _, g, s in c[1:]}) == len(c) - 1
+    assert all(24 <= g[0] * g[1] <= 300 for _, g, _ in c[1:])
+    # the helper that sizes a timing model knows every tensor-core family
+    assert tune._arg_sizes("reef_matmul_nt_bias_gelu", dict(m=128, n=3072, k=768))[:3] == (128 * 768, 3072 * 768, 128 * 3072)
+    assert tune._arg_sizes("reef_conv2d_add_preact", dict(ci=64, hi=8, wi=8, co=128, kh=1, kw=1, sh=1, sw=1, ph=0, pw=0))[3] == \
+        [("temp", 64 * 128), ("param", 128), ("temp", 64 * 128)]
+
+
+def test_estimate_slot_usage(libs, tmp_path):
+    from reef_b200 import estimate, resources
+    d = resources.generate("resnet18_64", str(tmp_path))
+    r = estimate.estimate(d)
+    assert r["kernels"] > 20 and 0 < r["busy_pct"] <= r["busy_with_parked_successor_pct"] <= 100
