@@ -70,7 +70,7 @@ REEFScheduler::~REEFScheduler() {
                 "depth full %.1f, fully issued %.1f, no fit %.1f\n", (double)t.segments / t.calls, (double)t.singles / t.calls,
                 (double)t.q_empty / t.calls, (double)t.q_draining / t.calls, (double)t.q_full / t.calls,
                 (double)t.q_issued / t.calls, (double)t.q_nofit / t.calls);
-        fprintf(stderr, "[reef]   slowdown controller: tail target %.3f, smoothed mean ratio %.3f, rate %.1f kernels per window\n", pad_target,
+        fprintf(stderr, "[reef]   slowdown controller: target %.3f, smoothed ratio %.3f, rate %.1f kernels per window\n", pad_target,
                 pad_ratio_ema, pad_rate);
     }
     reef_gpu_init(device);
@@ -793,18 +793,7 @@ void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
         const double baseline = rt_model.alone_ns() > 0.0 ? rt_model.alone_ns() : 1.02 * model_ns;
         const double ratio = (double)window_ns / baseline;
         pad_ratio_ema = pad_ratio_ema == 0.0 ? ratio : 0.8 * pad_ratio_ema + 0.2 * ratio;
-        pad_ratios[pad_ratio_count++ % kPadHistory] = ratio;
-        // 4th largest of the history (fewer samples: the largest)
-        double top[4] = {0, 0, 0, 0};
-        const uint32_t n = std::min<uint32_t>(pad_ratio_count, kPadHistory);
-        for (uint32_t i = 0; i < n; i++) {
-            double v = pad_ratios[i];
-            for (int k = 0; k < 4; k++)
-                if (v > top[k]) std::swap(v, top[k]);
-        }
-        static const bool use_mean = getenv("REEF_PAD_MEAN") != nullptr;   // experiment: regulate the smoothed mean instead
-        const double tail = use_mean ? pad_ratio_ema : (n >= 4 ? top[3] : top[0]);
-        if (tail > 1.0 + pad_target) pad_rate *= 0.97;
+        if (pad_ratio_ema > 1.0 + pad_target) pad_rate *= 0.97;
         else pad_rate *= 1.015;
         pad_rate = std::max(4.0, std::min(4096.0, pad_rate));
     }

@@ -108,13 +108,14 @@ public:
         pad_overcommit = overcommit_slots;
         pad_quantum = quantum < 1 ? 1 : quantum;
     }
-    // Padding is throttled so that the slow tail of padded real-time tasks stays within (1 + value) times the
-    // task's latency alone: the controlled quantity is the 4th largest of the last 32 window-time / baseline
-    // ratios (about the 90th percentile; the 99th sits roughly one percent above it).  What a best-effort kernel
-    // costs the real-time chain is close to a fixed time per kernel launch on the device, whatever its size, so
-    // the throttle is a rate: at most `pad_rate` best-effort kernels per real-time window, spread evenly over
-    // it; after every window the rate moves a step down when the statistic is above the target and a smaller
-    // step up when it is below.  0 switches the controller off (no rate limit).
+    // Padding is throttled so that a padded real-time task takes on average (1 + value) times its latency alone
+    // (the tail follows: at 0.08 the 99th percentile measured 9.4 % above the unpadded one).  What a best-effort
+    // kernel costs the real-time chain is close to a fixed time per kernel launch on the device, whatever its
+    // size, so the throttle is a rate: at most `pad_rate` best-effort kernels per real-time window, spread evenly
+    // over it; after every window the rate moves a step down when the smoothed window-time / baseline ratio is
+    // above the target and a smaller step up when it is below.  (Regulating a tail statistic of the last 32
+    // windows instead made the rate oscillate and gave a wider tail for the same best-effort throughput.)
+    // 0 switches the controller off (no rate limit).
     void set_pad_slowdown_target(double value) { pad_target = value < 0 ? 0 : value; }
     // after a real-time task, poll its queue this long before best-effort work is resumed (0: not at all)
     void set_rt_grace_us(int value) { rt_grace_us = value < 0 ? 0 : value; }
@@ -227,9 +228,6 @@ private:
     int pad_quantum = 24;
     double pad_target = 0.08;
     double pad_ratio_ema = 0.0;
-    static const int kPadHistory = 32;
-    double pad_ratios[kPadHistory] = {0};   // window time / baseline of the last padded windows
-    uint32_t pad_ratio_count = 0;
     double pad_rate = 100.0;            // best-effort kernels per real-time window (controller state)
     // loop statistics of timeline_padding, printed at destruction when REEF_PAD_TRACE is set
     struct PadTrace {
