@@ -37,7 +37,7 @@ __device__ __forceinline__ bool body_mock(const KTask& t, int vb, unsigned char*
 
 // ---- fused_add on the NCHW model input (reference: resource/resnet152/resnet152.cu:771-773) ----
 // args: out, in, bias.  One vblock = 4096 consecutive elements of one plane-major tensor.
-constexpr int kEltPerBlock = 4096;
+constexpr int kEltPerBlock = 1024;   // one 128-bit access per thread: batch-1 tensors are small, parallelism beats reuse
 __device__ __forceinline__ bool body_fused_add_nchw(const KTask& t, int vb, unsigned char*, const int*) {
     const EltP& p = t.p.elt;
     float* out = (float*)t.a[0];
@@ -109,8 +109,8 @@ __device__ __forceinline__ bool body_copy(const KTask& t, int vb, unsigned char*
 // ---- pooling, channels-last ---------------------------------------------------------------------
 // max: pad value -3.402823e38, optional +bias, ReLU (reference: resource/resnet152/resnet152.cu:365-374)
 // avg: count-include-pad multiplies by 1/k^2 (reference: resource/inception/inception.cu:578-587)
-// args: in, out[, bias].  One thread = 4 channels of one output pixel; vblock = 256*4 such items.
-constexpr int kPoolItemsPerBlock = kThreads * 4;
+// args: in, out[, bias].  One thread = 4 channels of one output pixel; vblock = 256 such items.
+constexpr int kPoolItemsPerBlock = kThreads;
 template <bool MAX>
 __device__ __forceinline__ bool body_pool(const KTask& t, int vb, unsigned char*, const int*) {
     const PoolP& p = t.p.pool;
@@ -120,7 +120,7 @@ __device__ __forceinline__ bool body_pool(const KTask& t, int vb, unsigned char*
     const int c4 = p.c >> 2;
     const int total = p.ho * p.wo * c4;
 #pragma unroll 1
-    for (int it = 0; it < 4; it++) {
+    for (int it = 0; it < kPoolItemsPerBlock / kThreads; it++) {
         int i = vb * kPoolItemsPerBlock + it * kThreads + threadIdx.x;
         if (i >= total) break;
         int pix = i / c4, cc = (i - pix * c4) << 2;
