@@ -39,12 +39,16 @@ def _cxx() -> str:
 
 
 def _digest(files, flags) -> str:
+    """Hash of the sources and the command, with paths taken relative to the repository so that a tree that was
+    built in one place and copied to another (same sources, same compiler flags) is not rebuilt there."""
+    root = os.path.dirname(PKG)
+    rel = lambda s: s.replace(root, ".")
     h = hashlib.sha256()
-    for f in sorted(files):
-        h.update(f.encode())
+    for f in sorted(files, key=rel):
+        h.update(rel(f).encode())
         with open(f, "rb") as fh:
             h.update(fh.read())
-    h.update(" ".join(flags).encode())
+    h.update(" ".join(rel(x) for x in flags).encode())
     return h.hexdigest()
 
 
