@@ -61,7 +61,7 @@ REEFScheduler::~REEFScheduler() {
         const PadTrace& t = pad_trace;
         fprintf(stderr,
                 "[reef] timeline padding: %llu windows avg %.1f us (graph launch %.1f us), per window: %.1f iterations, "
-                "%.1f pieces (launch %.2f us, turnaround %.1f us), skipped: no slot %.1f, no SMs %.1f, no queue %.1f, tail %.1f\n",
+                "%.1f pieces (launch %.2f us, turnaround %.1f us), iterations skipped: rate-limited %.1f, no free slots %.1f, no queue could take a piece %.1f, unused %.1f\n",
                 (unsigned long long)t.calls, t.window_ns / 1e3 / t.calls, t.graph_launch_ns / 1e3 / t.calls,
                 (double)t.iters / t.calls, (double)t.launched / t.calls, t.launched ? t.launch_ns / 1e3 / t.launched : 0.0,
                 t.retired ? t.turnaround_ns / 1e3 / t.retired : 0.0, (double)t.no_slot / t.calls, (double)t.no_sms / t.calls,
