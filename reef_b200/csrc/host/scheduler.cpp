@@ -52,6 +52,8 @@ REEFScheduler::REEFScheduler(ScheduleMode _mode, int _device)
     if (const char* v = getenv("REEF_PAD_QUANTUM")) set_pad_limits(pad_depth, pad_overcommit, atoi(v));
     if (const char* v = getenv("REEF_PAD_WINDOW")) set_pad_window(atoi(v));
     if (const char* v = getenv("REEF_RT_GRACE_US")) set_rt_grace_us(atoi(v));
+    if (const char* v = getenv("REEF_PAD_PIECE_CAP")) pad_piece_cap = atoi(v);
+    if (const char* v = getenv("REEF_PAD_PIECE_MB")) pad_piece_bytes = atof(v) * 1e6;
     if (const char* v = getenv("REEF_PAD_TARGET")) set_pad_slowdown_target(atof(v));
 }
 
@@ -712,8 +714,11 @@ void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
                 issued + G <= allowed + G - 1) {
                 const int k0 = be_task->kernel_offset, k1 = std::min((int)be_exe.num_kernels(), k0 + G);
                 int seg_slots = 0;
-                for (int k = k0; k < k1; k++) seg_slots = std::max(seg_slots, slots_of(be_exe.trans_args[k], be_exe.trans_args[k].block_num));
-                if (seg_slots <= avail) {
+                for (int k = k0; k < k1; k++) {
+                    seg_slots = std::max(seg_slots, slots_of(be_exe.trans_args[k], be_exe.trans_args[k].block_num));
+                    if (pad_piece_bytes > 0 && be_exe.trans_args[k].resource.bytes > pad_piece_bytes) seg_slots = 1 << 30;   // goes out in ranges
+                }
+                if (seg_slots <= avail && (pad_piece_cap <= 0 || seg_slots <= pad_piece_cap)) {
                     if (be_task->start.time_since_epoch().count() == 0) be_task->start = std::chrono::system_clock::now();
                     if (be_exe.launch_pad_segment(k0 / G, q.stream) != Status::Succ) {
                         err_ = be_exe.error();
@@ -741,7 +746,24 @@ void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
                     continue;
                 }
             }
-            if (slots_of(be_args, blocks) > avail) {
+            const double kbytes = be_args.resource.bytes;
+            if (pad_piece_bytes > 0 && kbytes > pad_piece_bytes && be_args.block_num > 1) {
+                // a kernel that streams hundreds of megabytes (VGG-16's first dense layer: 411 MB) would hold
+                // the whole HBM bandwidth for its duration: it goes out in block ranges of bounded traffic, which
+                // the rate limit then spreads over the window
+                int cap_blocks = (int)(be_args.block_num * (pad_piece_bytes / kbytes));
+                cap_blocks -= cap_blocks % be_args.granularity;
+                cap_blocks = std::max(cap_blocks, be_args.granularity);
+                blocks = std::min(remaining, cap_blocks);
+                if (slots_of(be_args, blocks) > avail && (active > 0 || avail <= 0)) { pad_trace.q_nofit++; continue; }
+            } else if (pad_piece_cap > 0 && slots_of(be_args, blocks) > pad_piece_cap && avail >= pad_piece_cap) {
+                // a wide kernel goes out in block ranges of at most the cap: it then shares fewer SMs with the
+                // real-time kernels at any one time
+                blocks = be_args.resource.tensor_core ? pad_piece_cap : pad_piece_cap * 4;
+                blocks -= blocks % be_args.granularity;
+                if (blocks <= 0) blocks = be_args.granularity;
+                blocks = std::min(blocks, remaining);
+            } else if (slots_of(be_args, blocks) > avail) {
                 // the kernel does not fit whole: a partial piece only when nothing else is out (progress)
                 if (active > 0 || avail <= 0) { pad_trace.q_nofit++; continue; }
                 blocks = be_args.resource.tensor_core ? avail : avail * 4;
