@@ -401,8 +401,9 @@ def main():
     if rank == 0:
         line = {"metric": wl["metric"], "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
                 "config": {"workload": wl["desc"], "inputs": "seeded synthetic: images N(0,1), token ids uniform",
+                           "arithmetic": "convolutions and matmuls multiply in TF32 on tcgen05 with fp32 accumulation; everything else fp32",
                            "clients": "1 RT + %d BE per GPU" % n_be,
                            "l2": "every client owns a weight replica; the replicas streamed per pass exceed the 126 MB L2"},
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
