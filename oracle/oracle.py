@@ -77,6 +77,15 @@ def run_kernel(name: str, bufs: list, acc64: bool = False) -> None:
         fn(_p(bufs[0]), _p(bufs[1]), _p(bufs[2]), i32(64), i32(128))
     elif op == "fused_add":
         L.reef_oracle_fused_add_nchw(_p(bufs[0]), _p(bufs[1]), _p(bufs[2]), i32(a["c"]), i32(a["hw"]))
+    elif op == "reef_nchw_to_nhwc4":
+        # the reference's fused_add on the planar input (input + per-channel bias), written channels-last with
+        # 4 channels per pixel (the 4th zero): bufs = out [hw][4], in [c][hw], bias [c]
+        c, hw = a["c"], a["hw"]
+        planar = np.empty(c * hw, np.float32)
+        L.reef_oracle_fused_add_nchw(_p(planar), _p(bufs[1]), _p(bufs[2]), i32(c), i32(hw))
+        out = bufs[0].reshape(hw, 4)
+        out[:] = 0.0
+        out[:, :c] = planar.reshape(c, hw).T
     elif op == "fused_add_nn_relu":
         L.reef_oracle_fused_add_nn_relu(_p(bufs[0]), _p(bufs[1]), _p(bufs[2]), i32(a["c"]), i32(a["n"]),
                                         i32(a.get("ics", a["c"])), i32(a.get("ioff", 0)))

@@ -94,7 +94,7 @@ static int tc_plan_cap(const ConvP& p, int cap, TcPlan* pl) {
 // (ResNet's 14x14 layers are fastest at 112-128 CTAs, BERT's 128-token matmuls at 48-96), so the resource
 // generator writes measured plans into the kernel names (tp = tile cap, ts = K splits; reef_b200/tune.py).
 int tc_plan(const ConvP& p, TcPlan* pl) {
-    if (p.nchw || (p.ci & 3) || p.ci < 16 || p.sh != p.sw || (p.sh != 1 && p.sh != 2)) return REEF_NOT_FOUND;
+    if (p.nchw || (p.ci & 3) || p.ci < 4 || p.sh != p.sw || (p.sh != 1 && p.sh != 2)) return REEF_NOT_FOUND;
     if ((p.ics & 3) || (p.ioff & 3) || (p.ocs & 3) || (p.ooff & 3) || (p.co & 3)) return REEF_NOT_FOUND;
     if (p.kh * p.kw > 64) return REEF_NOT_FOUND;
     if (p.plan_cap > 0) {
@@ -215,7 +215,7 @@ int tc_build_params(const ConvP& p, const TcPlan& pl, void* const* a, TcParams* 
     P->bias2 = (p.ep & EP_DUAL) ? (const float*)a[p.i_bias2] : nullptr;
     rc = tc_error_word(&P->error_word);
     if (rc != REEF_SUCC) return rc;
-    P->co = p.co; P->ptot = p.ptot; P->ocs = p.ocs; P->ooff = p.ooff;
+    P->co = p.co; P->ci = p.ci; P->ptot = p.ptot; P->ocs = p.ocs; P->ooff = p.ooff;
     P->spatial = pl.spatial; P->wo = p.wo; P->rows = pl.rows; P->xsplit = pl.xsplit; P->xw = pl.xw;
     P->n_valid = pl.n_valid; P->n_mma = pl.n_mma; P->tmem_cols = pl.tmem_cols;
     P->kh = p.kh; P->kw = p.kw; P->stride = p.sh; P->ph = p.ph; P->pw = p.pw;

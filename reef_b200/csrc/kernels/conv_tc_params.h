@@ -29,7 +29,7 @@ struct TcParams {
     int* task_slot;
     int* error_word;         // device word set non-zero when a bounded wait expired
     long long* trace;        // optional: 16 SM-clock stamps of block (0,0) (phase trace), else nullptr
-    int co, ptot;
+    int co, ci, ptot;
     int ocs, ooff;
     int spatial;             // 0: flat [P][C] view, tile = n_valid consecutive pixels; 1: tile = rows x Wo
     int wo, rows;            // spatial: output width, rows per tile

@@ -107,6 +107,15 @@ static int build_spec(const std::string& name, KernelSpec* s) {
         s->bytes = 4.0 * (2.0 * p.c * p.n + p.c);
         return REEF_SUCC;
     }
+    if (op == "reef_nchw_to_nhwc4") {
+        EltP& p = t.p.elt;
+        if (!a.need("c", &p.c) || !a.need("hw", &p.n) || p.c < 1 || p.c > 4) goto bad;
+        t.family = F_NCHW_TO_NHWC4;
+        t.nblocks = ceil_div(p.n, kThreads);
+        s->nargs = 3;
+        s->bytes = 4.0 * ((double)p.c * p.n + 4.0 * p.n + p.c);
+        return REEF_SUCC;
+    }
     if (op == "fused_add_nn_relu") {
         EltP& p = t.p.elt;
         if (!a.need("c", &p.c) || !a.need("n", &p.n)) goto bad;
@@ -299,8 +308,10 @@ static int build_spec(const std::string& name, KernelSpec* s) {
         if ((p.co | p.ocs | p.ooff) & 3) goto bad;
         if (!p.nchw && (p.ci % CBK) == 0 && ((p.ics | p.ioff) & 3)) goto bad;
         s->nargs = nargs;
-        s->flops = 2.0 * p.co * (double)p.ktot * p.ptot;
-        s->bytes = 4.0 * ((double)p.ci * p.hi * p.wi + (double)p.co * p.ktot + (double)p.co * p.ptot *
+        // algorithmic work counts the real input channels (cr: the 3-channel model input is padded to 4)
+        const double cr = (double)a.get("cr", p.ci);
+        s->flops = 2.0 * p.co * (double)(p.kh * p.kw) * cr * p.ptot;
+        s->bytes = 4.0 * (cr * p.hi * p.wi + (double)p.co * p.kh * p.kw * cr + (double)p.co * p.ptot *
                           ((p.ep & EP_RES) ? 2.0 : 1.0) + p.co * ((p.ep & EP_GB) ? 2.0 : ((p.ep & EP_BIAS) ? 1.0 : 0.0)));
         if (preact) s->bytes += 4.0 * ((double)p.co * p.ptot + p.co);
         int impl = (int)a.get("v", 0);
@@ -365,6 +376,7 @@ __device__ __forceinline__ bool run_body(const KTask& t, int vb, unsigned char* 
     if (F == F_MOCK_ADD) return body_mock<false>(t, vb, smem, flag);
     if (F == F_MOCK_MUL) return body_mock<true>(t, vb, smem, flag);
     if (F == F_FUSED_ADD_NCHW) return body_fused_add_nchw(t, vb, smem, flag);
+    if (F == F_NCHW_TO_NHWC4) return body_nchw_to_nhwc4(t, vb, smem, flag);
     if (F == F_BIAS_RELU) return body_bias_relu(t, vb, smem, flag);
     if (F == F_CONV_SIMT) return body_conv_simt(t, vb, smem, flag);
     if (F == F_MAX_POOL) return body_pool<true>(t, vb, smem, flag);
@@ -384,6 +396,7 @@ __device__ __forceinline__ bool run_any(const KTask& t, int vb, unsigned char* s
         case F_MOCK_ADD: return run_body<F_MOCK_ADD>(t, vb, smem, flag);
         case F_MOCK_MUL: return run_body<F_MOCK_MUL>(t, vb, smem, flag);
         case F_FUSED_ADD_NCHW: return run_body<F_FUSED_ADD_NCHW>(t, vb, smem, flag);
+        case F_NCHW_TO_NHWC4: return run_body<F_NCHW_TO_NHWC4>(t, vb, smem, flag);
         case F_BIAS_RELU: return run_body<F_BIAS_RELU>(t, vb, smem, flag);
         case F_CONV_SIMT: return run_body<F_CONV_SIMT>(t, vb, smem, flag);
         case F_MAX_POOL: return run_body<F_MAX_POOL>(t, vb, smem, flag);
@@ -518,7 +531,8 @@ void add_launches(unsigned long long n) { g_launches += n; }
 
 #define FOR_EACH_FAMILY(X)                                                                      \
     X(F_MOCK_ADD) X(F_MOCK_MUL) X(F_FUSED_ADD_NCHW) X(F_BIAS_RELU) X(F_CONV_SIMT) X(F_MAX_POOL) \
-    X(F_AVG_POOL) X(F_GLOBAL_AVG_POOL) X(F_COPY) X(F_DENSE) X(F_SOFTMAX) X(F_EMBEDDING) X(F_LAYERNORM) X(F_ATTENTION)
+    X(F_AVG_POOL) X(F_GLOBAL_AVG_POOL) X(F_COPY) X(F_DENSE) X(F_SOFTMAX) X(F_EMBEDDING) X(F_LAYERNORM) X(F_ATTENTION) \
+    X(F_NCHW_TO_NHWC4)
 
 static const void* plain_fn(int family) {
     switch (family) {

@@ -61,6 +61,29 @@ __device__ __forceinline__ bool body_fused_add_nchw(const KTask& t, int vb, unsi
     return true;
 }
 
+// ---- model input for the tensor-core stem: planar NCHW (c <= 4) + per-channel bias -> channels-last with 4
+// channels per pixel (the missing ones zero), rounded to the nearest TF32 value.  The reference adds the bias
+// with its fused_add kernel on the planar tensor (resource/resnet152/resnet152.cu:771-773); the layout change
+// lets the first convolution run on the tensor cores (a 16-byte pixel is the smallest TMA element).
+// args: out [hw][4], in [c][hw], bias [c].  One thread = one pixel.
+__device__ __forceinline__ bool body_nchw_to_nhwc4(const KTask& t, int vb, unsigned char*, const int*) {
+    const EltP& p = t.p.elt;
+    float* out = (float*)t.a[0];
+    const float* in = (const float*)t.a[1];
+    const float* bias = (const float*)t.a[2];
+    const int i = vb * kThreads + threadIdx.x;
+    if (i < p.n) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int c = 0; c < p.c; c++) {
+            uint32_t u;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(in[(size_t)c * p.n + i] + bias[c]));
+            v[c] = __uint_as_float(u);
+        }
+        *reinterpret_cast<float4*>(out + (size_t)i * 4) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    return true;
+}
+
 // ---- fused_add_nn_relu, channels-last (reference: resource/resnet152/resnet152.cu:4056-4066) ---
 // args: out, in, bias.  out[p][c] = max(in[p*ics+ioff+c] + bias[c], 0); c, ics, ioff multiples of 4.
 __device__ __forceinline__ bool body_bias_relu(const KTask& t, int vb, unsigned char*, const int*) {

@@ -32,6 +32,7 @@ enum Family : int {
     F_EMBEDDING,
     F_LAYERNORM,
     F_ATTENTION,
+    F_NCHW_TO_NHWC4,
     F_COUNT,
     // families with their own __global__ kernel (not hosted by the 256-thread logical-block wrappers)
     F_CONV_TC = 100

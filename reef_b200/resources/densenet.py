@@ -23,9 +23,8 @@ def build_densenet(depth: int = 201, *, name: str | None = None, image: int = 22
     b = Builder(name or f"densenet{depth}", seed, conv_impl)
     g = b.g
     data = g.input("data", 3 * image * image)
-    x = Tensor(data, image, image, 3)
     s0, t0 = b.bn(64)
-    x = b.conv(x, 64, 7, 2, 3, out_scale=s0, bias=t0, relu=True, nchw_in=True)
+    x = b.stem_conv(data, 3, image, image, 64, 7, 2, 3, out_scale=s0, bias=t0, relu=True)
     x = b.pool(x, "max", 3, 2, 1)
     c = 64
     for bi, n_layers in enumerate(blocks):

@@ -26,7 +26,8 @@ def build_inception_v3(*, name: str = "inception_v3", image: int = 299, classes:
         return Tensor(g.temp(h * w * c), h, w, c)
 
     data = g.input("data", 3 * image * image)
-    x = cbr(Tensor(data, image, image, 3), 32, 3, 2, 0, nchw=True)
+    s_in, t_in = b.bn(32)
+    x = b.stem_conv(data, 3, image, image, 32, 3, 2, 0, out_scale=s_in, bias=t_in, relu=True)
     x = cbr(x, 32, 3)
     x = cbr(x, 64, 3, 1, 1)
     x = b.pool(x, "max", 3, 2, 0)

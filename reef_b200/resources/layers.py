@@ -52,6 +52,12 @@ class Builder:
         self.seed = int(seed)
         self._n = 0
         self.conv_impl = conv_impl
+        # "tc_stem" as conv_impl: also the first convolution goes to the tensor cores (4-channel channels-last
+        # input).  Measured slower than the CUDA-core stem (ResNet-152 replay 1.04 -> 1.09 ms): with 4 real
+        # channels per 32-channel K block the operand tiles are 7/8 zero fill, so it is not the default.
+        self.tc_stem = conv_impl == "tc_stem"
+        if self.tc_stem:
+            self.conv_impl = "auto"
 
     # ---- randomness ----------------------------------------------------
     def rng(self) -> np.random.Generator:
@@ -88,10 +94,44 @@ class Builder:
         self.g.kernel(kname("fused_add", c=c, hw=h * w), [out.idx, data_idx, b])
         return out
 
+    def input_nhwc4(self, data_idx: int, c: int, h: int, w: int, bias=None) -> Tensor:
+        """The planar model input (+ per-channel bias) as a channels-last tensor with 4 channels per pixel, the
+        layout the tensor-core convolution can read (the 4th channel is zero)."""
+        out = Tensor(self.g.temp(4 * h * w), h, w, 4)
+        b = self.g.param(np.zeros(c, np.float32) if bias is None else np.asarray(bias, np.float32))
+        self.g.kernel(kname("reef_nchw_to_nhwc4", c=c, hw=h * w), [out.idx, data_idx, b])
+        return out
+
+    def stem_conv(self, data_idx: int, c: int, h: int, w: int, co: int, k, stride, pad, *, input_bias=None, **kw) -> Tensor:
+        """First convolution of a CNN on the planar input `data` (optionally input + per-channel bias first).
+        Tensor-core schedules convert the input to 4-channel channels-last and pad the weights' input channels
+        with zeros; the exact-fp32 schedules keep the reference's planar convolution (and its fused_add)."""
+        kh, kw_ = (k, k) if isinstance(k, int) else k
+        sh = stride if isinstance(stride, int) else stride[0]
+        ph = pad if isinstance(pad, int) else pad[0]
+        wgt = kw.pop("weight", None)
+        if wgt is None:
+            wgt = self.he_conv(co, kh, kw_, c)
+        attrs4 = dict(ci=4, hi=h, wi=w, co=co, kh=kh, kw=kw_, sh=sh, sw=sh, ph=ph, pw=ph, cr=c)
+        op = "fused_nn_conv2d" + ("_add" if kw.get("bias") is not None else "") + ("_nn_relu" if kw.get("relu") else "")
+        if self.tc_stem and self.pick_conv_impl(op, attrs4) == 1:
+            in_scale = kw.pop("in_scale", None)
+            if in_scale is not None:
+                wgt = wgt * np.asarray(in_scale, np.float32)[None, None, None, :]
+            w4 = np.zeros((co, kh, kw_, 4), np.float32)
+            w4[..., :c] = wgt
+            x = self.input_nhwc4(data_idx, c, h, w, input_bias)
+            return self.conv(x, co, k, stride, pad, weight=w4, real_ci=c, **kw)
+        if input_bias is not None:
+            x = self.input_bias_nchw(data_idx, c, h, w, input_bias)
+        else:
+            x = Tensor(data_idx, h, w, c)
+        return self.conv(x, co, k, stride, pad, weight=wgt, nchw_in=True, **kw)
+
     def conv(self, x: Tensor, co: int, k, stride=1, pad=0, *, weight=None,
              out_scale=None, in_scale=None, bias=None, relu=False,
              residual: Tensor | None = None, gamma_beta=None,
-             out: Tensor | None = None, nchw_in=False, w_gain: float = 1.0, preact_bias=None):
+             out: Tensor | None = None, nchw_in=False, w_gain: float = 1.0, preact_bias=None, real_ci=None):
         """One convolution kernel.  With ``preact_bias`` (residual convolutions only) the next unit's
         pre-activation relu(out + preact_bias) is produced as well and (out, act) is returned: by the same
         launch where the tensor-core variant exists (reef_conv2d_add_preact), else by a fused_add_nn_relu
@@ -131,6 +171,8 @@ class Builder:
         attrs = dict(ci=ci, hi=x.h, wi=x.w, co=co, kh=kh, kw=kw, sh=sh, sw=sw, ph=ph, pw=pw)
         if nchw_in:
             attrs["nchw"] = 1
+        if real_ci is not None and real_ci != ci:
+            attrs["cr"] = real_ci      # channels that carry data (the rest is zero padding): roofline bookkeeping
         if x.cstride != ci or x.coff:
             attrs["ics"] = x.cstride
             attrs["ioff"] = x.coff

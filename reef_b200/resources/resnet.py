@@ -40,9 +40,9 @@ def build_resnet(depth: int, *, name: str | None = None, image: int = 224, class
 
     # BN on the input image: scale folds into the stem weights, shift stays as a bias op.
     s0, t0 = b.bn(3)
-    x0 = b.input_bias_nchw(data, 3, image, image, t0 / s0)
     s_stem, t_stem = b.bn(widths[0])
-    x1 = b.conv(x0, widths[0], 7, 2, 3, in_scale=s0, out_scale=s_stem, bias=t_stem, relu=True, nchw_in=True)
+    x1 = b.stem_conv(data, 3, image, image, widths[0], 7, 2, 3, input_bias=t0 / s0, in_scale=s0, out_scale=s_stem,
+                     bias=t_stem, relu=True)
 
     # first unit's pre-activation BN rides on the max-pool (positive scale commutes with max and ReLU)
     s_pre, t_pre = b.bn(widths[0])

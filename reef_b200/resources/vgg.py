@@ -26,7 +26,10 @@ def build_vgg16(*, name: str = "vgg16", image: int = 224, classes: int = 1000, s
             x = b.pool(x, "max", 2, 2, 0)
             continue
         bias = b.rng().normal(0.0, 0.05, v).astype(np.float32)
-        x = b.conv(x, v, 3, 1, 1, bias=bias, relu=True, nchw_in=first)
+        if first:
+            x = b.stem_conv(data, 3, image, image, v, 3, 1, 1, bias=bias, relu=True)
+        else:
+            x = b.conv(x, v, 3, 1, 1, bias=bias, relu=True)
         first = False
     flat = b.flatten(x)
     h = b.dense(flat, fc, relu=True)

@@ -127,6 +127,31 @@ def test_conv_preact_dual_output(tmp_path, shape):
         assert np.array_equal(again[2], got[2]) and np.array_equal(again[5], got[5]), f
 
 
+def test_tensor_core_stem_variant(tmp_path):
+    """conv_impl="tc_stem": reef_nchw_to_nhwc4 (input + bias, planar -> 4-channel channels-last) feeds a 4-channel
+    tensor-core stem convolution (ragged channel blocks are zero-filled by TMA); every buffer against the oracle."""
+    from reef_b200 import resources
+    d = resources.generate("resnet18_64", str(tmp_path), conv_impl="tc_stem")
+    base = d + "/resnet18_64"
+    j = json.load(open(base + ".json"))
+    names = [k["name"] for k in j["kernels"]]
+    assert names[0].startswith("reef_nchw_to_nhwc4__c3") and "_ci4_" in names[1] and names[1].endswith("_v1")
+    x = seeded_input(3 * 64 * 64, seed=5)
+    e = load_executor(base)
+    o = oracle.OracleExecutor(base + ".json", base + ".param")
+    e.set_input("data", x)
+    o.set_input("data", x)
+    e.execute()
+    o.execute()
+    worst = compare_layers(e, o, j, lambda n: TF32_TOL)
+    print("tc_stem worst layer", worst)
+    assert capi.device_error() == 0
+    raw = e.get_output().copy()
+    for f in ("execute_preemptable", "execute_dispatch", "execute_graph"):
+        getattr(e, f)()
+        assert np.array_equal(e.get_output(), raw), f
+
+
 @pytest.mark.parametrize("case", CONV_CASES, ids=[c[0][9:] + f"_{c[1]}x{c[4]}k{c[5]}{c[6]}s{c[7]}" for c in CONV_CASES])
 def test_conv_kernel_parity(tmp_path, case):
     _conv_case(tmp_path, case, "", FP32_TOL)

@@ -43,6 +43,11 @@ def run_graph(json_path: str, param_path: str | None, inputs: dict, double: bool
         elif op == "fused_add":
             x = T(args[1]).reshape(a["c"], a["hw"])
             put(args[0], x + T(args[2])[:, None])
+        elif op == "reef_nchw_to_nhwc4":
+            x = T(args[1]).reshape(a["c"], a["hw"]) + T(args[2])[:, None]
+            y = torch.zeros(a["hw"], 4, dtype=x.dtype)
+            y[:, :a["c"]] = x.T
+            put(args[0], y)
         elif op == "fused_add_nn_relu":
             ics, ioff = a.get("ics", a["c"]), a.get("ioff", 0)
             x = T(args[1]).reshape(a["n"], ics)[:, ioff:ioff + a["c"]]
