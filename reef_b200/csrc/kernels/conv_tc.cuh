@@ -327,12 +327,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         const int first = nkb < NS ? nkb : NS;
         // tap and channel block of a K block (2^32/1 does not fit the magic: one channel block per tap is a copy)
         auto tap_of = [&](int kb) { return P.cblocks == 1 ? kb : (int)__umulhi((unsigned)kb, P.cb_magic); };
-        auto load_a = [&](int i) {   // weights: 32 channels of one tap for this tile's 128 output channels
-            const int s = i % NS, kb = kb_begin + i, tap = tap_of(kb), cb = kb - tap * P.cblocks;
+        auto load_a = [&](int i, int s) {   // weights: 32 channels of one tap for this tile's 128 output channels
+            const int kb = kb_begin + i, tap = tap_of(kb), cb = kb - tap * P.cblocks;
             tma_load_3d(base + s * stage_bytes, &P.tm_w, bar_full + 8 * s, cb * TC_BK, tap, m0);
         };
-        auto load_b = [&](int i) {
-            const int s = i % NS;
+        auto load_b = [&](int i, int s) {
             const uint32_t st = base + s * stage_bytes;
             const int kb = kb_begin + i;
             // the per-tap sub-lattice and offsets come from a host table
@@ -350,7 +349,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             // on the previous kernel: they are requested before the dependency wait, activations after it.
             if (lane < first) {
                 mbar_expect_tx(bar_full + 8 * lane, tx);
-                load_a(lane);
+                load_a(lane, lane);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             // Only now may the next kernel of the stream begin its prologue (set-up, weight loads).  Released
@@ -358,7 +357,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             // in this order at most two grids of a chain are resident and the other SM slots stay free for
             // best-effort kernels.  One thread per CTA executing the instruction counts for the CTA.
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-            if (lane < first) load_b(lane);
+            if (lane < first) load_b(lane, lane);
             if (lane == 0) tc_stamp(P, 2);   // ring filled (loads issued)
         }
         __syncwarp();
@@ -386,27 +385,33 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
 
         if (warp == 0 && lane == 0) {
             // ---------------- TMA producer, part 2: refill stages as the MMAs release them ----------------
+            // (stage index and phase parity are carried along: a division by the runtime ring depth per K block
+            // is dozens of cycles on this single thread's critical path)
             bool ok = true;
+            int s = first == NS ? 0 : first;      // first < NS only when nkb < NS, and then this loop does not run
+            uint32_t par = 0;                      // parity of the "empty" phase awaited: ((i / NS) - 1) & 1
             for (int i = first; i < nkb && ok; i++) {
-                const int s = i % NS;
-                ok = mbar_wait(bar_empty + 8 * s, ((i / NS) - 1) & 1);
+                ok = mbar_wait(bar_empty + 8 * s, par);
                 if (!ok) break;
                 mbar_expect_tx(bar_full + 8 * s, tx);
-                load_a(i);
-                load_b(i);
+                load_a(i, s);
+                load_b(i, s);
+                if (++s == NS) { s = 0; par ^= 1u; }
             }
             if (!ok) s_flags[1] = 1;
         } else if (warp == 1 && lane == 0) {
             // ---------------- MMA issuer ----------------
             bool ok = true;
             const uint32_t idesc = umma_idesc_tf32(P.n_mma);
+            const bool tr = P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+            int s = 0;
+            uint32_t par = 0;
             for (int i = 0; i < nkb && ok; i++) {
-                const int s = i % NS;
                 const uint32_t st = base + s * stage_bytes;
-                ok = mbar_wait(bar_full + 8 * s, (i / NS) & 1);
+                ok = mbar_wait(bar_full + 8 * s, par);
                 if (!ok) break;
-                if (i == 0) tc_stamp(P, 4);          // first K block landed
-                if (i == nkb - 1) tc_stamp(P, 5);    // last K block landed
+                if (tr && i == 0) P.trace[4] = clock64();          // first K block landed
+                if (tr && i == nkb - 1) P.trace[5] = clock64();    // last K block landed
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t da = umma_desc_sw128(st), db = umma_desc_sw128(st + TC_A_BYTES);
                 // one tcgen05.mma covers K = 8 tf32 = 32 bytes.  (Skipping the steps of a ragged last channel block
@@ -415,6 +420,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
                 for (int k = 0; k < TC_BK / 8; k++)
                     umma_tf32(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
                 umma_commit(bar_empty + 8 * s);   // frees the stage once these MMAs have read it
+                if (++s == NS) { s = 0; par ^= 1u; }
             }
             if (ok) umma_commit(bar_acc);
             else s_flags[1] = 1;
