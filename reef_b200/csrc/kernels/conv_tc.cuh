@@ -347,9 +347,20 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             // one lane per stage: issuing a load costs a few hundred cycles of address arithmetic and
             // descriptor traffic, so the ring is filled by up to eight lanes at once.  Weights do not depend
             // on the previous kernel: they are requested before the dependency wait, activations after it.
+            // coordinates of this lane's activation load: worked out before the dependency wait, so that after it
+            // only the copy instruction itself is left on the critical path
+            const CUtensorMap* bmap = &P.tm_x[0];
+            int bc0 = 0, bc1 = tile_n * P.n_valid, bc2 = 0;
             if (lane < first) {
                 mbar_expect_tx(bar_full + 8 * lane, tx);
                 load_a(lane, lane);
+                const int kb = kb_begin + lane, tap = tap_of(kb);
+                bc0 = (kb - tap * P.cblocks) * TC_BK;
+                if (P.spatial) {
+                    bmap = &P.tm_x[P.tap_map[tap]];
+                    bc1 = tile_x * P.xw + P.tap_qx[tap];
+                    bc2 = tile_y * P.rows + P.tap_qy[tap];
+                }
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             // Only now may the next kernel of the stream begin its prologue (set-up, weight loads).  Released
@@ -357,7 +368,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             // in this order at most two grids of a chain are resident and the other SM slots stay free for
             // best-effort kernels.  One thread per CTA executing the instruction counts for the CTA.
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-            if (lane < first) load_b(lane, lane);
+            if (lane < first) {
+                const uint32_t bdst = base + lane * stage_bytes + TC_A_BYTES;
+                if (P.spatial) tma_load_3d(bdst, bmap, bar_full + 8 * lane, bc0, bc1, bc2);
+                else tma_load_2d(bdst, bmap, bar_full + 8 * lane, bc0, bc1);
+            }
             if (lane == 0) tc_stamp(P, 2);   // ring filled (loads issued)
         }
         __syncwarp();
