@@ -33,6 +33,10 @@ sys.path.insert(0, ROOT)
 UNIT = "inf/s"
 # BASELINE.json configs; "c2" is the configuration the headline metric is quoted on and the default
 WORKLOADS = {
+    "c0": dict(metric="resnet18_b1_inferences_per_s_rt_only", rt="resnet18", be=[],
+               desc="configs[0]: ResNet-18 b1, single RT client, no contention"),
+    "c1": dict(metric="resnet152_b1_inferences_per_s_rt_only", rt="resnet152", be=[],
+               desc="configs[1]: ResNet-152 b1, RT-only closed-loop requests"),
     "c2": dict(metric="resnet152_b1_inferences_per_s_rt_plus_4be", rt="resnet152", be=["resnet152"] * 4,
                desc="configs[2]: ResNet-152 b1 RT client back-to-back + 4 BE ResNet-152 b1 closed-loop clients, REEF mode"),
     "c3": dict(metric="inception_v3_b1_inferences_per_s_rt_plus_vgg16_densenet201_be", rt="inception_v3",
@@ -238,12 +242,13 @@ def main():
     s.shutdown(); s.close()
 
     # ---- phase B: BE alone ---------------------------------------------------------------------
-    s, ids = make_sched(n_be, rt=False)
-    be_req = max(20, args.steps // 8)
-    rs = s.run_clients([dict(mid=m, max_requests=be_req, warmup=max(3, args.warmup // 8), want_output=False)
-                        for m in ids["be"]])
-    extra["be_alone_inf_s"] = sum(r["completed"] / r["elapsed_s"] for r in rs)
-    s.shutdown(); s.close()
+    if n_be:
+        s, ids = make_sched(n_be, rt=False)
+        be_req = max(20, args.steps // 8)
+        rs = s.run_clients([dict(mid=m, max_requests=be_req, warmup=max(3, args.warmup // 8), want_output=False)
+                            for m in ids["be"]])
+        extra["be_alone_inf_s"] = sum(r["completed"] / r["elapsed_s"] for r in rs)
+        s.shutdown(); s.close()
 
     # ---- phase C (timed region of `value`): RT + 4 BE, inputs resident in HBM --------------------
     s, ids = make_sched(n_be)
@@ -275,34 +280,35 @@ def main():
                   "device_event_ms_incl_warmup": ev0.elapsed_time(ev1), "be_stream_cap": args.be_cap})
     s.shutdown(); s.close()
 
-    # ---- phase D1: reset-based preemption.  The RT client pauses 2 ms between requests, so the BE clients run
-    # at full speed on their own streams and every RT arrival preempts them (under a back-to-back RT client the
-    # BE tasks only advance as padding and there is nothing to preempt).  Latency = flag raised + tasks rolled
-    # back, as the scheduler measures it (reference: scheduler.cpp:305-346).
-    s, ids = make_sched(n_be)
-    clients = [dict(mid=ids["rt"], max_requests=max(100, args.steps // 3), warmup=5, want_output=False, think_us=2000)] + \
-              [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
-    rs = s.run_clients(clients)
-    st = s.stats()
-    extra["preempt_avg_us"] = st["preempt_ns_sum"] / max(1, st["preempt_count"]) / 1e3
-    extra["preempt_max_us"] = st["preempt_ns_max"] / 1e3
-    extra["preempt_count"] = st["preempt_count"]
-    extra["rt_after_preempt_p50_ms"] = pct(rs[0]["latencies_ms"], 50)
-    extra["rt_after_preempt_p99_ms"] = pct(rs[0]["latencies_ms"], 99)
-    extra["be_inf_s_rt_every_2ms"] = sum(r["completed"] / r["elapsed_s"] for r in rs[1:] if r["elapsed_s"] > 0)
-    s.shutdown(); s.close()
+    if n_be:
+        # ---- phase D1: reset-based preemption.  The RT client pauses 2 ms between requests, so the BE clients run
+        # at full speed on their own streams and every RT arrival preempts them (under a back-to-back RT client the
+        # BE tasks only advance as padding and there is nothing to preempt).  Latency = flag raised + tasks rolled
+        # back, as the scheduler measures it (reference: scheduler.cpp:305-346).
+        s, ids = make_sched(n_be)
+        clients = [dict(mid=ids["rt"], max_requests=max(100, args.steps // 3), warmup=5, want_output=False, think_us=2000)] + \
+                  [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
+        rs = s.run_clients(clients)
+        st = s.stats()
+        extra["preempt_avg_us"] = st["preempt_ns_sum"] / max(1, st["preempt_count"]) / 1e3
+        extra["preempt_max_us"] = st["preempt_ns_max"] / 1e3
+        extra["preempt_count"] = st["preempt_count"]
+        extra["rt_after_preempt_p50_ms"] = pct(rs[0]["latencies_ms"], 50)
+        extra["rt_after_preempt_p99_ms"] = pct(rs[0]["latencies_ms"], 99)
+        extra["be_inf_s_rt_every_2ms"] = sum(r["completed"] / r["elapsed_s"] for r in rs[1:] if r["elapsed_s"] > 0)
+        s.shutdown(); s.close()
 
-    # ---- phase D2: preemption latency with drain (flag set -> BE streams idle -> counters read) ----
-    s, ids = make_sched(n_be)
-    s.set_wait_sync(True)
-    clients = [dict(mid=ids["rt"], max_requests=max(50, args.steps // 10), warmup=5, want_output=False, think_us=2000)] + \
-              [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
-    s.run_clients(clients)
-    st = s.stats()
-    extra["preempt_drain_avg_us"] = st["preempt_ns_sum"] / max(1, st["preempt_count"]) / 1e3
-    extra["preempt_drain_max_us"] = st["preempt_ns_max"] / 1e3
-    extra["preempt_drain_count"] = st["preempt_count"]
-    s.shutdown(); s.close()
+        # ---- phase D2: preemption latency with drain (flag set -> BE streams idle -> counters read) ----
+        s, ids = make_sched(n_be)
+        s.set_wait_sync(True)
+        clients = [dict(mid=ids["rt"], max_requests=max(50, args.steps // 10), warmup=5, want_output=False, think_us=2000)] + \
+                  [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
+        s.run_clients(clients)
+        st = s.stats()
+        extra["preempt_drain_avg_us"] = st["preempt_ns_sum"] / max(1, st["preempt_count"]) / 1e3
+        extra["preempt_drain_max_us"] = st["preempt_ns_max"] / 1e3
+        extra["preempt_drain_count"] = st["preempt_count"]
+        s.shutdown(); s.close()
 
     # ---- phase E (e2e): same workload through the request calls with pinned host buffers ---------
     s, ids = make_sched(n_be)
