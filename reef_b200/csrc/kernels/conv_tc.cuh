@@ -155,11 +155,15 @@ enum : int { TC_EP_RES = 1, TC_EP_BIAS = 2, TC_EP_GB = 4, TC_EP_RELU = 8, TC_EP_
 
 // Branch-free form of (+residual) (+bias | *gamma+beta) (ReLU): r = 0, sc = 1, sh = 0, lo = -inf stand in for
 // the absent terms (v + 0 and fma(v, 1, b) are exact, so this equals the conditional form bit for bit).
+// exact-erf GELU (reference: resource/bert/bert.cu:167-173).  Not inlined on purpose: inlined, the compiler turned
+// the uniform `if (gelu)` of the epilogue into straight-line code and every layer paid for erff on each element
+// (0.5 us per launch on the row-finishing loop).
+__device__ __noinline__ float tc_gelu(float v) { return v * (0.5f * erff(v * 0.70710678118654752440f) + 0.5f); }
+
 __device__ __forceinline__ float tc_epilogue(float v, float r, float sc, float sh, float lo, bool rnd, bool gelu = false) {
     if (gelu) {
-        // matmul + bias -> exact-erf GELU -> (+residual)   (reference: resource/bert/bert.cu:167-173)
-        v = v + sh;
-        v = v * (0.5f * erff(v * 0.70710678118654752440f) + 0.5f) + r;
+        // matmul + bias -> GELU -> (+residual)
+        v = tc_gelu(v + sh) + r;
     } else {
         v = fmaxf(fmaf(v + r, sc, sh), lo);
     }
