@@ -177,6 +177,26 @@ __device__ __forceinline__ float tc_epilogue(float v, float r, float sc, float s
     return v;
 }
 
+// the same on the 4 channels of a lane at once: one uniform branch per pixel row instead of one per element
+__device__ __forceinline__ float4 tc_epilogue4(float4 v, float4 r, float4 sc, float4 sh, float lo, bool rnd, bool gelu) {
+    float4 o;
+    if (gelu) {
+        o.x = tc_gelu(v.x + sh.x) + r.x; o.y = tc_gelu(v.y + sh.y) + r.y;
+        o.z = tc_gelu(v.z + sh.z) + r.z; o.w = tc_gelu(v.w + sh.w) + r.w;
+    } else {
+        o.x = fmaxf(fmaf(v.x + r.x, sc.x, sh.x), lo); o.y = fmaxf(fmaf(v.y + r.y, sc.y, sh.y), lo);
+        o.z = fmaxf(fmaf(v.z + r.z, sc.z, sh.z), lo); o.w = fmaxf(fmaf(v.w + r.w, sc.w, sh.w), lo);
+    }
+    if (rnd) {
+        uint32_t u;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(o.x)); o.x = __uint_as_float(u);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(o.y)); o.y = __uint_as_float(u);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(o.z)); o.z = __uint_as_float(u);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(o.w)); o.w = __uint_as_float(u);
+    }
+    return o;
+}
+
 // second output of the dual epilogue: relu(o + b2), rounded like the first when the layer rounds
 __device__ __forceinline__ float4 tc_preact(float4 o, float4 b2, bool rnd) {
     float4 r;
@@ -229,11 +249,7 @@ __device__ __forceinline__ void tc_finish_split(const TcParams& P, const float* 
 #pragma unroll
                 for (int q = 0; q < SMAX; q++)   // fixed rank order: deterministic sum
                     if (q < S) { v.x += part[u][q].x; v.y += part[u][q].y; v.z += part[u][q].z; v.w += part[u][q].w; }
-                float4 o;
-                o.x = tc_epilogue(v.x, rv[u].x, sc.x, sh.x, lo, rnd, gelu);
-                o.y = tc_epilogue(v.y, rv[u].y, sc.y, sh.y, lo, rnd, gelu);
-                o.z = tc_epilogue(v.z, rv[u].z, sc.z, sh.z, lo, rnd, gelu);
-                o.w = tc_epilogue(v.w, rv[u].w, sc.w, sh.w, lo, rnd, gelu);
+                const float4 o = tc_epilogue4(v, rv[u], sc, sh, lo, rnd, gelu);
                 *reinterpret_cast<float4*>(P.out + (size_t)(pix0 + jb + jr) * P.ocs + P.ooff + co) = o;
                 if (P.out2 != nullptr) *reinterpret_cast<float4*>(P.out2 + (size_t)(pix0 + jb + jr) * P.co + co) = tc_preact(o, b2, rnd);
             }
@@ -546,11 +562,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
                     for (int u = 0; u < RB; u++) {
                         const int j = jbase + 8 * u;
                         if (j < je) {
-                            float4 o;
-                            o.x = tc_epilogue(v[u].x, rv[u].x, sc.x, sh.x, lo, rnd, gelu);
-                            o.y = tc_epilogue(v[u].y, rv[u].y, sc.y, sh.y, lo, rnd, gelu);
-                            o.z = tc_epilogue(v[u].z, rv[u].z, sc.z, sh.z, lo, rnd, gelu);
-                            o.w = tc_epilogue(v[u].w, rv[u].w, sc.w, sh.w, lo, rnd, gelu);
+                            const float4 o = tc_epilogue4(v[u], rv[u], sc, sh, lo, rnd, gelu);
                             *reinterpret_cast<float4*>(P.out + (size_t)(pix0 + j) * P.ocs + P.ooff + co) = o;
                             if (P.out2 != nullptr) *reinterpret_cast<float4*>(P.out2 + (size_t)(pix0 + j) * P.co + co) = tc_preact(o, b2, rnd);
                         }
