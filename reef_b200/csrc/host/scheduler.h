@@ -109,7 +109,7 @@ public:
         pad_quantum = quantum < 1 ? 1 : quantum;
     }
     // Padding is throttled so that a padded real-time task takes on average (1 + value) times its latency alone
-    // (the tail follows: at 0.08 the 99th percentile measured 9.4 % above the unpadded one).  What a best-effort
+    // (the tail follows: the 99th percentile sits two to three percent above the mean slowdown).  What a best-effort
     // kernel costs the real-time chain is close to a fixed time per kernel launch on the device, whatever its
     // size, so the throttle is a rate: at most `pad_rate` best-effort kernels per real-time window, spread evenly
     // over it; after every window the rate moves a step down when the smoothed window-time / baseline ratio is
@@ -228,7 +228,7 @@ private:
     int pad_quantum = 24;
     double pad_piece_bytes = 32e6;      // a padded piece moves at most this many algorithmic bytes (0: no limit)
     int pad_piece_cap = 0;              // > 0: best-effort pieces never claim more slots than this (wide kernels are cut)
-    double pad_target = 0.08;
+    double pad_target = 0.07;
     double pad_ratio_ema = 0.0;
     double pad_rate = 100.0;            // best-effort kernels per real-time window (controller state)
     // loop statistics of timeline_padding, printed at destruction when REEF_PAD_TRACE is set
