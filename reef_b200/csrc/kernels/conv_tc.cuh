@@ -501,9 +501,15 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
                 uint32_t r[32];
                 tmem_ld32_nowait(taddr + j0, r);
                 tmem_ld_wait();
+                float* dst = stage + j0 * TC_BM + row;
+                if (j0 + 32 <= n_lim) {   // a full chunk: no per-column test
 #pragma unroll
-                for (int j = 0; j < 32; j++)
-                    if (j0 + j < n_lim) stage[(j0 + j) * TC_BM + row] = __uint_as_float(r[j]);
+                    for (int j = 0; j < 32; j++) dst[j * TC_BM] = __uint_as_float(r[j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (j0 + j < n_lim) dst[j * TC_BM] = __uint_as_float(r[j]);
+                }
             }
         }
         if (tid == 0) tc_stamp(P, 7);   // accumulator tile staged in shared memory
