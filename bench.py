@@ -162,8 +162,8 @@ def run_reference_arm(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
-    ap.add_argument("--warmup", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=200)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--be-cap", type=int, default=int(os.environ.get("REEF_BE_CAP", "4")))
     ap.add_argument("--skip-cpu", action="store_true")
