@@ -63,11 +63,11 @@ REEFScheduler::~REEFScheduler() {
         const PadTrace& t = pad_trace;
         fprintf(stderr,
                 "[reef] timeline padding: %llu windows avg %.1f us (graph launch %.1f us), per window: %.1f iterations, "
-                "%.1f pieces (launch %.2f us, turnaround %.1f us), iterations skipped: rate-limited %.1f, no free slots %.1f, no queue could take a piece %.1f, unused %.1f\n",
+                "%.1f pieces (launch %.2f us, turnaround %.1f us), iterations skipped: rate-limited %.1f, no free slots %.1f, no queue could take a piece %.1f\n",
                 (unsigned long long)t.calls, t.window_ns / 1e3 / t.calls, t.graph_launch_ns / 1e3 / t.calls,
                 (double)t.iters / t.calls, (double)t.launched / t.calls, t.launched ? t.launch_ns / 1e3 / t.launched : 0.0,
                 t.retired ? t.turnaround_ns / 1e3 / t.retired : 0.0, (double)t.no_slot / t.calls, (double)t.no_sms / t.calls,
-                (double)t.no_queue / t.calls, (double)t.tail / t.calls);
+                (double)t.no_queue / t.calls);
         fprintf(stderr, "[reef]   per window: segments %.1f, single pieces %.1f; queue visits skipped: empty %.1f, draining %.1f, "
                 "depth full %.1f, fully issued %.1f, no fit %.1f\n", (double)t.segments / t.calls, (double)t.singles / t.calls,
                 (double)t.q_empty / t.calls, (double)t.q_draining / t.calls, (double)t.q_full / t.calls,

@@ -110,8 +110,8 @@ public:
     }
     // Padding is throttled so that a padded real-time task takes on average (1 + value) times its latency alone
     // (the tail follows: the 99th percentile sits two to three percent above the mean slowdown).  What a best-effort
-    // kernel costs the real-time chain is close to a fixed time per kernel launch on the device, whatever its
-    // size, so the throttle is a rate: at most `pad_rate` best-effort kernels per real-time window, spread evenly
+    // tensor-core kernel costs the real-time chain is close to a fixed time per kernel (0.8-1.0 us on B200: about a
+    // tenth of the time the kernel is resident), whatever its launch plan, so the throttle is a rate: at most `pad_rate` best-effort kernels per real-time window, spread evenly
     // over it; after every window the rate moves a step down when the smoothed window-time / baseline ratio is
     // above the target and a smaller step up when it is below.  (Regulating a tail statistic of the last 32
     // windows instead made the rate oscillate and gave a wider tail for the same best-effort throughput.)
@@ -233,7 +233,7 @@ private:
     double pad_rate = 100.0;            // best-effort kernels per real-time window (controller state)
     // loop statistics of timeline_padding, printed at destruction when REEF_PAD_TRACE is set
     struct PadTrace {
-        uint64_t calls = 0, iters = 0, no_slot = 0, tail = 0, no_sms = 0, no_queue = 0, launched = 0;
+        uint64_t calls = 0, iters = 0, no_slot = 0, no_sms = 0, no_queue = 0, launched = 0;
         uint64_t launch_ns = 0, turnaround_ns = 0, retired = 0, graph_launch_ns = 0, window_ns = 0;
         uint64_t q_empty = 0, q_draining = 0, q_full = 0, q_issued = 0, q_nofit = 0, segments = 0, singles = 0;
     } pad_trace;
