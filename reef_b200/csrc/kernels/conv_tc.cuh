@@ -211,6 +211,12 @@ __device__ __forceinline__ float4 tc_preact(float4 o, float4 b2, bool rnd) {
     return r;
 }
 
+// by the warp that allocated, after a CTA barrier behind every tcgen05 operation that used the columns
+__device__ __forceinline__ void tmem_free(uint32_t tmem, uint32_t cols) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(cols) : "memory");
+}
+
 __device__ __forceinline__ void tc_stamp(const TcParams& P, int slot) {
     if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) P.trace[slot] = clock64();
 }
@@ -518,9 +524,14 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         // bytes and completes the owner's mbarrier); remote loads from distributed shared memory proved an
         // order of magnitude slower here.  Owners then read only their own shared memory.
         float* recv = stage + P.recv_offset_floats;    // recv[slot][cpc_max][128]; sender q uses slot q - (q > owner)
+        // The accumulator is out of tensor memory once every warp has passed the barrier below, so the allocating
+        // warp frees it there and not at the very end: nothing is then left to do between a CTA's last store and
+        // its exit, which is what the next kernel of the stream waits for.
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         if (S > 1) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staged tile -> visible to the copy engine
             __syncthreads();      // the whole tile is staged
+            if (warp == 1) tmem_free(tmem, (uint32_t)P.tmem_cols);
             cluster_wait();       // barrier #1: all peers are past their main loops (and their barriers are armed)
             if (tid == 0) tc_stamp(P, 3);
             if (tid < S && tid != split) {   // one thread per peer: the copies are issued side by side
@@ -545,6 +556,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             cluster_arrive();
         } else {
             __syncthreads();
+            if (warp == 1) tmem_free(tmem, (uint32_t)P.tmem_cols);
         }
 
         if (tid == 0) tc_stamp(P, 8);   // exchange complete
@@ -594,12 +606,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         }
     }
 
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)P.tmem_cols) : "memory");
+    if (abort) {   // a preempted best-effort launch did nothing but allocate
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (warp == 1) tmem_free(tmem, (uint32_t)P.tmem_cols);
     }
-    if (tid == 32) tc_stamp(P, 10);   // TMEM freed
+    if (tid == 32) tc_stamp(P, 10);   // leaving
 }
 
 }  // namespace reef
