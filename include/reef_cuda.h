@@ -116,6 +116,12 @@ REEF_API reef_status reef_kernel_cost(const char* name, double* flops, double* b
  * lazily when the pointers it is given differ from the prepared ones. */
 REEF_API reef_status reef_kernel_prepare(reef_kernel_t k, void** args);
 
+/* Least size in bytes of the buffer behind each of the kernel's positional arguments (n >= its argument count).
+ * The reference trusts <model>.json (executor_base.cpp:54-75 allocates what the storage table says and binds by
+ * index); here the loader refuses a json whose storage entry is smaller than what the shape in the kernel name
+ * makes the kernel touch. */
+REEF_API reef_status reef_kernel_arg_bytes(reef_kernel_t k, size_t* bytes, int n);
+
 /* GPUConfig::KernelResource + calculate_occupancy (reference: hip_impl.h:62-74, hip_impl.cpp:34-74). */
 typedef struct {
     int num_blocks;        /* logical thread blocks of one launch                           */
@@ -203,9 +209,16 @@ REEF_API reef_status reef_dispatch_static(reef_kernel_t rt, void** rt_args,
 REEF_API reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us);
 
 /* Device-side error word: kernels with bounded waits (mbarrier waits of the tensor-core convolution) set it
- * instead of hanging or trapping.  Reads the word of the current device (after the caller synchronised the
- * stream of interest) and clears it; *value != 0 means some wait expired and the outputs are not valid. */
+ * instead of hanging or trapping.  The word lives in pinned host memory that the device writes through a mapped
+ * pointer, so reading it costs no copy and no synchronisation of its own: call after the stream of interest has
+ * been synchronised.  reef_device_error reads the word of the current device and clears it; *value != 0 means
+ * some wait expired and the outputs are not valid.  reef_device_error_peek reads without clearing (the scheduler
+ * looks at it after every task).  reef_device_error_set stores a value from the host: a supervisor that found the
+ * device state invalid by other means marks it, and the tests inject a failure with it without making any device
+ * wait expire.  (The reference aborts the process on any GPU error: hip_impl.h:25-41.) */
 REEF_API reef_status reef_device_error(int* value);
+REEF_API reef_status reef_device_error_peek(int* value);
+REEF_API reef_status reef_device_error_set(int value);
 
 /* Phase trace of the tensor-core convolution (no reference counterpart; the reference has wall-clock stamps
  * only, scheduler.h:54-56).  While enabled, block (0,0) of every tensor-core launch records the SM clock at

@@ -23,6 +23,12 @@ typedef struct reef_scheduler_s* reef_scheduler_t;   /* REEFScheduler  */
 /* ---- resource parsers (reference tests: src/reef/test/test.cpp:59-91) ---------------------- */
 /* Model::from_json: counts of storage entries, kernels and I/O args; NotFound on a bad file. */
 REEF_HOST_API int reef_model_parse(const char* json_path, size_t* num_storage, size_t* num_kernels, size_t* num_args);
+/* The checks the model loader makes before it touches the GPU (ExecutorBase::init_executor_base; the reference
+ * resolves names only, executor_base.cpp:47-52): every kernel name resolves in the registry; launch_params,
+ * argument count and shared_memory equal the registry's plan; every bound storage entry is at least as large as
+ * what the kernel reads or writes through that argument (OutOfRange otherwise).  Needs no GPU.  `err` (may be
+ * NULL) receives the message. */
+REEF_HOST_API int reef_model_check(const char* json_path, char* err, size_t err_len);
 /* ModelParamParser::parse_from_file: element count of blob `key` (0 when absent) and blob count. */
 REEF_HOST_API int reef_param_parse(const char* param_path, const char* key, size_t* key_elems, size_t* num_blobs);
 /* ModelProfile::from_json: kernel count, model latency, and the smallest latency entry. */
@@ -86,11 +92,18 @@ REEF_HOST_API int reef_sched_get_data_size(reef_scheduler_t s, uint32_t mid, con
 REEF_HOST_API int reef_sched_set_input(reef_scheduler_t s, uint32_t mid, const void* data, size_t len, const char* name);
 REEF_HOST_API int reef_sched_get_output(reef_scheduler_t s, uint32_t mid, void* data, size_t len, const char* name);
 REEF_HOST_API int reef_sched_new_task(reef_scheduler_t s, uint32_t mid, uint32_t* tid);
+/* Blocks until the task is finished.  Returns Fail for a task that finished as failed (a kernel launch returned an
+ * error, or the device error word was set while it ran); the reference aborts the process instead
+ * (src/reef/executor/hip/hip_impl.h:34-41). */
 REEF_HOST_API int reef_sched_wait_task(reef_scheduler_t s, uint32_t tid);
+/* Host-side failure injection for tests: the next `n` kernel launches of model `mid` return an error without
+ * reaching the device. */
+REEF_HOST_API int reef_sched_inject_launch_failures(reef_scheduler_t s, uint32_t mid, int n);
 typedef struct {
     int state;                 /* 0 Init, 1 Waiting, 2 Executing, 3 Finish */
     int preempted, padded, padded_to_complete;
     int64_t submit_ns, start_ns, end_ns;   /* system_clock, ns since epoch */
+    int failed;                /* a launch failed or a device-side wait expired while the task ran: output invalid */
 } reef_task_info_t;
 REEF_HOST_API int reef_sched_task_info(reef_scheduler_t s, uint32_t tid, reef_task_info_t* info);
 REEF_HOST_API int reef_sched_set_wait_sync(reef_scheduler_t s, int value);
@@ -109,7 +122,9 @@ REEF_HOST_API int reef_sched_stats(reef_scheduler_t s, reef_sched_stats_t* out);
 /* ---- closed-loop clients (behaviour of the reference's reef_client_cont, src/example/rpc_client_cont.cpp:31-35):
  * every client thread repeats { set_input from its host buffer; new_task; wait_task; get_output into its host
  * buffer } and records the per-request wall-clock latency.  Clients whose max_requests is 0 run until all
- * clients with max_requests > 0 are done (background load). */
+ * clients with max_requests > 0 are done (background load).  All clients are measured over one window: a
+ * bounded client counts from its first request after its warm-up, a background client from the first request it
+ * submits once every bounded client is past its warm-up, so completed / elapsed_s of the clients can be added. */
 typedef struct {
     uint32_t mid;
     uint32_t max_requests;       /* 0 = run while the bounded clients run                       */
@@ -123,6 +138,7 @@ typedef struct {
     uint64_t completed;          /* out: recorded requests                                      */
     double elapsed_s;            /* out: wall time of the recorded requests                     */
     uint32_t think_us;           /* pause between requests                                      */
+    uint32_t failed;             /* out: 1 when a request of this client ended in error (the client stops) */
 } reef_client_t;
 REEF_HOST_API int reef_run_clients(reef_scheduler_t s, reef_client_t* clients, size_t n);
 

@@ -34,7 +34,7 @@ class KernelAttrs(C.Structure):
 
 class TaskInfo(C.Structure):
     _fields_ = [("state", C.c_int), ("preempted", C.c_int), ("padded", C.c_int), ("padded_to_complete", C.c_int),
-                ("submit_ns", C.c_int64), ("start_ns", C.c_int64), ("end_ns", C.c_int64)]
+                ("submit_ns", C.c_int64), ("start_ns", C.c_int64), ("end_ns", C.c_int64), ("failed", C.c_int)]
 
 
 class SchedStats(C.Structure):
@@ -46,7 +46,7 @@ class Client(C.Structure):
     _fields_ = [("mid", C.c_uint32), ("max_requests", C.c_uint32), ("warmup_requests", C.c_uint32),
                 ("input", C.c_void_p), ("input_len", C.c_size_t), ("input_name", C.c_char_p),
                 ("output", C.c_void_p), ("output_len", C.c_size_t), ("latencies_ms", C.POINTER(C.c_float)),
-                ("completed", C.c_uint64), ("elapsed_s", C.c_double), ("think_us", C.c_uint32)]
+                ("completed", C.c_uint64), ("elapsed_s", C.c_double), ("think_us", C.c_uint32), ("failed", C.c_uint32)]
 
 
 def cuda_lib():
@@ -118,6 +118,11 @@ def device_error() -> int:
     v = C.c_int()
     _check(cuda_lib().reef_device_error(C.byref(v)), "reef_device_error")
     return v.value
+
+
+def device_error_set(value: int):
+    """Stores a value into the device error word from the host (failure injection without any device wait)."""
+    _check(cuda_lib().reef_device_error_set(C.c_int(value)), "reef_device_error_set")
 
 
 def launch_count() -> int:
@@ -328,6 +333,10 @@ class REEFScheduler:
     def wait_task(self, tid: int):
         _check(self._lib.reef_sched_wait_task(self._h, C.c_uint32(tid)), "wait_task")
 
+    def inject_launch_failures(self, mid: int, n: int):
+        """Host-side failure injection: the next ``n`` kernel launches of model ``mid`` return an error."""
+        _check(self._lib.reef_sched_inject_launch_failures(self._h, C.c_uint32(mid), C.c_int(n)), "inject_launch_failures")
+
     def get_task(self, tid: int) -> TaskInfo:
         info = TaskInfo()
         _check(self._lib.reef_sched_task_info(self._h, C.c_uint32(tid), C.byref(info)), "get_task")
@@ -359,7 +368,7 @@ class REEFScheduler:
         self._lib.reef_sched_stats(self._h, C.byref(st))
         return {n: int(getattr(st, n)) for n, _ in SchedStats._fields_}
 
-    def run_clients(self, clients: list) -> list:
+    def run_clients(self, clients: list, allow_failed: bool = False) -> list:
         """clients: dicts(mid, max_requests, warmup, input (ndarray|None), input_name, want_output, think_us).
         Returns per client dict(latencies_ms ndarray, completed, elapsed_s, output)."""
         arr = (Client * len(clients))()
@@ -385,10 +394,11 @@ class REEFScheduler:
             arr[i].think_us = c.get("think_us", 0)
             keep.append((inp, nm, out, lat))
         rc = self._lib.reef_run_clients(self._h, arr, C.c_size_t(len(clients)))
-        _check(rc, "reef_run_clients", self._err())
+        if rc != SUCC and not allow_failed:
+            _check(rc, "reef_run_clients", self._err())
         res = []
         for i, (inp, nm, out, lat) in enumerate(keep):
             n = int(arr[i].completed)
             res.append(dict(latencies_ms=lat[:n] if arr[i].max_requests else lat[:0], completed=n,
-                            elapsed_s=float(arr[i].elapsed_s), output=out))
+                            elapsed_s=float(arr[i].elapsed_s), output=out, failed=bool(arr[i].failed)))
         return res

@@ -217,19 +217,31 @@ reef_status reef_stream_wait_event(reef_stream_t s, reef_event_t e) {
     return REEF_SUCC;
 }
 
+// kernels of a capture = what the capturing thread launched between begin and end (other threads may launch
+// at the same time; their launches are not part of this graph)
 static thread_local unsigned long long g_capture_start = 0;
 reef_status reef_graph_begin(reef_stream_t s) {
-    g_capture_start = launch_count();
+    g_capture_start = thread_launch_count();
     CK(cudaStreamBeginCapture((cudaStream_t)s, cudaStreamCaptureModeThreadLocal));
     return REEF_SUCC;
 }
 reef_status reef_graph_end(reef_stream_t s, reef_graph_t* g) {
-    cudaGraph_t graph;
+    *g = nullptr;
+    cudaGraph_t graph = nullptr;
     CK(cudaStreamEndCapture((cudaStream_t)s, &graph));
     cudaGraphExec_t exec;
-    CK(cudaGraphInstantiate(&exec, graph, 0));
-    reef_graph_s* h = new (std::nothrow) reef_graph_s{graph, exec, launch_count() - g_capture_start};
-    if (!h) return REEF_FAIL;
+    cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(graph);
+        set_error(std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+        return REEF_FAIL;
+    }
+    reef_graph_s* h = new (std::nothrow) reef_graph_s{graph, exec, thread_launch_count() - g_capture_start};
+    if (!h) {
+        cudaGraphExecDestroy(exec);
+        cudaGraphDestroy(graph);
+        return REEF_FAIL;
+    }
     *g = (reef_graph_t)h;
     return REEF_SUCC;
 }
@@ -299,6 +311,11 @@ reef_status reef_kernel_prepare(reef_kernel_t k, void** args) {
     if (!k || !args) return REEF_FAIL;
     return prepare_kernel(k->spec, args);
 }
+reef_status reef_kernel_arg_bytes(reef_kernel_t k, size_t* bytes, int n) {
+    if (!k || !bytes || n < k->spec.nargs) return REEF_OUT_OF_RANGE;
+    for (int i = 0; i < k->spec.nargs; i++) bytes[i] = k->spec.arg_bytes[i];
+    return REEF_SUCC;
+}
 reef_status reef_kernel_attrs(reef_kernel_t k, reef_kernel_attrs_t* out) {
     if (!k || !out) return REEF_FAIL;
     return kernel_attrs(k->spec, out);
@@ -350,11 +367,25 @@ reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us) {
 uint64_t reef_launch_count(void) { return launch_count(); }
 
 reef_status reef_device_error(int* value) {
-    int* w = nullptr;
-    int rc = tc_error_word(&w);
+    volatile int* w = nullptr;
+    int rc = tc_error_word_host(&w);
     if (rc != REEF_SUCC) return rc;
-    CK(cudaMemcpy(value, w, 4, cudaMemcpyDeviceToHost));
-    if (*value != 0) CK(cudaMemset(w, 0, 4));
+    *value = *w;
+    if (*value != 0) *w = 0;
+    return REEF_SUCC;
+}
+reef_status reef_device_error_peek(int* value) {
+    volatile int* w = nullptr;
+    int rc = tc_error_word_host(&w);
+    if (rc != REEF_SUCC) return rc;
+    *value = *w;
+    return REEF_SUCC;
+}
+reef_status reef_device_error_set(int value) {
+    volatile int* w = nullptr;
+    int rc = tc_error_word_host(&w);
+    if (rc != REEF_SUCC) return rc;
+    *w = value;
     return REEF_SUCC;
 }
 

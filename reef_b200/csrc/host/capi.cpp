@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
+#include <cstdio>
 #include <cstring>
 #include <thread>
 #include <vector>
@@ -32,6 +33,23 @@ int reef_model_parse(const char* json_path, size_t* ns, size_t* nk, size_t* na) 
     if (nk) *nk = m->kernels.size();
     if (na) *na = m->args.size();
     return Succ;
+}
+
+int reef_model_check(const char* json_path, char* err, size_t err_len) {
+    std::string e;
+    auto fail = [&](int rc) {
+        if (err && err_len) snprintf(err, err_len, "%s", e.c_str());
+        return rc;
+    };
+    std::unique_ptr<executor::Model> m(executor::Model::from_json(json_path, &e));
+    if (!m) return fail(NotFound);
+    reef_module_t mod = nullptr;
+    if (reef_module_open(nullptr, &mod) != REEF_SUCC) return fail(Fail);
+    std::vector<reef_kernel_t> ks;
+    std::vector<uint32_t> smem;
+    Status st = executor::ExecutorBase::resolve_kernels(*m, mod, &ks, &smem, &e);
+    reef_module_close(mod);
+    return st == Succ ? Succ : fail(st);
 }
 
 int reef_param_parse(const char* param_path, const char* key, size_t* key_elems, size_t* num_blobs) {
@@ -262,7 +280,11 @@ int reef_sched_task_info(reef_scheduler_t s, uint32_t tid, reef_task_info_t* inf
     info->submit_ns = ns(ts[0]);
     info->start_ns = ns(ts[1]);
     info->end_ns = ns(ts[2]);
+    info->failed = t->is_failed();
     return Succ;
+}
+int reef_sched_inject_launch_failures(reef_scheduler_t s, uint32_t mid, int n) {
+    return s->sched->inject_launch_failures(mid, n);
 }
 int reef_sched_set_wait_sync(reef_scheduler_t s, int v) { s->sched->set_wait_sync(v != 0); return Succ; }
 int reef_sched_set_be_stream_cap(reef_scheduler_t s, int v) { s->sched->set_be_stream_cap(v); return Succ; }
@@ -285,11 +307,17 @@ int reef_sched_stats(reef_scheduler_t s, reef_sched_stats_t* out) {
 }
 
 // ---- closed-loop clients -------------------------------------------------------------------
+// All clients are measured over ONE window: a bounded client records from its first request after its warm-up,
+// and a background client (max_requests == 0) starts to count with the first request it submits once every
+// bounded client has finished warming up, so the throughputs of the two kinds can be added.
 int reef_run_clients(reef_scheduler_t s, reef_client_t* clients, size_t n) {
-    std::atomic<int> bounded_left(0);
+    std::atomic<int> bounded_left(0), warming(0);
     std::atomic<int> failed(0);
     for (size_t i = 0; i < n; i++)
-        if (clients[i].max_requests > 0) bounded_left++;
+        if (clients[i].max_requests > 0) {
+            bounded_left++;
+            if (clients[i].warmup_requests > 0) warming++;
+        }
     if (bounded_left.load() == 0) return OutOfRange;
     std::vector<std::thread> threads;
     for (size_t i = 0; i < n; i++) {
@@ -300,21 +328,29 @@ int reef_run_clients(reef_scheduler_t s, reef_client_t* clients, size_t n) {
             const std::string in_name = c.input_name ? c.input_name : "data";
             uint64_t done = 0;
             c.completed = 0;
+            c.failed = 0;
             c.elapsed_s = 0;
+            bool recording = false;
             auto t_first = std::chrono::steady_clock::now();
             for (uint64_t r = 0;; r++) {
                 if (bounded ? (r >= (uint64_t)c.warmup_requests + c.max_requests) : (bounded_left.load() == 0)) break;
-                if (r == c.warmup_requests) t_first = std::chrono::steady_clock::now();
+                if (!recording && (bounded ? r == c.warmup_requests : warming.load() == 0)) {
+                    if (bounded && c.warmup_requests > 0) warming--;
+                    recording = true;
+                    t_first = std::chrono::steady_clock::now();
+                }
                 auto t0 = std::chrono::steady_clock::now();
                 uint32_t tid;
                 if ((c.input && sc->set_input(c.mid, c.input, c.input_len, in_name) != Succ) ||
                     sc->new_task(c.mid, tid) != Succ || sc->wait_task(tid) != Succ ||
                     (c.output && sc->get_output(c.mid, c.output, c.output_len) != Succ)) {
+                    // a task that ended in error (wait_task returns Fail) ends this client
+                    c.failed = 1;
                     failed++;
                     break;
                 }
                 auto t1 = std::chrono::steady_clock::now();
-                if (r >= c.warmup_requests) {
+                if (recording) {
                     if (bounded && c.latencies_ms)
                         c.latencies_ms[done] = (float)(std::chrono::duration_cast<std::chrono::nanoseconds>(t1 - t0).count() * 1e-6);
                     done++;
@@ -323,7 +359,10 @@ int reef_run_clients(reef_scheduler_t s, reef_client_t* clients, size_t n) {
                 }
                 if (c.think_us) std::this_thread::sleep_for(std::chrono::microseconds(c.think_us));
             }
-            if (bounded) bounded_left--;
+            if (bounded) {
+                if (!recording && c.warmup_requests > 0) warming--;   // left early: do not hold the others' window shut
+                bounded_left--;
+            }
         });
     }
     for (auto& t : threads) t.join();

@@ -32,37 +32,69 @@ size_t ExecutorBase::storage_bytes(size_t idx) const {
     return Model::get_stype_size(si.stype) * si.size;
 }
 
+// Resolves every kernel of the schedule by name and checks the json against the registry: launch_params,
+// argument count, shared_memory, and that every bound storage entry is at least as large as what the shape in the
+// kernel name makes the kernel read or write through that argument (a hand-edited or stale json would otherwise
+// let a kernel run past its slice of the arena).  Needs no GPU.
+Status ExecutorBase::resolve_kernels(const Model& m, GPUModule_t mod, std::vector<GPUFunction_t>* out_kernels,
+                                     std::vector<uint32_t>* out_smem, std::string* err) {
+    out_kernels->clear();
+    out_smem->clear();
+    for (const KernelInfo& ki : m.kernels) {
+        GPUFunction_t k;
+        int rc = reef_module_get_kernel(mod, ki.name.c_str(), &k);
+        if (rc != REEF_SUCC) {
+            *err = reef_last_error();
+            return (Status)rc;
+        }
+        uint32_t dims[6], smem = 0;
+        int nargs = 0;
+        rc = reef_kernel_plan(ki.name.c_str(), dims, &smem, &nargs);
+        if (rc != REEF_SUCC) {
+            *err = reef_last_error();
+            return (Status)rc;
+        }
+        if (memcmp(dims, ki.launch_params, sizeof(dims)) != 0 || (size_t)nargs != ki.args.size()) {
+            *err = "launch_params or argument count of " + ki.name + " do not match the kernel registry";
+            return Status::Fail;
+        }
+        auto it = m.shared_memory.find(ki.name);
+        // "shared_memory" is descriptive in the reference (the LDS use of the code object's kernel; launches pass
+        // their own value, executor_base.cpp:217-221): an entry may claim more than the kernel here uses — the
+        // reference's mocked_kernel.json says 1024 bytes — but never less; launches use the registry's value
+        if (it != m.shared_memory.end() && it->second < smem) {
+            *err = "shared_memory of " + ki.name + " is smaller than the kernel needs";
+            return Status::Fail;
+        }
+        size_t need[16] = {0};
+        if (reef_kernel_arg_bytes(k, need, 16) != REEF_SUCC) return Status::Fail;
+        for (size_t j = 0; j < ki.args.size(); j++) {
+            const size_t idx = ki.args[j];
+            if (idx >= m.storage.size()) {
+                *err = "argument " + std::to_string(j) + " of " + ki.name + " names a storage entry that does not exist";
+                return Status::OutOfRange;
+            }
+            const size_t have = Model::get_stype_size(m.storage[idx].stype) * m.storage[idx].size;
+            if (have < need[j]) {
+                *err = "storage entry " + std::to_string(idx) + " (" + std::to_string(have) + " bytes) is smaller than argument " +
+                       std::to_string(j) + " of " + ki.name + " needs (" + std::to_string(need[j]) + " bytes)";
+                return Status::OutOfRange;
+            }
+        }
+        out_kernels->push_back(k);
+        out_smem->push_back(smem);
+    }
+    return Status::Succ;
+}
+
 Status ExecutorBase::init_executor_base(const char* json_file_path, GPUModule_t mod) {
     base_mod = mod;
     // 1. json
     model.reset(Model::from_json(json_file_path, &err_));
     if (model.get() == nullptr) RETURN_STATUS(Status::NotFound);
 
-    // 2. kernels, by name; launch geometry in the json must be the registry's plan
-    kernels.clear();
-    kernel_smem.clear();
-    for (KernelInfo& ki : model->kernels) {
-        GPUFunction_t k;
-        int rc = reef_module_get_kernel(mod, ki.name.c_str(), &k);
-        if (rc != REEF_SUCC) {
-            err_ = reef_last_error();
-            RETURN_STATUS(rc);
-        }
-        uint32_t dims[6], smem = 0;
-        int nargs = 0;
-        GPU_RETURN_STATUS(reef_kernel_plan(ki.name.c_str(), dims, &smem, &nargs));
-        if (memcmp(dims, ki.launch_params, sizeof(dims)) != 0 || (size_t)nargs != ki.args.size()) {
-            err_ = "launch_params or argument count of " + ki.name + " do not match the kernel registry";
-            RETURN_STATUS(Status::Fail);
-        }
-        auto it = model->shared_memory.find(ki.name);
-        if (it != model->shared_memory.end() && it->second != smem) {
-            err_ = "shared_memory of " + ki.name + " does not match the kernel registry";
-            RETURN_STATUS(Status::Fail);
-        }
-        kernels.push_back(k);
-        kernel_smem.push_back(smem);
-    }
+    // 2. kernels, by name; launch geometry, shared memory and storage sizes in the json must fit the registry
+    RETURN_STATUS(resolve_kernels(*model, mod, &kernels, &kernel_smem, &err_));
 
     // 3. device storage: one zero-filled arena, 256-byte aligned slices (the reference does one
     //    hipMalloc + zero copy per entry, executor_base.cpp:54-63)
@@ -213,6 +245,11 @@ Status ExecutorBase::execute_kernel(int idx, GPUStream_t stream) {
 }
 
 Status ExecutorBase::launch_kernel(int i, GPUStream_t stream) {
+    if (fail_launches > 0) {   // host-side failure injection (tests): the launch call "returns an error"
+        fail_launches--;
+        err_ = "injected launch failure at kernel " + std::to_string(i);
+        return Status::Fail;
+    }
     int rc = reef_launch(kernels[i], model->kernels[i].launch_params, kernel_smem[i], stream, raw_args[i].data());
     if (rc != REEF_SUCC) err_ = reef_last_error();
     GPU_RETURN_STATUS(rc);
@@ -317,6 +354,11 @@ int HybridExecutor::get_be_kernel_offset(int begin) {
 }
 
 Status HybridExecutor::launch_preempt_kernel(int i, GPUStream_t stream) {
+    if (fail_launches > 0) {
+        fail_launches--;
+        err_ = "injected launch failure at kernel " + std::to_string(i);
+        return Status::Fail;
+    }
     int rc = reef_launch_be(kernels[i], model->kernels[i].launch_params, kernel_smem[i], stream, preempt_flag,
                             task_slot_base + (size_t)i * 4, raw_args[i].data());
     if (rc != REEF_SUCC) err_ = reef_last_error();
@@ -391,8 +433,14 @@ Status HybridExecutor::execute_graph(GPUStream_t stream) {
         Status st = Status::Succ;
         for (size_t i = 0; i < num_kernels() && st == Status::Succ; i++) st = ExecutorBase::launch_kernel((int)i, stream);
         int rc = reef_graph_end(stream, &graph);
-        if (st != Status::Succ) return st;
-        GPU_RETURN_STATUS(rc);
+        if (st != Status::Succ || rc != REEF_SUCC) {
+            // a launch failed while capturing: what was captured is a partial graph and must never be replayed
+            if (rc != REEF_SUCC && st == Status::Succ) err_ = reef_last_error();
+            if (graph) reef_graph_destroy(graph);
+            graph = nullptr;
+            graph_stream = nullptr;
+            return st != Status::Succ ? st : Status::Fail;
+        }
         graph_stream = stream;
     }
     GPU_RETURN_STATUS(reef_graph_launch(graph, stream));

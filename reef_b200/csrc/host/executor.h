@@ -56,8 +56,13 @@ public:
     void set_stream(GPUStream_t stream);
     GPUStream_t stream() const;
     const std::string& error() const { return err_; }
+    // Failure injection on the host: the next `n` kernel launches of this executor return Status::Fail without
+    // reaching the device (how the tests exercise the failed-task path; no GPU fault is involved).
+    void inject_launch_failures(int n) { fail_launches = n; }
 
     std::unique_ptr<Model> model;
+    static Status resolve_kernels(const Model& m, GPUModule_t mod, std::vector<GPUFunction_t>* out_kernels,
+                                  std::vector<uint32_t>* out_smem, std::string* err);
 
 protected:
     Status init_executor_base(const char* json_file_path, GPUModule_t module);
@@ -74,6 +79,7 @@ protected:
     GPUModule_t base_mod = nullptr;
     bool own_module = false;
     GPUStream_t s = nullptr;
+    int fail_launches = 0;
     std::string err_;
 };
 

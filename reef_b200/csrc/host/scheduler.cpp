@@ -195,6 +195,7 @@ Status REEFScheduler::new_task(const ModelID& mid, TaskID& tid) {
     task->padding_to_finish = false;
     task->needs_recover = false;
     task->all_issued_by_padding = false;
+    task->failed = false;
     tid = task->id;
     {
         std::unique_lock<std::mutex> lock(task_pool_mtx);
@@ -240,7 +241,40 @@ Status REEFScheduler::wait_task(TaskID tid) {
         std::unique_lock<std::mutex> lock(task_pool_mtx);
         if (task_pool.size() > 4096) task_pool.erase(tid);
     }
+    return task->failed ? Status::Fail : Status::Succ;
+}
+
+Status REEFScheduler::inject_launch_failures(ModelID mid, int n) {
+    if (mid >= model_pool_size.load()) return Status::OutOfRange;
+    model_pool[mid]->executor.inject_launch_failures(n);
     return Status::Succ;
+}
+
+// The device error word is read after a task's stream has been synchronised (or seen drained): non-zero means a
+// bounded wait of some kernel expired since the last look, so what ran since then did not produce valid output.
+bool REEFScheduler::device_error_seen(const char* where) {
+    int v = 0;
+    if (reef_device_error_peek(&v) != REEF_SUCC || v == 0) return false;
+    reef_device_error(&v);   // clear: the next task starts clean
+    err_ = std::string("device error word set (a bounded device-side wait expired) seen after ") + where;
+    fprintf(stderr, "[reef] %s\n", err_.c_str());
+    return true;
+}
+
+// a best-effort task whose launch failed: ended as failed, off its queue, nothing left in the window
+void REEFScheduler::fail_be_task(TaskQueue& q, std::shared_ptr<Task>& t, const std::string& why) {
+    err_ = why;
+    fprintf(stderr, "[reef] best-effort task %u failed: %s\n", t->id, why.c_str());
+    for (auto& f : q.inflight) q.free_events.push_back(f.ev);
+    q.inflight.clear();
+    t->failed = true;
+    t->end = std::chrono::system_clock::now();
+    t->kernel_offset = 0;
+    t->block_offset = 0;
+    t->state.store(TaskState::Finish);
+    if (!q.task_queue.empty() && q.task_queue.front() == t) q.task_queue.pop();
+    n_be_tasks++;
+    finish_task(t);
 }
 
 Status REEFScheduler::get_data_size(ModelID mid, const std::string& name, size_t& size) {
@@ -495,30 +529,32 @@ void REEFScheduler::execute_rt_task(std::shared_ptr<Task>& task) {
     task->state.store(TaskState::Executing);
     task->start = std::chrono::system_clock::now();
     auto& exe = task->model->executor;
+    bool ok = true;
     if (mode == ScheduleMode::REEF && any_be_waiting() && side_padding_needed(exe)) {
         // the graph goes out first; the best-effort streams are preempted while it starts up
-        timeline_padding(task);
-        reef_stream_sync(rt_queue->stream);
-        task->end = std::chrono::system_clock::now();
-        n_rt_tasks++;
-        finish_task(task);
-        return;
-    }
-    preempt_be_tasks();
-    if (mode == ScheduleMode::REEF && any_be_waiting()) {
-        dynamic_kernel_padding(task);
-        reef_stream_sync(rt_queue->stream);
-    } else if (rt_graph) {
-        auto t0 = sclock::now();
-        if (exe.execute_graph(rt_queue->stream) != Status::Succ) {
-            err_ = "real-time graph launch failed: " + exe.error();
-            fprintf(stderr, "[reef] %s\n", err_.c_str());
-        }
-        reef_stream_sync(rt_queue->stream);
-        task->model->add_alone_sample((double)ns_since(t0));
+        ok = timeline_padding(task);
+        if (reef_stream_sync(rt_queue->stream) != REEF_SUCC) ok = false;
     } else {
-        exe.execute(rt_queue->stream);
+        preempt_be_tasks();
+        if (mode == ScheduleMode::REEF && any_be_waiting()) {
+            ok = dynamic_kernel_padding(task);
+            if (reef_stream_sync(rt_queue->stream) != REEF_SUCC) ok = false;
+        } else if (rt_graph) {
+            auto t0 = sclock::now();
+            if (exe.execute_graph(rt_queue->stream) != Status::Succ) {
+                err_ = "real-time graph launch failed: " + exe.error();
+                fprintf(stderr, "[reef] %s\n", err_.c_str());
+                ok = false;
+            }
+            if (reef_stream_sync(rt_queue->stream) != REEF_SUCC) ok = false;
+            if (ok) task->model->add_alone_sample((double)ns_since(t0));
+        } else if (exe.execute(rt_queue->stream) != Status::Succ) {
+            err_ = "real-time launch failed: " + exe.error();
+            ok = false;
+        }
     }
+    if (device_error_seen("a real-time task")) ok = false;
+    task->failed = !ok;
     task->end = std::chrono::system_clock::now();
     n_rt_tasks++;
     finish_task(task);
@@ -596,7 +632,7 @@ static int slots_of(const HybridExecutor::KernelArg& a, int blocks) {
     return a.resource.tensor_core ? blocks : (blocks + 3) / 4;
 }
 
-void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
+bool REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
     auto& rt_exe = rt_task->model->executor;
     const size_t n_rt = rt_exe.num_kernels();
     const uint32_t nq = be_queue_cnt.load();
@@ -618,7 +654,7 @@ void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
     if (rt_exe.execute_graph(rt_queue->stream) != Status::Succ) {
         err_ = "real-time graph launch failed: " + rt_exe.error();
         fprintf(stderr, "[reef] %s\n", err_.c_str());
-        return;
+        return false;
     }
     pad_trace.calls++;
     pad_trace.graph_launch_ns += ns_since(t0);
@@ -687,6 +723,7 @@ void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
                 if (be_task->all_issued_by_padding && be_task->get_state() == TaskState::Executing) {
                     retire(q, *be_task);
                     if (q.inflight.empty()) {
+                        if (device_error_seen("a padded best-effort task")) be_task->failed = true;
                         be_task->end = std::chrono::system_clock::now();
                         n_be_padded_finish++;
                         be_task->state.store(TaskState::Finish);
@@ -721,8 +758,10 @@ void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
                 if (seg_slots <= avail && (pad_piece_cap <= 0 || seg_slots <= pad_piece_cap)) {
                     if (be_task->start.time_since_epoch().count() == 0) be_task->start = std::chrono::system_clock::now();
                     if (be_exe.launch_pad_segment(k0 / G, q.stream) != Status::Succ) {
-                        err_ = be_exe.error();
-                        break;
+                        // the task is failed and taken off its queue: the window goes on with the other queues
+                        // instead of retrying the same failing launch until the real-time stream is idle
+                        fail_be_task(q, be_task, "padding segment launch failed: " + be_exe.error());
+                        continue;
                     }
                     reef_event_t ev;
                     if (!q.free_events.empty()) {
@@ -772,8 +811,8 @@ void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
             }
             if (be_task->start.time_since_epoch().count() == 0) be_task->start = std::chrono::system_clock::now();
             if (be_exe.launch_pad_piece(be_task->kernel_offset, be_task->block_offset, blocks, occ, q.stream) != Status::Succ) {
-                err_ = be_exe.error();
-                break;
+                fail_be_task(q, be_task, "padding piece launch failed: " + be_exe.error());
+                continue;
             }
             reef_event_t ev;
             if (!q.free_events.empty()) {
@@ -819,6 +858,7 @@ void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
         else pad_rate *= 1.015;
         pad_rate = std::max(4.0, std::min(4096.0, pad_rate));
     }
+    return true;
 }
 
 // reference: scheduler.cpp:477-683.  Per real-time kernel: pick a best-effort queue whose head kernel can
@@ -827,8 +867,9 @@ void REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
 // and advance the best-effort task's (kernel_offset, block_offset).  Used when every kernel on both sides is a
 // logical-block family.  Queues are tried round-robin (the reference always starts at queue 0,
 // scheduler.cpp:533, which starves the later clients under a busy real-time client).
-void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
+bool REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
     auto& rt_exe = rt_task->model->executor;
+    bool ok = true;
     std::vector<std::shared_ptr<Task>> complete_be_tasks;
     auto current_time_point = std::chrono::system_clock::now();
     const uint32_t nq = be_queue_cnt.load();
@@ -887,13 +928,21 @@ void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
         kernel_sel_count++;
         kernel_sel_latency_sum += ns_since(sel_start);
 
+        Status lst;
         if (final_be_task == nullptr) {
-            rt_exe.launch_dispatch((int)i, nullptr, 0, 0, 0, num_sms, required_occupancy, rt_queue->stream);
+            lst = rt_exe.launch_dispatch((int)i, nullptr, 0, 0, 0, num_sms, required_occupancy, rt_queue->stream);
         } else {
             if (final_be_task->start.time_since_epoch().count() == 0) final_be_task->start = current_time_point;
-            rt_exe.launch_dispatch((int)i, &final_be_task->model->executor, final_be_task->kernel_offset,
-                                   final_be_task->block_offset, final_be_block_num, sm_partition, final_occupancy,
-                                   rt_queue->stream, nullptr);
+            lst = rt_exe.launch_dispatch((int)i, &final_be_task->model->executor, final_be_task->kernel_offset,
+                                         final_be_task->block_offset, final_be_block_num, sm_partition, final_occupancy,
+                                         rt_queue->stream, nullptr);
+        }
+        if (lst != Status::Succ) {
+            // the real-time task cannot complete: stop here, the best-effort task keeps its position
+            err_ = "dispatcher launch failed: " + rt_exe.error();
+            fprintf(stderr, "[reef] %s\n", err_.c_str());
+            ok = false;
+            break;
         }
         current_time_point += std::chrono::nanoseconds((int64_t)rt_args.profile.total_latency * unit);
         if (final_be_task != nullptr) {
@@ -910,6 +959,7 @@ void REEFScheduler::dynamic_kernel_padding(std::shared_ptr<Task>& rt_task) {
             finish_task(t);
         }
     }
+    return ok;
 }
 
 // reference: scheduler.cpp:685-740
@@ -949,6 +999,7 @@ void REEFScheduler::execute_be_task(std::shared_ptr<Task>& task, std::shared_ptr
     } else {
         retire(*tqueue, *task);
         if (task->launch_offset >= num_kernels && tqueue->inflight.empty()) {
+            if (device_error_seen("a best-effort task")) task->failed = true;
             task->end = std::chrono::system_clock::now();
             if (task->all_issued_by_padding) n_be_padded_finish++;
             task->state.store(TaskState::Finish);
@@ -962,9 +1013,16 @@ void REEFScheduler::execute_be_task(std::shared_ptr<Task>& task, std::shared_ptr
     while (task->launch_offset < num_kernels && (int)tqueue->inflight.size() < be_stream_device_queue_cap) {
         int k = task->launch_offset;
         if (exe.launch_preempt_kernel(k, tqueue->stream) != Status::Succ) {
-            err_ = exe.error();
+            // fail the task rather than spin on it: Finish with the failed mark (wait_task returns Fail)
+            err_ = "best-effort launch failed: " + exe.error();
+            fprintf(stderr, "[reef] %s\n", err_.c_str());
+            for (auto& f : tqueue->inflight) tqueue->free_events.push_back(f.ev);
+            tqueue->inflight.clear();
+            task->failed = true;
+            task->kernel_offset = 0;
+            task->block_offset = 0;
             task->end = std::chrono::system_clock::now();
-            task->state.store(TaskState::Finish);   // fail the task rather than spin on it
+            task->state.store(TaskState::Finish);
             return;
         }
         reef_event_t ev;

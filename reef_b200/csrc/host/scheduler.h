@@ -67,11 +67,15 @@ public:
         bool padding_to_finish;
         bool needs_recover;
         bool all_issued_by_padding;   // every kernel went out as padding; the stream only has to drain
+        bool failed;                  // a launch failed or a device-side wait expired: the output is not valid
 
     public:
         bool is_preempted() const { return preempted; }
         bool is_padded() const { return padding; }
         bool is_padded_to_complete() const { return padding_to_finish; }
+        // The reference aborts the process on a GPU error (hip_impl.h:34-41); here the task ends in Finish with
+        // this mark and wait_task returns Status::Fail, so a client never mistakes stale output for a result.
+        bool is_failed() const { return failed; }
         TaskState get_state() const { return (TaskState)state.load(); }
         std::vector<std::chrono::system_clock::time_point> get_timestamp() const { return {submit, start, end}; }
     };
@@ -131,6 +135,8 @@ public:
     };
     Stats stats() const;
     const std::string& error() const { return err_; }
+    // host-side failure injection for tests: the next n kernel launches of model `mid` return an error
+    Status inject_launch_failures(ModelID mid, int n);
 
 private:
     struct Model {
@@ -179,8 +185,10 @@ private:
     void reset_preempt_flag_async();
     void preempt_reset();
     void preempt_wait();
-    void dynamic_kernel_padding(std::shared_ptr<Task>& rt_task);
-    void timeline_padding(std::shared_ptr<Task>& rt_task);
+    bool dynamic_kernel_padding(std::shared_ptr<Task>& rt_task);
+    bool timeline_padding(std::shared_ptr<Task>& rt_task);
+    bool device_error_seen(const char* where);
+    void fail_be_task(TaskQueue& q, std::shared_ptr<Task>& t, const std::string& why);
     bool side_padding_needed(executor::HybridExecutor& rt_exe);
     void advance_padded(Task* be_task, TaskQueue* q, int blocks, bool side_launch,
                         std::vector<std::shared_ptr<Task>>* complete);

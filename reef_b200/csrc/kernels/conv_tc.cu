@@ -155,19 +155,38 @@ static int encode(CUtensorMap* tm, const void* base, int rank, const cuuint64_t*
     return REEF_SUCC;
 }
 
-static int* g_error_word[16] = {nullptr};
+// The error word is pinned host memory mapped into the device's address space: a kernel whose bounded wait
+// expired stores 1 through the device pointer, the host reads the word directly once the stream is synchronised.
+static int* g_error_word[16] = {nullptr};        // device view
+static int* g_error_word_host[16] = {nullptr};   // host view of the same word
 
 int tc_error_word(int** out) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 16) return REEF_FAIL;
     if (!g_error_word[dev]) {
-        if (cudaMalloc(&g_error_word[dev], 4) != cudaSuccess || cudaMemset(g_error_word[dev], 0, 4) != cudaSuccess) {
+        int* h = nullptr;
+        int* d = nullptr;
+        if (cudaHostAlloc((void**)&h, 64, cudaHostAllocMapped) != cudaSuccess ||
+            cudaHostGetDevicePointer((void**)&d, h, 0) != cudaSuccess) {
             set_error("cannot allocate the device error word");
             return REEF_FAIL;
         }
+        *h = 0;
+        g_error_word_host[dev] = h;
+        g_error_word[dev] = d;
     }
     *out = g_error_word[dev];
+    return REEF_SUCC;
+}
+
+int tc_error_word_host(volatile int** out) {
+    int* d = nullptr;
+    int rc = tc_error_word(&d);
+    if (rc != REEF_SUCC) return rc;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    *out = g_error_word_host[dev];
     return REEF_SUCC;
 }
 

@@ -489,7 +489,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         if (S > 1) cluster_arrive_relaxed();
         if (!ok || s_flags[1]) {
             ok = false;
-            if (tid == 0 && P.error_word) atomicExch(P.error_word, 1);
+            if (tid == 0 && P.error_word) *reinterpret_cast<volatile int*>(P.error_word) = 1;
         }
         // Phase A — eight warps move the accumulator tile TMEM -> registers -> shared memory as
         // stage[pixel][channel] (warp w reads TMEM lanes 32*(w%4).., its hardware quadrant, and the column
@@ -549,7 +549,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             }
             if (!mbar_wait(bar_red, 0)) {
                 ok = false;
-                if (tid == 0 && P.error_word) atomicExch(P.error_word, 1);
+                if (tid == 0 && P.error_word) *reinterpret_cast<volatile int*>(P.error_word) = 1;
             }
             // cluster barrier #2 (arrive here, wait before leaving): once all ranks have received what they are
             // owed, nobody reads a peer's shared memory any more and every CTA may exit

@@ -5,6 +5,7 @@
 // src/reef/executor/hybrid_executor.cpp:153-163, src/reef/server/scheduler.cpp:613-649).
 #include "registry.h"
 
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -18,7 +19,14 @@
 
 namespace reef {
 
-static unsigned long long g_launches = 0;
+// launches are counted from the scheduler thread and from request threads (a best-effort model captures its
+// padding segments when it is bound to a queue)
+static std::atomic<unsigned long long> g_launches{0};
+static thread_local unsigned long long t_launches = 0;
+static inline void count_launch() {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    t_launches++;
+}
 
 struct TcCache {
     TcParams params;
@@ -353,9 +361,94 @@ bad:
     return REEF_NOT_FOUND;
 }
 
+// Least size in bytes of the buffer behind each positional argument: what one launch reads or writes through it.
+// The model loader compares these with the storage table of <model>.json, so that a json whose storage entry is too
+// small for the shape in the kernel name is refused instead of letting the kernel run past its slice of the arena.
+static void fill_arg_bytes(KernelSpec* s) {
+    for (int i = 0; i < kMaxArgs; i++) s->arg_bytes[i] = 0;
+    const KTask& t = s->task;
+    size_t* b = s->arg_bytes;
+    auto f4 = [](double n) { return (size_t)(n > 0 ? n : 0) * 4; };
+    switch (t.family) {
+        case F_MOCK_ADD:
+        case F_MOCK_MUL:
+            b[0] = f4(kMockThreads); b[1] = f4(64.0 * kMockThreads); b[2] = b[1];
+            break;
+        case F_FUSED_ADD_NCHW:
+            b[0] = b[1] = f4((double)t.p.elt.c * t.p.elt.n); b[2] = f4(t.p.elt.c);
+            break;
+        case F_NCHW_TO_NHWC4:
+            b[0] = f4(4.0 * t.p.elt.n); b[1] = f4((double)t.p.elt.c * t.p.elt.n); b[2] = f4(t.p.elt.c);
+            break;
+        case F_BIAS_RELU:
+            b[0] = f4((double)t.p.elt.c * t.p.elt.n);
+            b[1] = f4((double)(t.p.elt.n - 1) * t.p.elt.ics + t.p.elt.ioff + t.p.elt.c);
+            b[2] = f4(t.p.elt.c);
+            break;
+        case F_COPY:
+            b[0] = b[1] = f4(t.p.elt.n);
+            break;
+        case F_GLOBAL_AVG_POOL:
+            b[0] = f4((double)t.p.elt.c * t.p.elt.n); b[1] = f4(t.p.elt.c);
+            break;
+        case F_MAX_POOL:
+        case F_AVG_POOL: {
+            const PoolP& p = t.p.pool;
+            b[0] = f4((double)(p.hi * p.wi - 1) * p.ics + p.ioff + p.c);
+            b[1] = f4((double)(p.ho * p.wo - 1) * p.ocs + p.ooff + p.c);
+            if (p.has_bias) b[2] = f4(p.c);
+            break;
+        }
+        case F_DENSE:
+            b[0] = f4(t.p.dense.k); b[1] = f4((double)t.p.dense.k * t.p.dense.n); b[2] = b[3] = f4(t.p.dense.n);
+            break;
+        case F_SOFTMAX:
+            b[0] = b[1] = f4((double)t.p.softmax.rows * t.p.softmax.n);
+            break;
+        case F_EMBEDDING: {
+            const double sN = t.p.raw[0], h = t.p.raw[1], vocab = t.p.raw[2];
+            b[0] = f4(sN * h); b[1] = f4(vocab * h); b[2] = (size_t)sN * 8; b[3] = f4(sN * h);
+            break;
+        }
+        case F_LAYERNORM: {
+            const double rows = t.p.raw[0], h = t.p.raw[1];
+            int i = 0;
+            b[i++] = f4(rows * h); b[i++] = f4(rows * h);
+            if (t.p.raw[2]) b[i++] = f4(rows * h);
+            b[i++] = f4(h); b[i++] = f4(h);
+            break;
+        }
+        case F_ATTENTION: {
+            const double sN = t.p.raw[0], H = (double)t.p.raw[1] * t.p.raw[2];
+            int i = 0;
+            b[i++] = f4(sN * 3 * H);
+            if (t.p.raw[3]) b[i++] = f4(sN);
+            b[i++] = f4(sN * H);
+            break;
+        }
+        case F_CONV_SIMT:
+        case F_CONV_TC: {
+            const ConvP& p = t.p.conv;
+            b[0] = p.nchw ? f4((double)p.ci * p.hi * p.wi) : f4((double)(p.hi * p.wi - 1) * p.ics + p.ioff + p.ci);
+            b[1] = f4((double)p.co * p.ktot);
+            b[2] = f4((double)(p.ptot - 1) * p.ocs + p.ooff + p.co);
+            if (p.i_res >= 0) b[p.i_res] = f4((double)p.ptot * p.co);
+            if (p.i_bias >= 0) b[p.i_bias] = f4(p.co);
+            if (p.i_gamma >= 0) b[p.i_gamma] = f4(p.co);
+            if (p.i_beta >= 0) b[p.i_beta] = f4(p.co);
+            if (p.i_bias2 >= 0) b[p.i_bias2] = f4(p.co);
+            if (p.i_out2 >= 0) b[p.i_out2] = f4((double)p.ptot * p.co);
+            break;
+        }
+        default:
+            break;
+    }
+}
+
 int plan_kernel(const char* name, KernelSpec* s) {
     int rc = build_spec(name, s);
     if (rc != REEF_SUCC) return rc;
+    fill_arg_bytes(s);
     if (s->task.family == F_CONV_TC) {
         s->grid[0] = (uint32_t)s->tc.splits;
         s->grid[1] = (uint32_t)(s->tc.n_tiles * s->tc.m_tiles);
@@ -526,8 +619,9 @@ int launch_delay(cudaStream_t st, unsigned long long ns) {
 // ------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------
-unsigned long long launch_count() { return g_launches; }
-void add_launches(unsigned long long n) { g_launches += n; }
+unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+unsigned long long thread_launch_count() { return t_launches; }
+void add_launches(unsigned long long n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 #define FOR_EACH_FAMILY(X)                                                                      \
     X(F_MOCK_ADD) X(F_MOCK_MUL) X(F_FUSED_ADD_NCHW) X(F_BIAS_RELU) X(F_CONV_SIMT) X(F_MAX_POOL) \
@@ -635,7 +729,7 @@ static int launch_tc(const KernelSpec& s, cudaStream_t st, void** args, const in
     int rc = bind_tc(s, args);
     if (rc != REEF_SUCC) return rc;
     TcCache& c = *s.tc_cache;
-    g_launches++;
+    count_launch();
     return tc_launch(c.params, s.tc, st, flag, slot, tile_begin, tile_count);
 }
 
@@ -650,7 +744,7 @@ int launch_plain(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cud
     void* kargs[] = {&t};
     cudaError_t e = launch_pdl(plain_fn(t.family), dim3(dims[0], dims[1], dims[2]), dim3(dims[3], dims[4], dims[5]), kargs,
                                smem, st);
-    g_launches++;
+    count_launch();
     return check_cuda(e, "cudaLaunchKernel");
 }
 
@@ -666,7 +760,7 @@ int launch_be(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cudaSt
     void* kargs[] = {&t, (void*)&flag, (void*)&slot};
     cudaError_t e = launch_pdl(be_fn(t.family), dim3(dims[0], dims[1], dims[2]), dim3(dims[3], dims[4], dims[5]), kargs, smem,
                                st);
-    g_launches++;
+    count_launch();
     return check_cuda(e, "cudaLaunchKernel(be)");
 }
 
@@ -709,7 +803,7 @@ int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, 
         int grid = num_sms * occupancy;
         void* kargs[] = {&trt, &tbe, &be_off, &be_num, &sm_partition, (void*)&be_slot, (void*)&ctrl};
         cudaError_t e = cudaLaunchKernel((const void*)k_dispatch, dim3(grid), dim3(kThreads), kargs, smem, st);
-        g_launches++;
+        count_launch();
         return check_cuda(e, "cudaLaunchKernel(dispatch)");
     }
 
@@ -728,7 +822,7 @@ int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, 
             if (grid > trt.nblocks) grid = trt.nblocks;
             void* kargs[] = {&trt, &tbe, &zero, &zero, &part, (void*)&null_slot, (void*)&ctrl};
             cudaError_t e = cudaLaunchKernel((const void*)k_dispatch, dim3(grid), dim3(kThreads), kargs, rt->dyn_smem, st);
-            g_launches++;
+            count_launch();
             rc = check_cuda(e, "cudaLaunchKernel(dispatch rt)");
         }
         if (rc != REEF_SUCC) return rc;
@@ -757,7 +851,7 @@ int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, 
         }
         void* kargs[] = {&trt, &tbe, &be_off, &be_num, &part, (void*)&be_slot, (void*)&ctrl2};
         cudaError_t e = cudaLaunchKernel((const void*)k_dispatch, dim3(grid), dim3(kThreads), kargs, be->dyn_smem, bs);
-        g_launches++;
+        count_launch();
         return check_cuda(e, "cudaLaunchKernel(dispatch be)");
     }
     return REEF_SUCC;
@@ -825,7 +919,7 @@ int launch_dispatch_static(const KernelSpec* rt, void** rt_args, const KernelSpe
     int grid = num_sms * occupancy;
     void* kargs[] = {&trt, &tbe, &be_off, &be_num, &sm_partition, (void*)&be_slot, (void*)&ctrl};
     cudaError_t e = cudaLaunchKernel((const void*)k_dispatch, dim3(grid), dim3(kThreads), kargs, smem, st);
-    g_launches++;
+    count_launch();
     return check_cuda(e, "cudaLaunchKernel(dispatch, static lane)");
 }
 

@@ -32,6 +32,7 @@ struct KernelSpec {
     uint32_t dyn_smem;
     int nargs;
     double flops, bytes;   // algorithmic work of one launch
+    size_t arg_bytes[kMaxArgs];   // least size of the buffer behind each positional argument
     int tensor_core;
     TcPlan tc;
     mutable std::shared_ptr<TcCache> tc_cache;
@@ -62,10 +63,12 @@ int tc_launch(const TcParams& P, const TcPlan& pl, cudaStream_t st, const int* f
               int tile_count = -1);
 int tc_func_attrs(const TcPlan& pl, cudaFuncAttributes* fa, int* occ);
 int tc_error_word(int** out);
+int tc_error_word_host(volatile int** out);
 int tc_prepare_device();
 int tc_trace_enable(int on);
 int tc_trace_read(long long* out16);
-unsigned long long launch_count();
+unsigned long long launch_count();          // kernels launched by this library, all threads
+unsigned long long thread_launch_count();   // ... by the calling thread (a stream capture counts its own launches)
 void add_launches(unsigned long long n);
 
 }  // namespace reef

@@ -175,3 +175,85 @@ def test_estimate_slot_usage(libs, tmp_path):
     d = resources.generate("resnet18_64", str(tmp_path))
     r = estimate.estimate(d)
     assert r["kernels"] > 20 and 0 < r["busy_pct"] <= r["busy_with_parked_successor_pct"] <= 100
+
+
+REF_FIXTURES = os.path.join(ROOT, "tests", "golden", "ref")
+
+
+@pytest.mark.parametrize("model,storage,kernels,args,profile_kernels,model_latency", [
+    ("mocked_kernel", 5, 2, 3, 2, 30),
+    ("resnet18", 101, 57, 44, 54, 2189),
+    ("resnet152", 317, 207, 312, 35, 13233),
+    ("bert", 112, 205, 102, 23, 5426),
+    ("inception", 204, 146, 191, 75, 8273),
+])
+def test_cpp_parsers_read_the_reference_shipped_resources(libs, model, storage, kernels, args, profile_kernels, model_latency):
+    """The reference's own <model>.json and <model>.profile.json (copied unchanged from its resource/ directory into
+    tests/golden/ref) go through the C++ parsers with the expectations of the reference's parser tests
+    (src/reef/test/test.cpp:59-65 parse_model: kernels != 0; :79-91 parse_profile: 54 kernels for resnet18, every kernel
+    has a latency table and every latency is > 0).  Counts are those of the files themselves."""
+    L = capi.host_lib()
+    jpath = os.path.join(REF_FIXTURES, model + ".json")
+    ns, nk, na = C.c_size_t(), C.c_size_t(), C.c_size_t()
+    assert L.reef_model_parse(jpath.encode(), C.byref(ns), C.byref(nk), C.byref(na)) == capi.SUCC
+    j = json.load(open(jpath))
+    assert (ns.value, nk.value, na.value) == (len(j["storage"]), len(j["kernels"]), len(j["args"])) == (storage, kernels, args)
+    assert nk.value != 0
+    ppath = os.path.join(REF_FIXTURES, model + ".profile.json")
+    nkp, ml, mn = C.c_size_t(), C.c_int(), C.c_int()
+    assert L.reef_profile_parse(ppath.encode(), C.byref(nkp), C.byref(ml), C.byref(mn)) == capi.SUCC
+    assert nkp.value == profile_kernels and ml.value == model_latency
+    assert mn.value > 0          # every kernel has a non-empty latency table with entries > 0
+    # the reference's kernels are TVM symbols of a per-model code object: the registry here does not know them
+    # and says so instead of guessing
+    if model != "mocked_kernel":
+        err = C.create_string_buffer(512)
+        assert L.reef_model_check(jpath.encode(), err, C.c_size_t(512)) == capi.NOT_FOUND
+        assert b"kernel" in err.value
+
+
+def test_reference_mocked_kernel_json_is_loadable_as_is(libs):
+    """The reference's mocked_kernel.json (two kernels `add`, `multiply`, launch [64,1,1,4,8,4]) passes every check the
+    loader makes before it touches the GPU: same names, same launch geometry, same storage sizes."""
+    L = capi.host_lib()
+    err = C.create_string_buffer(512)
+    rc = L.reef_model_check(os.path.join(REF_FIXTURES, "mocked_kernel.json").encode(), err, C.c_size_t(512))
+    assert rc == capi.SUCC, err.value
+
+
+def test_loader_refuses_a_storage_entry_smaller_than_the_kernel_needs(gen, libs, tmp_path):
+    """A json whose storage entry is smaller than what the shape in the kernel name makes the kernel touch is refused
+    with OutOfRange before any device memory is allocated."""
+    L = capi.host_lib()
+    base = gen("resnet18_64")
+    j = json.load(open(base + ".json"))
+    err = C.create_string_buffer(512)
+    assert L.reef_model_check((base + ".json").encode(), err, C.c_size_t(512)) == capi.SUCC, err.value
+    # shrink the output buffer of a convolution in the middle of the network by one element
+    k = [k for k in j["kernels"] if "conv2d" in k["name"]][5]
+    victim = k["args"][2]
+    j["storage"][victim]["size"] -= 1
+    bad = tmp_path / "shrunk.json"
+    bad.write_text(json.dumps(j))
+    assert L.reef_model_check(str(bad).encode(), err, C.c_size_t(512)) == capi.OUT_OF_RANGE
+    assert b"smaller than argument 2" in err.value and k["name"].encode() in err.value
+    # and a weight buffer
+    j = json.load(open(base + ".json"))
+    j["storage"][k["args"][1]]["size"] //= 2
+    bad.write_text(json.dumps(j))
+    assert L.reef_model_check(str(bad).encode(), err, C.c_size_t(512)) == capi.OUT_OF_RANGE
+    assert b"argument 1" in err.value
+
+
+@pytest.mark.parametrize("model", ["resnet18", "resnet50_64", "vgg16_32", "densenet121_64", "inception_v3_139", "bert_tiny",
+                                   "resnet18_64_fp32"])
+def test_generated_schedules_pass_the_storage_size_check(gen, libs, model):
+    """Every generated schedule binds each kernel argument to a storage entry of at least the size the kernel needs
+    (one model per family here; the full-size schedules pass the same check whenever a GPU test loads them)."""
+    L = capi.host_lib()
+    if model.endswith("_fp32"):
+        base = gen(model[:-5], variant="_fp32")
+    else:
+        base = gen(model)
+    err = C.create_string_buffer(512)
+    assert L.reef_model_check((base + ".json").encode(), err, C.c_size_t(512)) == capi.SUCC, err.value
