@@ -6,10 +6,13 @@ real-time (RT) client issuing back-to-back ResNet-152 batch-1 requests while 4 b
 clients run ResNet-152 batch-1 closed-loop, all on one GPU through REEFScheduler in REEF mode
 (flag preemption + dynamic kernel padding).  Synthetic, seeded weights and inputs.
 
-A "step" is one RT request.  `value` is whole-job inferences/s (RT + BE) with inputs resident in
-HBM; `e2e` is the same measured through the scheduler's public request calls with pinned HOST
-buffers (set_input H2D + new_task + wait_task + get_output D2H inside the timed region).  RT
-p50/p99, RT-alone p99, BE inf/s, BE-alone inf/s and preemption latency ride along in `rt_be`.
+A "step" is a block of 100 RT requests (so the default 20 steps after 3 warm-up steps are 2000 timed RT
+requests after 300 warm-up requests: percentiles over 2000 samples, the padding controller in steady state).
+`value` is whole-job inferences/s = RT inf/s + BE inf/s over ONE window (the BE clients start counting when the
+RT client has finished its warm-up), inputs resident in HBM; `e2e` is the same measured through the scheduler's
+public request calls with pinned HOST buffers (set_input H2D + new_task + wait_task + get_output D2H inside the
+timed region).  RT p50/p99, RT-alone p99, BE inf/s, BE-alone inf/s and the preemption latencies ride along in
+`rt_be`.
 
 N > 1 (torchrun, one rank per GPU): one scheduler + full weight replica per GPU, requests are
 independent, no data-path collective ("scaling": "weak").
@@ -31,6 +34,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 UNIT = "inf/s"
+REQS_PER_STEP = 100     # one step = this many back-to-back RT requests
+# DRAM traffic of the dominant kernel per launch, from an ncu capture of all 154 tensor-core launches of one
+# ResNet-152 pass (dram__bytes_read.sum + dram__bytes_write.sum; summary committed as
+# profiles/conv_tc_resnet152_dram.md).  A constant of that capture: it is NOT measured in a bench run.
+CONV_TC_TRAFFIC_PER_LAUNCH = {"c2": 2407620, "c1": 2407620}
 # BASELINE.json configs; "c2" is the configuration the headline metric is quoted on and the default
 WORKLOADS = {
     "c0": dict(metric="resnet18_b1_inferences_per_s_rt_only", rt="resnet18", be=[],
@@ -79,7 +87,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except OSError:
@@ -162,10 +170,14 @@ def run_reference_arm(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
-    ap.add_argument("--warmup", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=20, help="timed steps; one step = %d RT requests" % REQS_PER_STEP)
+    ap.add_argument("--warmup", type=int, default=3, help="warm-up steps (at least 3)")
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--be-cap", type=int, default=int(os.environ.get("REEF_BE_CAP", "4")))
+    ap.add_argument("--be-cap", type=int, default=int(os.environ.get("REEF_BE_CAP", "2")),
+                    help="kernels a BE task keeps on its stream (reference: 2, scheduler.cpp:32)")
+    ap.add_argument("--pad-target", type=float, default=None,
+                    help="slowdown the padding controller may cost a real-time task (default: the scheduler's 0.06)")
+    ap.add_argument("--no-pin", action="store_true", help="do not pin the scheduler and client threads to CPU cores")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--profile-out", default="")
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
@@ -173,6 +185,7 @@ def main():
     wl = WORKLOADS[args.workload]
     n_be = len(wl["be"])
     args.warmup = max(args.warmup, 3)
+    n_req, n_warm = args.steps * REQS_PER_STEP, args.warmup * REQS_PER_STEP
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -200,6 +213,19 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # CPU placement: every rank takes an equal slice of the cores this process may run on; inside it the scheduler
+    # thread and the RT client get a core each, the BE clients share the rest (the scheduler thread and the RT client
+    # both spin: left unpinned, eight ranks of them fight over the same cores and the RT tail grows)
+    cpu_slice = None
+    try:
+        cores = sorted(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = list(range(os.cpu_count() or 1))
+    per_rank = len(cores) // max(1, int(os.environ.get("LOCAL_WORLD_SIZE", world)))
+    if not args.no_pin and per_rank >= 3 and cores == list(range(cores[0], cores[0] + len(cores))):
+        cpu_slice = (cores[0] + local_rank * per_rank, per_rank)
+    torch.set_num_threads(1)
+
     models = sorted(set([wl["rt"]] + wl["be"]))
     if rank == 0:
         from reef_b200 import profiler
@@ -221,9 +247,17 @@ def main():
         s.set_input(mid, inputs[m][1], inputs[m][0])
         return mid
 
-    def make_sched(n_be_clients, rt=True):
+    def make_sched(n_be_clients, rt=True, mapped_flag=False, stamps=False):
         s = S(S.REEF, local_rank)
         s.set_be_stream_cap(args.be_cap)
+        if args.pad_target is not None:
+            s.set_pad_slowdown_target(args.pad_target)
+        if cpu_slice is not None:
+            s.set_cpu_slice(*cpu_slice)
+        if mapped_flag:
+            s.use_mapped_flag()
+        if stamps:
+            s.set_device_stamps(True)
         s.run()
         ids = {"rt": None, "be": [], "be_models": wl["be"][:n_be_clients]}
         if rt:
@@ -235,7 +269,7 @@ def main():
     extra = {}
     # ---- phase A: RT alone (closed loop, inputs resident) -------------------------------------
     s, ids = make_sched(0)
-    r = s.run_clients([dict(mid=ids["rt"], max_requests=args.steps, warmup=args.warmup, want_output=False)])[0]
+    r = s.run_clients([dict(mid=ids["rt"], max_requests=n_req, warmup=n_warm, want_output=False)])[0]
     extra["rt_alone_p50_ms"] = pct(r["latencies_ms"], 50)
     extra["rt_alone_p99_ms"] = pct(r["latencies_ms"], 99)
     extra["rt_alone_inf_s"] = r["completed"] / r["elapsed_s"]
@@ -244,15 +278,15 @@ def main():
     # ---- phase B: BE alone ---------------------------------------------------------------------
     if n_be:
         s, ids = make_sched(n_be, rt=False)
-        be_req = max(20, args.steps // 8)
-        rs = s.run_clients([dict(mid=m, max_requests=be_req, warmup=max(3, args.warmup // 8), want_output=False)
+        be_req = max(20, n_req // 8)
+        rs = s.run_clients([dict(mid=m, max_requests=be_req, warmup=max(3, n_warm // 8), want_output=False)
                             for m in ids["be"]])
         extra["be_alone_inf_s"] = sum(r["completed"] / r["elapsed_s"] for r in rs)
         s.shutdown(); s.close()
 
     # ---- phase C (timed region of `value`): RT + 4 BE, inputs resident in HBM --------------------
     s, ids = make_sched(n_be)
-    clients = [dict(mid=ids["rt"], max_requests=args.steps, warmup=args.warmup, want_output=False)] + \
+    clients = [dict(mid=ids["rt"], max_requests=n_req, warmup=n_warm, want_output=False)] + \
               [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
     sampler = ClockSampler(local_rank)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -268,9 +302,9 @@ def main():
     clocks = sampler.stop()
     barrier()
     rt_r, be_r = rs[0], rs[1:]
-    # the timed region of the K steps is the RT client's recorded window; BE throughput over the same window
+    # the timed region of the K steps is the RT client's recorded window; the BE clients count over the same window
+    # (they start counting when the RT client has finished its warm-up), so the two throughputs add up
     region_s = rt_r["elapsed_s"]
-    total_inf = rt_r["completed"] + sum(r["completed"] for r in be_r)
     be_inf_s = sum(r["completed"] / r["elapsed_s"] for r in be_r if r["elapsed_s"] > 0)
     st = s.stats()
     extra.update({"rt_p50_ms": pct(rt_r["latencies_ms"], 50), "rt_p99_ms": pct(rt_r["latencies_ms"], 99),
@@ -281,34 +315,36 @@ def main():
     s.shutdown(); s.close()
 
     if n_be:
-        # ---- phase D1: reset-based preemption.  The RT client pauses 2 ms between requests, so the BE clients run
-        # at full speed on their own streams and every RT arrival preempts them (under a back-to-back RT client the
-        # BE tasks only advance as padding and there is nothing to preempt).  Latency = flag raised + tasks rolled
-        # back, as the scheduler measures it (reference: scheduler.cpp:305-346).
-        s, ids = make_sched(n_be)
-        clients = [dict(mid=ids["rt"], max_requests=max(100, args.steps // 3), warmup=5, want_output=False, think_us=2000)] + \
-                  [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
-        rs = s.run_clients(clients)
-        st = s.stats()
-        extra["preempt_avg_us"] = st["preempt_ns_sum"] / max(1, st["preempt_count"]) / 1e3
-        extra["preempt_max_us"] = st["preempt_ns_max"] / 1e3
-        extra["preempt_count"] = st["preempt_count"]
-        extra["rt_after_preempt_p50_ms"] = pct(rs[0]["latencies_ms"], 50)
-        extra["rt_after_preempt_p99_ms"] = pct(rs[0]["latencies_ms"], 99)
-        extra["be_inf_s_rt_every_2ms"] = sum(r["completed"] / r["elapsed_s"] for r in rs[1:] if r["elapsed_s"] > 0)
-        s.shutdown(); s.close()
-
-        # ---- phase D2: preemption latency with drain (flag set -> BE streams idle -> counters read) ----
-        s, ids = make_sched(n_be)
-        s.set_wait_sync(True)
-        clients = [dict(mid=ids["rt"], max_requests=max(50, args.steps // 10), warmup=5, want_output=False, think_us=2000)] + \
-                  [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
-        s.run_clients(clients)
-        st = s.stats()
-        extra["preempt_drain_avg_us"] = st["preempt_ns_sum"] / max(1, st["preempt_count"]) / 1e3
-        extra["preempt_drain_max_us"] = st["preempt_ns_max"] / 1e3
-        extra["preempt_drain_count"] = st["preempt_count"]
-        s.shutdown(); s.close()
+        # ---- phase D: reset-based preemption.  The RT client pauses 2 ms between requests, so the BE clients run at
+        # full speed on their own streams and every RT arrival preempts them (under a back-to-back RT client the BE
+        # tasks only advance as padding and there is nothing to preempt).  Three figures per preemption:
+        #   flag    host clock: flag raised, queued launches dropped, tasks rolled back
+        #   drain   host clock: flag write -> BE streams idle and completion counters read.  This is the figure to
+        #           hold against the 20 us target: the reference's switch also ends with no BE wavefront running
+        #           (scheduler.cpp:305-346, 374-439: flag, clear queues, kill wavefronts, measured around the whole)
+        #   device  %globaltimer: first BE block that saw the flag -> last BE block that left
+        # measured with the flag in device memory (stream write, the default) and in mapped host memory (host store).
+        for tag, mapped in (("", False), ("mapped_flag_", True)):
+            s, ids = make_sched(n_be, mapped_flag=mapped, stamps=True)
+            n_pre = max(200, n_req // 8)
+            clients = [dict(mid=ids["rt"], max_requests=n_pre, warmup=5, want_output=False, think_us=2000)] + \
+                      [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
+            rs = s.run_clients(clients)
+            st = s.stats()
+            extra["preempt_%sflag_avg_us" % tag] = st["preempt_ns_sum"] / max(1, st["preempt_count"]) / 1e3
+            extra["preempt_%sflag_max_us" % tag] = st["preempt_ns_max"] / 1e3
+            extra["preempt_%sdrain_avg_us" % tag] = st["drain_ns_sum"] / max(1, st["drain_count"]) / 1e3
+            extra["preempt_%sdrain_max_us" % tag] = st["drain_ns_max"] / 1e3
+            extra["preempt_%sdevice_avg_us" % tag] = st["dev_ns_sum"] / max(1, st["dev_count"]) / 1e3
+            extra["preempt_%sdevice_max_us" % tag] = st["dev_ns_max"] / 1e3
+            extra["preempt_%scount" % tag] = st["drain_count"]
+            extra["preempt_%sdevice_samples" % tag] = st["dev_count"]
+            if not mapped:
+                extra["rt_after_preempt_p50_ms"] = pct(rs[0]["latencies_ms"], 50)
+                extra["rt_after_preempt_p99_ms"] = pct(rs[0]["latencies_ms"], 99)
+            extra["be_inf_s_%srt_every_2ms" % tag] = sum(r["completed"] / r["elapsed_s"] for r in rs[1:] if r["elapsed_s"] > 0)
+            s.shutdown(); s.close()
+        extra["preempt_target_metric"] = "preempt_drain_avg_us (flag write -> best-effort streams drained, host clock) < 20"
 
     # ---- phase E (e2e): same workload through the request calls with pinned host buffers ---------
     s, ids = make_sched(n_be)
@@ -320,7 +356,7 @@ def main():
         pin = pinned_array(capi, arr.nbytes, arr.dtype)
         pin[:] = arr
         pins.append(pin)
-        clients.append(dict(mid=mid, max_requests=args.steps if i == 0 else 0, warmup=args.warmup if i == 0 else 0,
+        clients.append(dict(mid=mid, max_requests=n_req if i == 0 else 0, warmup=n_warm if i == 0 else 0,
                             input=pin, input_name=nm, want_output=True))
     barrier()
     rs = s.run_clients(clients)
@@ -350,12 +386,12 @@ def main():
     # kernels would add several microseconds of serialisation to every launch)
     tc_ms, tc_n = e.time_tensor_core(5, 50)
     achieved = conv_bytes / (tc_ms * 1e-3) / 1e9
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "conv_traffic.json")
-    if os.path.exists(tpath) and args.workload == "c2":
-        traffic = json.load(open(tpath)).get("traffic_bytes_per_launch")
+    traffic = CONV_TC_TRAFFIC_PER_LAUNCH.get(args.workload)
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "peak_kind": peak_kind,
+                "traffic_source": ("constant from an ncu capture of the 154 ResNet-152 launches (dram bytes read + written "
+                                   "per launch, profiles/conv_tc_resnet152_dram.md); not measured in this run"
+                                   if traffic is not None else None),
                 "kernel": "reef_conv_tc_kernel (tcgen05 TF32 convolution/matmul: the %d launches of one %s pass as a CUDA "
                           "graph of their own, timed with CUDA events over 50 replays)" % (tc_n, wl["rt"]),
                 "algorithmic_bytes_per_pass": conv_bytes, "algorithmic_bytes_per_launch": conv_bytes / max(1, tc_n),
@@ -374,8 +410,8 @@ def main():
     e.close()
 
     # ---- aggregate over ranks --------------------------------------------------------------------
-    value = total_inf / region_s
-    ms_per_step = 1000.0 * region_s / max(1, rt_r["completed"])
+    value = rt_r["completed"] / region_s + be_inf_s
+    ms_per_step = 1000.0 * region_s / max(1, args.steps)
     e2e_value = e2e_total
     from reef_b200 import replicas
     sums, maxes = replicas.aggregate(dist, {"value": value, "e2e": e2e_value, "launches": float(launches)},
@@ -403,6 +439,24 @@ def main():
         dt = time.perf_counter() - t0
         cpu = {"value": n_cpu / dt, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
                "sample": f"{n_cpu} sequential {wl['rt']} b1 inferences of the same schedule (plain-C oracle, OpenMP)"}
+        # second CPU row: the same schedule interpreted with PyTorch's CPU operators on all host cores
+        try:
+            from oracle import torch_ref
+            torch.set_num_threads(os.cpu_count() or 1)
+            te = torch_ref.TorchExecutor(base + ".json", base + ".param")
+            te.set_input(in_name, x)
+            te.execute()
+            n_t = 0
+            t0 = time.perf_counter()
+            while n_t < 3 or (time.perf_counter() - t0 < 8.0 and n_t < 200):
+                te.execute()
+                n_t += 1
+            dt = time.perf_counter() - t0
+            cpu["pytorch_cpu"] = {"value": n_t / dt, "unit": UNIT, "cores": torch.get_num_threads(),
+                                  "sample": f"{n_t} sequential {wl['rt']} b1 inferences, PyTorch {torch.__version__} CPU operators "
+                                            "over the same schedule and weights"}
+        except Exception as ex:   # the row is informative; the port above is the baseline
+            cpu["pytorch_cpu"] = {"unavailable": repr(ex)[:200]}
 
     if rank == 0:
         line = {"metric": wl["metric"], "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -411,6 +465,8 @@ def main():
                 "config": {"workload": wl["desc"], "inputs": "seeded synthetic: images N(0,1), token ids uniform",
                            "arithmetic": "convolutions and matmuls multiply in TF32 on tcgen05 with fp32 accumulation; everything else fp32",
                            "clients": "1 RT + %d BE per GPU" % n_be,
+                           "step": "%d back-to-back RT requests (%d timed after %d warm-up)" % (REQS_PER_STEP, n_req, n_warm),
+                           "cpu_slice": list(cpu_slice) if cpu_slice else None,
                            "l2": "every client owns a weight replica; the replicas streamed per pass exceed the 126 MB L2"},
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,

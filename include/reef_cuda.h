@@ -220,17 +220,29 @@ REEF_API reef_status reef_device_error(int* value);
 REEF_API reef_status reef_device_error_peek(int* value);
 REEF_API reef_status reef_device_error_set(int value);
 
-/* Phase trace of the tensor-core convolution (no reference counterpart; the reference has wall-clock stamps
- * only, scheduler.h:54-56).  While enabled, block (0,0) of every tensor-core launch records the SM clock at
- * {0 entry, 1 set-up done, 2 ring filled, 3 peers up, 4 first K block landed, 5 last K block landed,
- * 6 accumulator complete, 7 tile staged, 8 exchange complete, 9 rows finished, 10 TMEM freed};
- * reef_trace_read copies the 16-word record of the latest launch (call after synchronising). */
-REEF_API reef_status reef_trace_enable(int on);
-REEF_API reef_status reef_trace_read(int64_t* stamps16);
-
-/* Profiling aid (no reference counterpart): occupies `s` with a one-thread kernel for `ns` nanoseconds
- * (clamped to 20 ms, bounded loop) so that launches queued behind it run back to back. */
+/* Occupies `s` with a one-thread kernel for `ns` nanoseconds (clamped to 20 ms, bounded loop).  Used by the kernel
+ * profiler (HybridExecutor::profile_kernels, which writes <model>.profile.json) to hold a stream while a whole pass
+ * is queued behind it, so that the events between kernels measure no launch latency.  No reference counterpart (the
+ * reference's profiler binary is not in its tree, resource/Makefile:32-36). */
 REEF_API reef_status reef_stream_delay(reef_stream_t s, uint64_t ns);
+
+/* Preemption latency on the device's own clock (no reference counterpart: the reference measures host wall clock
+ * around its switch, scheduler.cpp:378,406-410).  While armed, the first best-effort block that finds the preempt
+ * flag up records %globaltimer (a minimum over blocks) and every best-effort block that leaves because of the flag
+ * records it again (a maximum): last_leave - first_seen is the time from the flag becoming visible on the device to
+ * the last best-effort block having left.  reef_preempt_stamps_read returns both (0, 0 when no block saw the flag)
+ * and re-arms; call it when the best-effort streams have drained.  Arming allocates 16 bytes of device memory. */
+REEF_API reef_status reef_preempt_stamps_arm(int on);
+REEF_API reef_status reef_preempt_stamps_read(uint64_t* first_seen_ns, uint64_t* last_leave_ns);
+
+/* A preempt flag the host can raise with a plain store (the alternative to reef_write32_async on a device flag;
+ * GPUWriteValue32Async, reference: hip_impl.h:20): 4 bytes of pinned host memory mapped into the device's address
+ * space.  *dev_ptr is what kernels are given as their preempt flag; reef_flag_set stores through host_ptr with
+ * release semantics and returns at once.  Every device-side poll is then a read across PCIe, which is why the
+ * scheduler's default stays the device-resident flag. */
+REEF_API reef_status reef_flag_alloc_mapped(uint32_t** host_ptr, reef_dptr_t* dev_ptr);
+REEF_API reef_status reef_flag_free_mapped(uint32_t* host_ptr);
+REEF_API reef_status reef_flag_set(uint32_t* host_ptr, uint32_t value);
 
 /* Number of kernels this library launched since load (its own kernels only; graph replays count
  * the kernels inside the graph). */

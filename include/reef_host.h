@@ -55,8 +55,10 @@ REEF_HOST_API int reef_executor_execute_graph(reef_executor_t e);           /* C
 REEF_HOST_API int reef_executor_execute_dispatch(reef_executor_t e);        /* every kernel through the dispatcher, unpadded */
 /* Best-effort run with the preempt flag raised `delay_us` after the first launch (host timer), then
  * resumed from the first kernel whose completion counter is short until the model is done.
- * *restarts = number of resume rounds, *first_incomplete = restart kernel of the first round. */
-REEF_HOST_API int reef_executor_execute_preempt_resume(reef_executor_t e, int delay_us, int* restarts, int* first_incomplete);
+ * *restarts = number of resume rounds, *first_incomplete = restart kernel of the first round,
+ * *first_count (may be NULL) = that kernel's completion counter when it was found short. */
+REEF_HOST_API int reef_executor_execute_preempt_resume(reef_executor_t e, int delay_us, int* restarts, int* first_incomplete,
+                                                       int* first_count);
 /* Completion counters (task slots) and logical block counts per kernel, n entries each. */
 REEF_HOST_API int reef_executor_task_slots(reef_executor_t e, int* slots, int* block_nums, size_t n);
 /* Average milliseconds of `iters` executions after `warmup` (mode: 0 raw launches, 1 graph, 2 best-effort). */
@@ -108,14 +110,29 @@ typedef struct {
 REEF_HOST_API int reef_sched_task_info(reef_scheduler_t s, uint32_t tid, reef_task_info_t* info);
 REEF_HOST_API int reef_sched_set_wait_sync(reef_scheduler_t s, int value);
 REEF_HOST_API int reef_sched_set_be_stream_cap(reef_scheduler_t s, int value);
+/* Preempt flag in pinned host memory raised by a host store instead of a stream write (before the first load_model). */
+REEF_HOST_API int reef_sched_use_mapped_flag(reef_scheduler_t s);
+/* Device-clock preemption stamps on/off (implies wait_sync). */
+REEF_HOST_API int reef_sched_set_device_stamps(reef_scheduler_t s, int on);
+/* Dynamic-kernel-padding controller: padded real-time tasks may take (1 + value) x their latency alone; 0 = no limit. */
+REEF_HOST_API int reef_sched_set_pad_slowdown_target(reef_scheduler_t s, double value);
+/* CPU placement: scheduler thread on first_cpu, real-time clients of reef_run_clients on first_cpu + 1, best-effort
+ * clients on the rest of [first_cpu, first_cpu + n_cpus); n_cpus < 3 pins nothing.  Call before reef_sched_run. */
+REEF_HOST_API int reef_sched_set_cpu_slice(reef_scheduler_t s, int first_cpu, int n_cpus);
 REEF_HOST_API int reef_sched_set_rt_graph(reef_scheduler_t s, int value);
 REEF_HOST_API int reef_sched_run(reef_scheduler_t s);
 REEF_HOST_API int reef_sched_shutdown(reef_scheduler_t s);
 REEF_HOST_API int64_t reef_sched_avg_preempt_latency(reef_scheduler_t s);
 REEF_HOST_API int64_t reef_sched_avg_kernel_sel_latency(reef_scheduler_t s);
 typedef struct {
-    uint64_t preempt_count, preempt_ns_sum, preempt_ns_max;
+    uint64_t preempt_count, preempt_ns_sum, preempt_ns_max;   /* flag raised + queued launches dropped + tasks rolled back */
     uint64_t rt_tasks, be_tasks, be_tasks_padded_to_finish, padded_kernels, padded_blocks;
+    /* preemptions that also waited for the drain (set_wait_sync): host clock from the flag write to "best-effort
+     * streams idle and completion counters read" — what the reference's figure covers, whose switch ends with the
+     * running wavefronts killed (scheduler.cpp:332-345,406-410) */
+    uint64_t drain_count, drain_ns_sum, drain_ns_max;
+    /* the same on the device's clock (set_device_stamps): first best-effort block that saw the flag -> last one that left */
+    uint64_t dev_count, dev_ns_sum, dev_ns_max;
 } reef_sched_stats_t;
 REEF_HOST_API int reef_sched_stats(reef_scheduler_t s, reef_sched_stats_t* out);
 

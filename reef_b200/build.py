@@ -25,6 +25,11 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared", "-cudart", "static",
 ]
 CXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-pthread", "-Wall"]
+# REEF_DEBUG_AIDS=1 in the environment builds the development flavour: phase-trace stamps in the tensor-core kernel,
+# reef_trace_* entry points (include/reef_debug_aids.h), REEF_PAD_* / REEF_PDL environment knobs, padding-loop statistics
+if os.environ.get("REEF_DEBUG_AIDS", "") not in ("", "0"):
+    NVCC_FLAGS.append("-DREEF_DEBUG_AIDS")
+    CXX_FLAGS.append("-DREEF_DEBUG_AIDS")
 
 
 def _nvcc() -> str:

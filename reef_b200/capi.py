@@ -39,7 +39,9 @@ class TaskInfo(C.Structure):
 
 class SchedStats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("preempt_count", "preempt_ns_sum", "preempt_ns_max", "rt_tasks", "be_tasks",
-                                          "be_tasks_padded_to_finish", "padded_kernels", "padded_blocks")]
+                                          "be_tasks_padded_to_finish", "padded_kernels", "padded_blocks",
+                                          "drain_count", "drain_ns_sum", "drain_ns_max",
+                                          "dev_count", "dev_ns_sum", "dev_ns_max")]
 
 
 class Client(C.Structure):
@@ -207,11 +209,14 @@ class HybridExecutor:
     def execute_dispatch(self):
         _check(self._lib.reef_executor_execute_dispatch(self._h), "execute_dispatch", self._err())
 
-    def execute_preempt_resume(self, delay_us: int):
-        restarts, first = C.c_int(), C.c_int()
+    def execute_preempt_resume(self, delay_us: int, with_count: bool = False):
+        """Best-effort run, flag raised ``delay_us`` after the first launch, resumed until done.  Returns (restarts,
+        first incomplete kernel) and, with ``with_count``, that kernel's completion counter when it was found short."""
+        restarts, first, count = C.c_int(), C.c_int(), C.c_int()
         _check(self._lib.reef_executor_execute_preempt_resume(self._h, C.c_int(delay_us), C.byref(restarts),
-                                                              C.byref(first)), "execute_preempt_resume", self._err())
-        return restarts.value, first.value
+                                                              C.byref(first), C.byref(count)), "execute_preempt_resume",
+               self._err())
+        return (restarts.value, first.value, count.value) if with_count else (restarts.value, first.value)
 
     def task_slots(self):
         n = self.num_kernels()
@@ -344,6 +349,18 @@ class REEFScheduler:
 
     def set_wait_sync(self, v: bool):
         self._lib.reef_sched_set_wait_sync(self._h, C.c_int(int(v)))
+
+    def use_mapped_flag(self):
+        _check(self._lib.reef_sched_use_mapped_flag(self._h), "use_mapped_flag", self._err())
+
+    def set_device_stamps(self, on: bool):
+        _check(self._lib.reef_sched_set_device_stamps(self._h, C.c_int(int(on))), "set_device_stamps", self._err())
+
+    def set_pad_slowdown_target(self, v: float):
+        self._lib.reef_sched_set_pad_slowdown_target(self._h, C.c_double(v))
+
+    def set_cpu_slice(self, first_cpu: int, n_cpus: int):
+        self._lib.reef_sched_set_cpu_slice(self._h, C.c_int(first_cpu), C.c_int(n_cpus))
 
     def set_be_stream_cap(self, v: int):
         self._lib.reef_sched_set_be_stream_cap(self._h, C.c_int(v))

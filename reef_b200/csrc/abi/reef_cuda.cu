@@ -7,6 +7,9 @@
 #include <vector>
 
 #include "../kernels/registry.h"
+#ifdef REEF_DEBUG_AIDS
+#include "../../../include/reef_debug_aids.h"
+#endif
 
 using namespace reef;
 
@@ -366,6 +369,39 @@ reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us) {
 
 uint64_t reef_launch_count(void) { return launch_count(); }
 
+reef_status reef_preempt_stamps_arm(int on) { return preempt_stamps_arm(on); }
+reef_status reef_preempt_stamps_read(uint64_t* first_seen_ns, uint64_t* last_leave_ns) {
+    unsigned long long v[2] = {0, 0};
+    int rc = preempt_stamps_read(v);
+    if (rc != REEF_SUCC) return rc;
+    if (first_seen_ns) *first_seen_ns = v[0] == ~0ull ? 0 : v[0];
+    if (last_leave_ns) *last_leave_ns = v[1];
+    return REEF_SUCC;
+}
+
+// A preempt flag in pinned host memory that the device reads through a mapped pointer: the host raises it with a
+// plain store (no stream operation, no driver call), the price being that every poll of a best-effort block is a
+// read across PCIe instead of an L2 hit.
+reef_status reef_flag_alloc_mapped(uint32_t** host_ptr, reef_dptr_t* dev_ptr) {
+    void* h = nullptr;
+    void* d = nullptr;
+    CK(cudaHostAlloc(&h, 64, cudaHostAllocMapped));
+    CK(cudaHostGetDevicePointer(&d, h, 0));
+    *(volatile uint32_t*)h = 0;
+    *host_ptr = (uint32_t*)h;
+    *dev_ptr = (reef_dptr_t)d;
+    return REEF_SUCC;
+}
+reef_status reef_flag_free_mapped(uint32_t* host_ptr) {
+    CK(cudaFreeHost(host_ptr));
+    return REEF_SUCC;
+}
+reef_status reef_flag_set(uint32_t* host_ptr, uint32_t value) {
+    if (!host_ptr) return REEF_FAIL;
+    __atomic_store_n(host_ptr, value, __ATOMIC_RELEASE);
+    return REEF_SUCC;
+}
+
 reef_status reef_device_error(int* value) {
     volatile int* w = nullptr;
     int rc = tc_error_word_host(&w);
@@ -389,8 +425,10 @@ reef_status reef_device_error_set(int value) {
     return REEF_SUCC;
 }
 
+#ifdef REEF_DEBUG_AIDS
 reef_status reef_trace_enable(int on) { return tc_trace_enable(on); }
 reef_status reef_trace_read(int64_t* stamps16) { return tc_trace_read((long long*)stamps16); }
+#endif
 
 reef_status reef_stream_delay(reef_stream_t s, uint64_t ns) { return launch_delay((cudaStream_t)s, ns); }
 

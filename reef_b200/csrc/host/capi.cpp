@@ -1,6 +1,9 @@
 // C entry points over the C++ host classes (see include/reef_host.h).
 #include "../../../include/reef_host.h"
 
+#include <pthread.h>
+#include <sched.h>
+
 #include <algorithm>
 #include <atomic>
 #include <chrono>
@@ -125,8 +128,9 @@ int reef_executor_execute_graph(reef_executor_t e) {
     return reef_stream_sync(e->exe.stream());
 }
 int reef_executor_execute_dispatch(reef_executor_t e) { return e->exe.execute_dispatch(); }
-int reef_executor_execute_preempt_resume(reef_executor_t e, int delay_us, int* restarts, int* first_incomplete) {
-    return e->exe.execute_preempt_resume(delay_us, restarts, first_incomplete);
+int reef_executor_execute_preempt_resume(reef_executor_t e, int delay_us, int* restarts, int* first_incomplete,
+                                         int* first_count) {
+    return e->exe.execute_preempt_resume(delay_us, restarts, first_incomplete, first_count);
 }
 int reef_executor_task_slots(reef_executor_t e, int* slots, int* block_nums, size_t n) {
     if (n < e->exe.num_kernels()) return OutOfRange;
@@ -288,6 +292,10 @@ int reef_sched_inject_launch_failures(reef_scheduler_t s, uint32_t mid, int n) {
 }
 int reef_sched_set_wait_sync(reef_scheduler_t s, int v) { s->sched->set_wait_sync(v != 0); return Succ; }
 int reef_sched_set_be_stream_cap(reef_scheduler_t s, int v) { s->sched->set_be_stream_cap(v); return Succ; }
+int reef_sched_use_mapped_flag(reef_scheduler_t s) { return s->sched->use_mapped_flag(); }
+int reef_sched_set_device_stamps(reef_scheduler_t s, int on) { return s->sched->set_device_stamps(on != 0); }
+int reef_sched_set_pad_slowdown_target(reef_scheduler_t s, double v) { s->sched->set_pad_slowdown_target(v); return Succ; }
+int reef_sched_set_cpu_slice(reef_scheduler_t s, int first_cpu, int n_cpus) { s->sched->set_cpu_slice(first_cpu, n_cpus); return Succ; }
 int reef_sched_set_rt_graph(reef_scheduler_t s, int v) { s->sched->set_rt_graph(v != 0); return Succ; }
 int reef_sched_run(reef_scheduler_t s) { return s->sched->run(); }
 int reef_sched_shutdown(reef_scheduler_t s) { return s->sched->shutdown(); }
@@ -303,6 +311,12 @@ int reef_sched_stats(reef_scheduler_t s, reef_sched_stats_t* out) {
     out->be_tasks_padded_to_finish = st.be_tasks_padded_to_finish;
     out->padded_kernels = st.padded_kernels;
     out->padded_blocks = st.padded_blocks;
+    out->drain_count = st.drain_count;
+    out->drain_ns_sum = st.drain_ns_sum;
+    out->drain_ns_max = st.drain_ns_max;
+    out->dev_count = st.dev_count;
+    out->dev_ns_sum = st.dev_ns_sum;
+    out->dev_ns_max = st.dev_ns_max;
     return Succ;
 }
 
@@ -325,6 +339,22 @@ int reef_run_clients(reef_scheduler_t s, reef_client_t* clients, size_t n) {
             reef_client_t& c = clients[i];
             REEFScheduler* sc = s->sched;
             const bool bounded = c.max_requests > 0;
+            {
+                // CPU placement inside the scheduler's slice: the real-time client gets a core of its own next to the
+                // scheduler thread's, best-effort clients share the rest
+                int first = -1, count = 0;
+                sc->cpu_slice(&first, &count);
+                if (first >= 0 && count >= 3) {
+                    cpu_set_t set;
+                    CPU_ZERO(&set);
+                    if (sc->is_realtime_model(c.mid)) {
+                        CPU_SET(first + 1, &set);
+                    } else {
+                        for (int k = 2; k < count; k++) CPU_SET(first + k, &set);
+                    }
+                    pthread_setaffinity_np(pthread_self(), sizeof(set), &set);
+                }
+            }
             const std::string in_name = c.input_name ? c.input_name : "data";
             uint64_t done = 0;
             c.completed = 0;

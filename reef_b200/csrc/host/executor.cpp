@@ -463,12 +463,13 @@ static void busy_wait_us(int us) {
     }
 }
 
-Status HybridExecutor::execute_preempt_resume(int delay_us, int* restarts, int* first_incomplete) {
+Status HybridExecutor::execute_preempt_resume(int delay_us, int* restarts, int* first_incomplete, int* first_count) {
     GPUStream_t flag_stream;
     GPU_RETURN_STATUS(reef_stream_create(&flag_stream, 1));
     const int n = (int)num_kernels();
     int from = 0, rounds = 0;
     if (first_incomplete) *first_incomplete = -1;
+    if (first_count) *first_count = -1;
     GPU_RETURN_STATUS(reef_write32_async(flag_stream, preempt_flag, 0));
     GPU_RETURN_STATUS(reef_stream_sync(flag_stream));
     reset_task_slots(s, 0);
@@ -492,6 +493,7 @@ Status HybridExecutor::execute_preempt_resume(int delay_us, int* restarts, int* 
         }
         if (k >= n) break;
         if (rounds == 0 && first_incomplete) *first_incomplete = k;
+        if (rounds == 0 && first_count) *first_count = task_slots_host[k];
         reset_task_slots(s, k);
         from = k;
         rounds++;

@@ -135,7 +135,8 @@ public:
     // every kernel through the dispatcher without a best-effort partner, then sync
     Status execute_dispatch(GPUStream_t stream = nullptr);
     // best-effort run, flag raised after delay_us, resumed from the first incomplete kernel until done
-    Status execute_preempt_resume(int delay_us, int* restarts, int* first_incomplete);
+    // (*first_count: the completion counter of that kernel when it was found short — between 0 and its block count)
+    Status execute_preempt_resume(int delay_us, int* restarts, int* first_incomplete, int* first_count = nullptr);
     // device time of each kernel (us, CUDA events, average of iters)
     Status profile_kernels(int iters, float* us);
     // one persistent wave of kernel idx: sms*occupancy logical blocks through the dispatcher (us)

@@ -1,5 +1,8 @@
 #include "scheduler.h"
 
+#include <pthread.h>
+#include <sched.h>
+
 #include <algorithm>
 #include <cassert>
 #include <cstdlib>
@@ -47,6 +50,8 @@ REEFScheduler::REEFScheduler(ScheduleMode _mode, int _device)
         num_sms = 0;   // run()/load_model() refuse to work
     }
     be_stream_device_queue_cap = mode == WaitPreempt ? 1024 : 2;
+#ifdef REEF_DEBUG_AIDS
+    // development builds: the padding parameters can be set from the environment for sweeps
     if (const char* v = getenv("REEF_PAD_DEPTH")) set_pad_limits(atoi(v), pad_overcommit, pad_quantum);
     if (const char* v = getenv("REEF_PAD_OVERCOMMIT")) set_pad_limits(pad_depth, atoi(v), pad_quantum);
     if (const char* v = getenv("REEF_PAD_QUANTUM")) set_pad_limits(pad_depth, pad_overcommit, atoi(v));
@@ -55,10 +60,12 @@ REEFScheduler::REEFScheduler(ScheduleMode _mode, int _device)
     if (const char* v = getenv("REEF_PAD_PIECE_CAP")) pad_piece_cap = atoi(v);
     if (const char* v = getenv("REEF_PAD_PIECE_MB")) pad_piece_bytes = atof(v) * 1e6;
     if (const char* v = getenv("REEF_PAD_TARGET")) set_pad_slowdown_target(atof(v));
+#endif
 }
 
 REEFScheduler::~REEFScheduler() {
     if (scheduler && scheduler->joinable()) shutdown();
+#ifdef REEF_DEBUG_AIDS
     if (getenv("REEF_PAD_TRACE") && pad_trace.calls) {
         const PadTrace& t = pad_trace;
         fprintf(stderr,
@@ -75,6 +82,7 @@ REEFScheduler::~REEFScheduler() {
         fprintf(stderr, "[reef]   slowdown controller: target %.3f, smoothed ratio %.3f, rate %.1f kernels per window\n", pad_target,
                 pad_ratio_ema, pad_rate);
     }
+#endif
     reef_gpu_init(device);
     reef_device_sync();
     model_pool.clear();
@@ -87,7 +95,35 @@ REEFScheduler::~REEFScheduler() {
         }
     if (rt_queue && rt_queue->stream) reef_stream_destroy(rt_queue->stream);
     if (preempt_stream) reef_stream_destroy(preempt_stream);
+    if (device_stamps) reef_preempt_stamps_arm(0);
+    if (mapped_flag_host) reef_flag_free_mapped(mapped_flag_host);
+    else if (preempt_flag) reef_free(preempt_flag);
+}
+
+Status REEFScheduler::use_mapped_flag() {
+    if (model_pool_size.load() != 0 || mapped_flag_host != nullptr) return Status::Fail;   // executors already hold the flag
+    GPU_RETURN_STATUS(reef_gpu_init(device));
+    uint32_t* h = nullptr;
+    executor::GPUDevicePtr_t d = 0;
+    GPU_RETURN_STATUS(reef_flag_alloc_mapped(&h, &d));
     if (preempt_flag) reef_free(preempt_flag);
+    mapped_flag_host = h;
+    preempt_flag = d;
+    return Status::Succ;
+}
+
+Status REEFScheduler::set_device_stamps(bool on) {
+    GPU_RETURN_STATUS(reef_gpu_init(device));
+    GPU_RETURN_STATUS(reef_preempt_stamps_arm(on ? 1 : 0));
+    device_stamps = on;
+    if (on) wait_sync = true;
+    return Status::Succ;
+}
+
+// raises or clears the preempt flag; returns when the new value is on its way (mapped flag: stored)
+void REEFScheduler::write_flag(uint32_t v) {
+    if (mapped_flag_host) reef_flag_set(mapped_flag_host, v);
+    else reef_write32_async(preempt_stream, preempt_flag, v);
 }
 
 Status REEFScheduler::create_task_queue(std::shared_ptr<TaskQueue>& ret, bool rt) {
@@ -226,10 +262,13 @@ Status REEFScheduler::wait_task(TaskID tid) {
     std::shared_ptr<Task> task;
     Status st = get_task(tid, task);
     if (st != Status::Succ) return st;
-    // spin briefly (a real-time inference is tens of microseconds), then block on the task's condvar
-    auto t0 = sclock::now();
-    while (task->state.load(std::memory_order_acquire) != TaskState::Finish) {
-        if (ns_since(t0) > 2000000ull) break;
+    // a real-time caller spins briefly (its inference takes well under a millisecond), then blocks on the task's
+    // condvar; a best-effort caller blocks at once and leaves its core to the threads that are on the critical path
+    if (task->qid == rt_queue_id) {
+        auto t0 = sclock::now();
+        while (task->state.load(std::memory_order_acquire) != TaskState::Finish) {
+            if (ns_since(t0) > 2000000ull) break;
+        }
     }
     {
         std::unique_lock<std::mutex> lock(task->mtx);
@@ -308,6 +347,12 @@ Status REEFScheduler::run() {
     }
     _shutdown.store(false);
     scheduler.reset(new std::thread([this] {
+        if (cpu_first >= 0 && cpu_count >= 3) {
+            cpu_set_t set;
+            CPU_ZERO(&set);
+            CPU_SET(cpu_first, &set);
+            pthread_setaffinity_np(pthread_self(), sizeof(set), &set);   // best effort: a refusal changes nothing else
+        }
         reef_gpu_init(device);
         auto last_busy = sclock::now();
         while (!this->_shutdown.load()) {
@@ -401,7 +446,7 @@ void REEFScheduler::retire(TaskQueue& q, Task& t) {
     }
 }
 
-void REEFScheduler::reset_preempt_flag_async() { reef_write32_async(preempt_stream, preempt_flag, 0); }
+void REEFScheduler::reset_preempt_flag_async() { write_flag(0); }
 
 // reference: scheduler.cpp:305-346.  Step 1 raises the flag; step 2 "clears the host queue": the kernels
 // not yet handed to the stream simply stay unlaunched, and the task rolls back to the first kernel not
@@ -409,16 +454,17 @@ void REEFScheduler::reset_preempt_flag_async() { reef_write32_async(preempt_stre
 // idempotent and the schedules generated here never reuse a buffer, so re-running is exact); step 3 has
 // no CUDA form — running blocks leave at their next flag poll.
 void REEFScheduler::preempt_reset() {
-    reef_write32_async(preempt_stream, preempt_flag, 1);
+    auto t_flag = sclock::now();
+    write_flag(1);
     uint32_t nq = be_queue_cnt.load();
-    std::vector<std::shared_ptr<Task>> hit;   // tasks that had kernels on their stream
+    std::vector<std::pair<std::shared_ptr<Task>, TaskQueue*>> hit;   // tasks that had kernels on their stream
     for (uint32_t i = 0; i < nq; i++) {
         auto& q = *be_queues[i];
         if (q.task_queue.empty()) continue;
         auto task = q.task_queue.front();
         if (task->get_state() == TaskState::Executing && task->all_issued_by_padding) continue;   // nothing to abort
         if (task->get_state() == TaskState::Executing) {
-            hit.push_back(task);
+            hit.push_back({task, &q});
             // An event that fires after the flag went up may belong to a kernel that left early, so the
             // window is not consulted here: kernel_offset stays at what the last poll saw complete.
             for (auto& f : q.inflight) q.free_events.push_back(f.ev);
@@ -429,29 +475,43 @@ void REEFScheduler::preempt_reset() {
             task->needs_recover = true;
         }
     }
-    reef_stream_sync(preempt_stream);
+    if (!mapped_flag_host) reef_stream_sync(preempt_stream);
+    last_flag_ns = ns_since(t_flag);   // flag raised, queued launches dropped, tasks rolled back
     if (wait_sync) {
-        // bounded replacement of the reference's reset-until-idle loop (scheduler.cpp:336-345), then the
-        // exact restart point from the completion counters
+        // Bounded replacement of the reference's reset-until-idle loop (scheduler.cpp:336-345), then the exact
+        // restart point from the completion counters.  Every hit task's counters are copied on the task's OWN
+        // stream, behind its kernels in flight (which leave at their next flag poll), so "copy landed" also means
+        // "stream drained"; the copies of all tasks run side by side and there is one wait per stream.
+        for (auto& h : hit) h.first->model->executor.copy_be_kernel_offset(h.second->stream);
         for (uint32_t i = 0; i < nq; i++) reef_preempt_wait(be_queues[i]->stream, 200000);
-        for (auto& task : hit) {
-            auto& exe = task->model->executor;
-            exe.copy_be_kernel_offset(preempt_stream);
-            reef_stream_sync(preempt_stream);
-            int k = exe.get_be_kernel_offset(task->kernel_offset);
+        for (auto& h : hit) {
+            auto& task = h.first;
+            int k = task->model->executor.get_be_kernel_offset(task->kernel_offset);
             if (k > task->kernel_offset) {
                 task->kernel_offset = k;
                 task->block_offset = 0;
             }
             task->launch_offset = task->kernel_offset;
         }
+        const uint64_t ns = ns_since(t_flag);
+        drain_count++;
+        drain_ns_sum += ns;
+        drain_ns_max = std::max(drain_ns_max, ns);
+        if (device_stamps) {
+            uint64_t first = 0, last = 0;
+            if (reef_preempt_stamps_read(&first, &last) == REEF_SUCC && first != 0 && last >= first) {
+                dev_count++;
+                dev_ns_sum += last - first;
+                dev_ns_max = std::max(dev_ns_max, last - first);
+            }
+        }
     }
 }
 
 // reference: scheduler.cpp:348-372
 void REEFScheduler::preempt_wait() {
-    reef_write32_async(preempt_stream, preempt_flag, 1);
-    reef_stream_sync(preempt_stream);
+    write_flag(1);
+    if (!mapped_flag_host) reef_stream_sync(preempt_stream);
     uint32_t nq = be_queue_cnt.load();
     for (uint32_t i = 0; i < nq; i++) reef_preempt_wait(be_queues[i]->stream, 1000000);
     for (uint32_t i = 0; i < nq; i++) {
@@ -500,7 +560,8 @@ void REEFScheduler::preempt_be_tasks() {
         default:
             break;
     }
-    uint64_t ns = ns_since(start);
+    // with wait_sync the drain is accounted on its own (drain_*): this figure stays "flag raised and rolled back"
+    uint64_t ns = (mode == REEF || mode == Reset) ? last_flag_ns : ns_since(start);
     preempt_count++;
     preempt_latency_sum += ns;
     preempt_latency_max = std::max(preempt_latency_max, ns);
@@ -514,7 +575,8 @@ int64_t REEFScheduler::avg_kernel_sel_latency() const {
 }
 REEFScheduler::Stats REEFScheduler::stats() const {
     return Stats{preempt_count, preempt_latency_sum, preempt_latency_max, n_rt_tasks, n_be_tasks,
-                 n_be_padded_finish, n_padded_kernels, n_padded_blocks};
+                 n_be_padded_finish, n_padded_kernels, n_padded_blocks,
+                 drain_count, drain_ns_sum, drain_ns_max, dev_count, dev_ns_sum, dev_ns_max};
 }
 
 bool REEFScheduler::any_be_waiting() {

@@ -95,7 +95,22 @@ public:
     Status wait_task(TaskID tid);
     Status get_task(TaskID tid, std::shared_ptr<Task>& t);
     ScheduleMode sche_mode() const { return mode; }
+    // wait_sync: a preemption also waits (bounded) until the best-effort streams have drained and reads the completion
+    // counters for the exact restart kernel (reference: scheduler.cpp:336-345, the reset-until-idle loop)
     void set_wait_sync(bool value) { wait_sync = value; }
+    // The preempt flag lives in device memory and is raised by an ordered 32-bit stream write (GPUWriteValue32Async,
+    // reference: hip_impl.h:20).  With the mapped flag it lives in pinned host memory instead and is raised by a plain
+    // host store; every device-side poll then crosses PCIe.  Call before the first load_model.
+    Status use_mapped_flag();
+    // Records, on the device's own clock, when the flag was first seen by a best-effort block and when the last one
+    // left (measurement; read once per preemption after the drain, so it implies wait_sync).
+    Status set_device_stamps(bool on);
+    // CPU placement of the threads that serve this GPU (no reference counterpart; one scheduler per GPU on a shared
+    // host): the scheduler thread is pinned to `first_cpu`, a real-time closed-loop client of reef_run_clients to
+    // first_cpu + 1, best-effort clients to the rest of [first_cpu, first_cpu + n_cpus).  n_cpus < 3 pins nothing.
+    void set_cpu_slice(int first_cpu, int n_cpus) { cpu_first = first_cpu; cpu_count = n_cpus; }
+    void cpu_slice(int* first_cpu, int* n_cpus) const { *first_cpu = cpu_first; *n_cpus = cpu_count; }
+    bool is_realtime_model(ModelID mid) const { return mid < model_pool_size.load() && model_pool[mid]->qid == rt_queue_id; }
     void set_be_stream_cap(int value) { be_stream_device_queue_cap = value < 1 ? 1 : value; }
     // real-time tasks that find no best-effort work replay a CUDA graph of the model (default on)
     void set_rt_graph(bool value) { rt_graph = value; }
@@ -132,6 +147,10 @@ public:
     struct Stats {
         uint64_t preempt_count, preempt_ns_sum, preempt_ns_max;
         uint64_t rt_tasks, be_tasks, be_tasks_padded_to_finish, padded_kernels, padded_blocks;
+        // preemptions that waited for the drain (wait_sync): host clock from the flag write to the best-effort streams
+        // idle and the counters read; device clock from the first block that saw the flag to the last that left
+        uint64_t drain_count, drain_ns_sum, drain_ns_max;
+        uint64_t dev_count, dev_ns_sum, dev_ns_max;
     };
     Stats stats() const;
     const std::string& error() const { return err_; }
@@ -246,6 +265,13 @@ private:
         uint64_t q_empty = 0, q_draining = 0, q_full = 0, q_issued = 0, q_nofit = 0, segments = 0, singles = 0;
     } pad_trace;
     uint64_t preempt_count, preempt_latency_sum, preempt_latency_max;
+    uint64_t drain_count = 0, drain_ns_sum = 0, drain_ns_max = 0;
+    uint64_t dev_count = 0, dev_ns_sum = 0, dev_ns_max = 0;
+    uint32_t* mapped_flag_host = nullptr;   // non-null: the flag is pinned host memory raised by a host store
+    bool device_stamps = false;
+    int cpu_first = -1, cpu_count = 0;
+    uint64_t last_flag_ns = 0;
+    void write_flag(uint32_t v);
     uint64_t kernel_sel_count, kernel_sel_latency_sum;
     uint64_t n_rt_tasks, n_be_tasks, n_be_padded_finish, n_padded_kernels, n_padded_blocks;
     std::string err_;

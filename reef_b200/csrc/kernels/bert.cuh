@@ -98,7 +98,7 @@ constexpr int kAttRows = 16;
 constexpr int kAttChunk = 64;
 constexpr int kAttD = 64;
 constexpr int kAttSmem = (2 * kAttChunk * (kAttD + 1) + 8 * 2 * kAttD + 8 * 2 * kAttChunk) * 4;   // 41.3 KB
-__device__ __forceinline__ bool body_attention(const KTask& t, int vb, unsigned char* smem_raw, const int*) {
+__device__ __forceinline__ bool body_attention(const KTask& t, int vb, unsigned char* smem_raw, const int* flag) {
     const int S = t.p.raw[0], heads = t.p.raw[1], has_mask = t.p.raw[3];
     const int H = heads * kAttD;
     const float* qkv = (const float*)t.a[0];
@@ -124,7 +124,13 @@ __device__ __forceinline__ bool body_attention(const KTask& t, int vb, unsigned 
     for (int r = 0; r < 2; r++) { m[r] = ninf; l[r] = 0.f; acc[r][0] = acc[r][1] = 0.f; }
 
     for (int k0 = 0; k0 < S; k0 += kAttChunk) {
-        __syncthreads();   // previous chunk fully consumed
+        // the barrier says the previous chunk is fully consumed; in the best-effort flavour it also carries the
+        // loop-head poll of the preempt flag (an OR over the block, so that all threads take the same exit)
+        if (flag != nullptr) {
+            if (__syncthreads_or(ld_flag(flag))) return false;
+        } else {
+            __syncthreads();
+        }
         for (int i = threadIdx.x; i < kAttChunk * (kAttD / 4); i += kThreads) {
             const int j = i / (kAttD / 4), c = (i - j * (kAttD / 4)) * 4, key = k0 + j;
             float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;

@@ -268,11 +268,12 @@ int tc_build_params(const ConvP& p, const TcPlan& pl, void* const* a, TcParams* 
 }
 
 static bool g_attr_set[16] = {false};
-static long long* g_trace[16] = {nullptr};
 
-// Phase trace of the tensor-core convolution: when enabled, block (0,0) of every launch stamps the SM clock
-// at 11 points (entry, set-up done, ring filled, peers up, first K block landed, last K block landed,
-// accumulator complete, tile staged, exchange complete, rows finished, TMEM freed) into one 16-word device
+#ifdef REEF_DEBUG_AIDS
+static long long* g_trace[16] = {nullptr};
+// Phase trace of the tensor-core convolution (development builds only): when enabled, block (0,0) of every launch
+// stamps the SM clock at 11 points (entry, set-up done, ring filled, peers up, first K block landed, last K block
+// landed, accumulator complete, tile staged, exchange complete, rows finished, TMEM freed) into one 16-word device
 // record that the host reads back.
 int tc_trace_enable(int on) {
     int dev = 0;
@@ -296,21 +297,34 @@ int tc_trace_read(long long* out16) {
     if (cudaMemcpy(out16, g_trace[dev], 128, cudaMemcpyDeviceToHost) != cudaSuccess) return REEF_FAIL;
     return REEF_SUCC;
 }
-static int g_use_pdl = -1;
+#endif
 
-// one-time, per device: shared-memory opt-in of the kernel and the error word (never during a capture)
+// Programmatic dependent launch is on (development builds can switch it off with REEF_PDL=0, and for padded
+// best-effort pieces alone with REEF_PAD_PDL=0).
+static bool env_flag_on(const char* name) {
+#ifdef REEF_DEBUG_AIDS
+    const char* v = getenv(name);
+    return !(v && v[0] == '0');
+#else
+    (void)name;
+    return true;
+#endif
+}
+
+// one-time, per device: shared-memory opt-in of both flavours of the kernel and the error word (never during a capture)
 int tc_prepare_device() {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 16 && !g_attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute((const void*)reef_conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             226 * 1024);
-        if (e == cudaSuccess)   // the whole unified L1/shared array as shared memory, so that two CTAs are resident
-            e = cudaFuncSetAttribute((const void*)reef_conv_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                     cudaSharedmemCarveoutMaxShared);
-        if (e != cudaSuccess) {
-            set_error(std::string("cudaFuncSetAttribute(conv_tc): ") + cudaGetErrorString(e));
-            return REEF_FAIL;
+        const void* fns[2] = {(const void*)reef_conv_tc_kernel<false>, (const void*)reef_conv_tc_kernel<true>};
+        for (const void* fn : fns) {
+            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+            if (e == cudaSuccess)   // the whole unified L1/shared array as shared memory, so that two CTAs are resident
+                e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            if (e != cudaSuccess) {
+                set_error(std::string("cudaFuncSetAttribute(conv_tc): ") + cudaGetErrorString(e));
+                return REEF_FAIL;
+            }
         }
         int* w = nullptr;
         int rc = tc_error_word(&w);
@@ -322,10 +336,7 @@ int tc_prepare_device() {
 
 int tc_launch(const TcParams& P0, const TcPlan& pl, cudaStream_t st, const int* flag, int* slot, int tile_begin,
               int tile_count) {
-    if (g_use_pdl < 0) {
-        const char* v = getenv("REEF_PDL");
-        g_use_pdl = (v && v[0] == '0') ? 0 : 1;
-    }
+    static const bool use_pdl = env_flag_on("REEF_PDL"), pad_pdl = env_flag_on("REEF_PAD_PDL");
     TcParams P = P0;
     P.preempt_flag = flag;
     P.task_slot = slot;
@@ -336,11 +347,15 @@ int tc_launch(const TcParams& P0, const TcPlan& pl, cudaStream_t st, const int* 
         return REEF_OUT_OF_RANGE;
     }
     P.tile_begin = tile_begin;
+    P.stamps = flag != nullptr ? preempt_stamps_ptr() : nullptr;
+    P.trace = nullptr;
+#ifdef REEF_DEBUG_AIDS
     {
         int dev = 0;
         cudaGetDevice(&dev);
         P.trace = (dev >= 0 && dev < 16) ? g_trace[dev] : nullptr;
     }
+#endif
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(pl.splits, tile_count, 1);
@@ -356,20 +371,18 @@ int tc_launch(const TcParams& P0, const TcPlan& pl, cudaStream_t st, const int* 
         attrs[na].val.clusterDim.z = 1;
         na++;
     }
-    static int pad_pdl = -1;
-    if (pad_pdl < 0) {
-        const char* v = getenv("REEF_PAD_PDL");
-        pad_pdl = (v && v[0] == '0') ? 0 : 1;
-    }
     const bool piece = flag == nullptr && slot != nullptr;   // a padded best-effort piece
-    if (g_use_pdl && (!piece || pad_pdl)) {
+    if (use_pdl && (!piece || pad_pdl)) {
         attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attrs[na].val.programmaticStreamSerializationAllowed = 1;
         na++;
     }
     cfg.attrs = attrs;
     cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, reef_conv_tc_kernel, P);
+    // the best-effort flavour (flag polls at block entry and at the producer's loop head) is its own instantiation:
+    // the real-time flavour carries no poll
+    cudaError_t e = flag != nullptr ? cudaLaunchKernelEx(&cfg, reef_conv_tc_kernel<true>, P)
+                                    : cudaLaunchKernelEx(&cfg, reef_conv_tc_kernel<false>, P);
     if (e != cudaSuccess) {
         set_error(std::string("cudaLaunchKernelEx(conv_tc): ") + cudaGetErrorString(e));
         return REEF_FAIL;
@@ -378,7 +391,7 @@ int tc_launch(const TcParams& P0, const TcPlan& pl, cudaStream_t st, const int* 
 }
 
 int tc_func_attrs(const TcPlan& pl, cudaFuncAttributes* fa, int* occ) {
-    cudaError_t e = cudaFuncGetAttributes(fa, (const void*)reef_conv_tc_kernel);
+    cudaError_t e = cudaFuncGetAttributes(fa, (const void*)reef_conv_tc_kernel<false>);
     if (e != cudaSuccess) {
         set_error(std::string("cudaFuncGetAttributes(conv_tc): ") + cudaGetErrorString(e));
         return REEF_FAIL;

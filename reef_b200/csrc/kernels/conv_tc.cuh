@@ -58,6 +58,31 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
     return false;
 }
+// The same wait for the best-effort flavour's MMA thread: it also gives up when `abort_word` (shared memory, written
+// by the TMA producer of the same CTA when it saw the preempt flag) becomes non-zero.  0 = phase complete,
+// 1 = wait expired, 2 = abort requested.
+__device__ __forceinline__ int mbar_wait_abortable(uint32_t bar, uint32_t parity, const volatile uint32_t* abort_word) {
+    unsigned long long t0 = 0;
+    for (int i = 0; i < (1 << 26); i++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return 0;
+        if (*abort_word) return 2;
+        if ((i & 255) == 255) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > 1000000000ull) return 1;
+        }
+    }
+    return 1;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -217,9 +242,14 @@ __device__ __forceinline__ void tmem_free(uint32_t tmem, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(cols) : "memory");
 }
 
+// Phase trace: compiled in only with -DREEF_DEBUG_AIDS (a development aid; the default build carries no stamps)
+#ifdef REEF_DEBUG_AIDS
 __device__ __forceinline__ void tc_stamp(const TcParams& P, int slot) {
     if (P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0) P.trace[slot] = clock64();
 }
+#else
+__device__ __forceinline__ void tc_stamp(const TcParams&, int) {}
+#endif
 
 // Finishes the pixel rows [jb, je) a cluster rank owns after a K split: sums the partials of ranks 0..S-1 in
 // rank order (a fixed order: bit-reproducible), applies the epilogue and stores 512-byte rows.  RB rows per warp
@@ -263,6 +293,13 @@ __device__ __forceinline__ void tc_finish_split(const TcParams& P, const float* 
     }
 }
 
+// BE = best-effort flavour (reference wrapper contract: script/best_effort_kernel.py:22-33, with the polls the
+// reference gets for free from killing wavefronts): the preempt flag is read at block entry and, by the TMA producer,
+// at the head of its refill loop (every 4th K block).  A CTA that saw the flag stops loading, lets the tensor core
+// finish what has landed, and takes part in every cluster barrier; at the first barrier the ranks of a cluster
+// exchange what they saw, and if any rank stopped, ALL ranks skip the exchange, the stores and the completion counter —
+// the kernel is idempotent, so it is simply launched again later.  The real-time flavour carries none of this.
+template <bool BE>
 __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __grid_constant__ TcParams P) {
     extern __shared__ __align__(16) unsigned char tc_smem_raw[];
     // stage buffers need 1024-byte alignment (swizzle atom); carve barriers behind them
@@ -276,7 +313,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
     const uint32_t bar_full = ctrl, bar_empty = ctrl + 8 * TC_MAX_STAGES, bar_acc = ctrl + 16 * TC_MAX_STAGES;
     const uint32_t bar_red = bar_acc + 8;
     volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + P.region_bytes + 16 * TC_MAX_STAGES + 16);
-    volatile uint32_t* s_flags = s_tmem + 1;    // [0] abort (preempt flag seen), [1] wait expired
+    volatile uint32_t* s_flags = s_tmem + 1;    // [0] abort (preempt flag seen by this CTA), [1] wait expired,
+                                                //  [2] K blocks whose loads were issued when the producer stopped
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) tc_stamp(P, 0);
@@ -296,8 +334,9 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         }
         mbar_init(bar_acc, 1);
         mbar_init(bar_red, 1);
-        s_flags[0] = 0;
+        s_flags[0] = BE ? (uint32_t)(*reinterpret_cast<const volatile int*>(P.preempt_flag) != 0) : 0u;   // poll at block entry
         s_flags[1] = 0;
+        s_flags[2] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&P.tm_w) : "memory");
@@ -324,29 +363,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
     const int n_lim = min(P.n_valid, P.ptot - pix0);   // columns of this tile that are real pixels
     const int cpc = (n_lim + S - 1) / S;               // pixel rows one rank finishes
     const int jb = min(split * cpc, n_lim), je = min(jb + cpc, n_lim);
-    if (S > 1 && P.preempt_flag == nullptr && tid == 0) mbar_expect_tx(bar_red, (uint32_t)((S - 1) * (je - jb) * TC_BM * 4));
+    if (S > 1 && tid == 0) mbar_expect_tx(bar_red, (uint32_t)((S - 1) * (je - jb) * TC_BM * 4));
+    // best-effort flavour: what this CTA saw at entry.  Nothing is loaded then; the cluster agrees at its first barrier.
+    const bool abort0 = BE && s_flags[0] != 0;
 
-    // best-effort flavour: one flag read per cluster (rank 0), published to every CTA, so that all CTAs of
-    // a cluster take the same decision and none is left alone at a cluster barrier
-    bool abort = false;
-    if (P.preempt_flag != nullptr) {
-        if (tid == 0) {
-            s_flags[0] = (uint32_t)(*reinterpret_cast<const volatile int*>(P.preempt_flag) != 0);
-            if (S > 1) mbar_expect_tx(bar_red, (uint32_t)((S - 1) * (je - jb) * TC_BM * 4));
-        }
-        __syncthreads();
-        if (S > 1) {
-            cluster_sync_all();   // rank 0's observation is written, every peer is running and has armed its barrier
-            uint32_t f;
-            asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(f) : "r"(mapa_shared(smem_u32((const void*)&s_flags[0]), 0)) : "memory");
-            abort = f != 0;
-            cluster_sync_all();   // rank 0 may leave only after everyone has read it
-        } else {
-            abort = s_flags[0] != 0;
-        }
-    }
-
-    if (!abort) {
+    {
         const int m0 = tile_m * TC_BM;
         // ---------------- TMA producer, part 1: fill the ring (no waits) ----------------
         const uint32_t tx = TC_A_BYTES + (uint32_t)P.b_bytes;
@@ -377,7 +398,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             // only the copy instruction itself is left on the critical path
             const CUtensorMap* bmap = &P.tm_x[0];
             int bc0 = 0, bc1 = tile_n * P.n_valid, bc2 = 0;
-            if (lane < first) {
+            if (lane < first && !abort0) {
                 mbar_expect_tx(bar_full + 8 * lane, tx);
                 load_a(lane, lane);
                 const int kb = kb_begin + lane, tap = tap_of(kb);
@@ -394,7 +415,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             // in this order at most two grids of a chain are resident and the other SM slots stay free for
             // best-effort kernels.  One thread per CTA executing the instruction counts for the CTA.
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-            if (lane < first) {
+            if (lane < first && !abort0) {
                 const uint32_t bdst = base + lane * stage_bytes + TC_A_BYTES;
                 if (P.spatial) tma_load_3d(bdst, bmap, bar_full + 8 * lane, bc0, bc1, bc2);
                 else tma_load_2d(bdst, bmap, bar_full + 8 * lane, bc0, bc1);
@@ -431,28 +452,62 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             bool ok = true;
             int s = first == NS ? 0 : first;      // first < NS only when nkb < NS, and then this loop does not run
             uint32_t par = 0;                      // parity of the "empty" phase awaited: ((i / NS) - 1) & 1
-            for (int i = first; i < nkb && ok; i++) {
+            int issued = abort0 ? 0 : first;       // K blocks whose loads are out
+            bool stop = abort0;
+            for (int i = first; i < nkb && ok && !stop; i++) {
+                // loop-head poll of the preempt flag (every 4th K block): the load is issued before the wait for a
+                // free stage and looked at after it, so its latency hides behind the wait
+                int f = 0;
+                if (BE && (i & 3) == 0) f = *reinterpret_cast<const volatile int*>(P.preempt_flag);
                 ok = mbar_wait(bar_empty + 8 * s, par);
                 if (!ok) break;
+                if (BE && f != 0) { stop = true; break; }
                 mbar_expect_tx(bar_full + 8 * s, tx);
                 load_a(i, s);
                 load_b(i, s);
+                issued++;
                 if (++s == NS) { s = 0; par ^= 1u; }
+            }
+            if (BE && stop) {
+                s_flags[2] = (uint32_t)issued;     // first how far the loads got, then the request to stop
+                __threadfence_block();
+                s_flags[0] = 1;
             }
             if (!ok) s_flags[1] = 1;
         } else if (warp == 1 && lane == 0) {
             // ---------------- MMA issuer ----------------
             bool ok = true;
             const uint32_t idesc = umma_idesc_tf32(P.n_mma);
+#ifdef REEF_DEBUG_AIDS
             const bool tr = P.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+#endif
             int s = 0;
             uint32_t par = 0;
             for (int i = 0; i < nkb && ok; i++) {
                 const uint32_t st = base + s * stage_bytes;
-                ok = mbar_wait(bar_full + 8 * s, par);
+                if (BE) {
+                    const int w = mbar_wait_abortable(bar_full + 8 * s, par, &s_flags[0]);
+                    if (w == 2) {
+                        // The producer stopped.  Loads it had issued may still be in flight: they must have landed
+                        // before this CTA leaves or reuses its shared memory, so their barriers are awaited (bounded)
+                        // without multiplying.
+                        __threadfence_block();
+                        const int issued = (int)s_flags[2];
+                        for (; i < issued && ok; i++) {
+                            ok = mbar_wait(bar_full + 8 * s, par);
+                            if (++s == NS) { s = 0; par ^= 1u; }
+                        }
+                        break;
+                    }
+                    ok = w == 0;
+                } else {
+                    ok = mbar_wait(bar_full + 8 * s, par);
+                }
                 if (!ok) break;
+#ifdef REEF_DEBUG_AIDS
                 if (tr && i == 0) P.trace[4] = clock64();          // first K block landed
                 if (tr && i == nkb - 1) P.trace[5] = clock64();    // last K block landed
+#endif
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t da = umma_desc_sw128(st), db = umma_desc_sw128(st + TC_A_BYTES);
                 // one tcgen05.mma covers K = 8 tf32 = 32 bytes.  (Skipping the steps of a ragged last channel block
@@ -486,7 +541,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         if (tid == 0) tc_stamp(P, 6);   // accumulator complete
         // cluster barrier #1 (arrive here, wait after staging): every rank has finished its main loop, so its
         // stage ring is free to receive exchange data
-        if (S > 1) cluster_arrive_relaxed();
+        // (best-effort flavour: with release semantics, the peers read this CTA's abort word behind the barrier)
+        if (S > 1) {
+            if (BE) cluster_arrive();
+            else cluster_arrive_relaxed();
+        }
+        const bool my_abort = BE && s_flags[0] != 0;   // final: producer and MMA thread are past their loops
         if (!ok || s_flags[1]) {
             ok = false;
             if (tid == 0 && P.error_word) *reinterpret_cast<volatile int*>(P.error_word) = 1;
@@ -502,7 +562,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         const int row = quad * 32 + lane;              // TMEM lane == output channel within the tile
         const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
         float* stage = reinterpret_cast<float*>(smem);
-        if (ok) {
+        if (ok && !my_abort) {
             for (int j0 = half * 32; j0 < n_lim; j0 += 64) {
                 uint32_t r[32];
                 tmem_ld32_nowait(taddr + j0, r);
@@ -528,31 +588,43 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         // warp frees it there and not at the very end: nothing is then left to do between a CTA's last store and
         // its exit, which is what the next kernel of the stream waits for.
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        bool abort_all = my_abort;
         if (S > 1) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staged tile -> visible to the copy engine
             __syncthreads();      // the whole tile is staged
             if (warp == 1) tmem_free(tmem, (uint32_t)P.tmem_cols);
             cluster_wait();       // barrier #1: all peers are past their main loops (and their barriers are armed)
             if (tid == 0) tc_stamp(P, 3);
-            if (tid < S && tid != split) {   // one thread per peer: the copies are issued side by side
-                const int q = tid;
-                const int qb = min(q * cpc, n_lim), qe = min(qb + cpc, n_lim);
-                const uint32_t bytes = (uint32_t)((qe - qb) * TC_BM * 4);
-                if (bytes != 0) {
-                    const int slot = split < q ? split : split - 1;   // the owner keeps no slot for itself
-                    const uint32_t dst = mapa_shared(smem_u32(recv + (size_t)slot * P.cpc_max * TC_BM), (uint32_t)q);
-                    const uint32_t rbar = mapa_shared(bar_red, (uint32_t)q);
-                    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(dst), "r"(smem_u32(stage + (size_t)qb * TC_BM)), "r"(bytes), "r"(rbar)
-                                 : "memory");
+            if (BE) {
+                // every rank learns whether ANY rank of the cluster stopped for the preempt flag: one thread per rank
+                // reads that rank's abort word through distributed shared memory; all ranks compute the same OR
+                uint32_t f = 0;
+                if (tid < S)
+                    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(f) : "r"(mapa_shared(smem_u32((const void*)&s_flags[0]), (uint32_t)tid)) : "memory");
+                abort_all = __syncthreads_or((int)f) != 0;
+            }
+            if (!abort_all) {
+                if (tid < S && tid != split) {   // one thread per peer: the copies are issued side by side
+                    const int q = tid;
+                    const int qb = min(q * cpc, n_lim), qe = min(qb + cpc, n_lim);
+                    const uint32_t bytes = (uint32_t)((qe - qb) * TC_BM * 4);
+                    if (bytes != 0) {
+                        const int slot = split < q ? split : split - 1;   // the owner keeps no slot for itself
+                        const uint32_t dst = mapa_shared(smem_u32(recv + (size_t)slot * P.cpc_max * TC_BM), (uint32_t)q);
+                        const uint32_t rbar = mapa_shared(bar_red, (uint32_t)q);
+                        asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(dst), "r"(smem_u32(stage + (size_t)qb * TC_BM)), "r"(bytes), "r"(rbar)
+                                     : "memory");
+                    }
+                }
+                if (!mbar_wait(bar_red, 0)) {
+                    ok = false;
+                    if (tid == 0 && P.error_word) *reinterpret_cast<volatile int*>(P.error_word) = 1;
                 }
             }
-            if (!mbar_wait(bar_red, 0)) {
-                ok = false;
-                if (tid == 0 && P.error_word) *reinterpret_cast<volatile int*>(P.error_word) = 1;
-            }
             // cluster barrier #2 (arrive here, wait before leaving): once all ranks have received what they are
-            // owed, nobody reads a peer's shared memory any more and every CTA may exit
+            // owed (and, best-effort flavour, have read each other's abort words), nobody reads a peer's shared
+            // memory any more and every CTA may exit
             cluster_arrive();
         } else {
             __syncthreads();
@@ -562,7 +634,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         if (tid == 0) tc_stamp(P, 8);   // exchange complete
         // Four pixel rows per warp are in flight at a time (all partial and residual loads issued before the
         // first use): with one or two warps per scheduler the loop is latency-bound, not bandwidth-bound.
-        if (ok && cvalid) {
+        if (ok && cvalid && !abort_all) {
             constexpr int RB = 4;
             if (S == 1) {
                 for (int jbase = jb + warp; jbase < je; jbase += 8 * RB) {
@@ -597,7 +669,14 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         }
         if (S > 1) cluster_wait();      // barrier #2
         if (tid == 0) tc_stamp(P, 9);   // rows finished
-        if (P.task_slot != nullptr && ok) {
+        if (BE && abort_all && tid == 0 && P.stamps != nullptr) {
+            // measurement only: when this block saw the preempt flag and left (device clock)
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            atomicMin(&P.stamps[0], t);
+            atomicMax(&P.stamps[1], t);
+        }
+        if (P.task_slot != nullptr && ok && !abort_all) {
             __syncthreads();
             if (tid == 0) {
                 __threadfence();
@@ -606,11 +685,6 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         }
     }
 
-    if (abort) {   // a preempted best-effort launch did nothing but allocate
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (warp == 1) tmem_free(tmem, (uint32_t)P.tmem_cols);
-    }
     if (tid == 32) tc_stamp(P, 10);   // leaving
 }
 

@@ -29,6 +29,7 @@ struct TcParams {
     int* task_slot;
     int* error_word;         // device word set non-zero when a bounded wait expired
     long long* trace;        // optional: 16 SM-clock stamps of block (0,0) (phase trace), else nullptr
+    unsigned long long* stamps;   // optional: {first flag observation, last leave} in %globaltimer ns, else nullptr
     int co, ci, ptot;
     int ocs, ooff;
     int spatial;             // 0: flat [P][C] view, tile = n_valid consecutive pixels; 1: tile = rows x Wo

@@ -517,6 +517,21 @@ __device__ __forceinline__ void pdl_prologue() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// Device-side preemption stamps (optional, measurement only): when the host has armed the two words with
+// reef_preempt_stamps_arm, the first best-effort block that sees the preempt flag up records %globaltimer into word
+// 0 (minimum) and every block that leaves because of the flag records it into word 1 (maximum), so that
+// word1 - word0 is the time, on the device's own clock, from the flag becoming visible to the last best-effort
+// block leaving.
+__device__ unsigned long long* g_preempt_stamps = nullptr;
+__device__ __forceinline__ void preempt_stamp_leave() {
+    unsigned long long* w = g_preempt_stamps;
+    if (w == nullptr) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    atomicMin(&w[0], t);
+    atomicMax(&w[1], t);
+}
+
 template <int F>
 __global__ void __launch_bounds__(kThreads) k_plain(const __grid_constant__ KTask t) {
     pdl_prologue();
@@ -530,12 +545,21 @@ template <int F>
 __global__ void __launch_bounds__(kThreads) k_be(const __grid_constant__ KTask t, const int* __restrict__ flag,
                                                  int* __restrict__ task_slot) {
     pdl_prologue();
-    if (ld_flag(flag)) return;
+    if (ld_flag(flag)) {
+        preempt_stamp_leave();
+        return;
+    }
     const bool done = run_body<F>(t, blockIdx.x, reef_dyn_smem, flag);
-    __syncthreads();
-    if (done && threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
-        __threadfence();
-        atomicAdd(task_slot, 1);
+    // a body may stop at a loop head in some of its warps only (the GEMV polls per warp): the block counts as
+    // complete only when every thread ran to the end
+    const int stopped = __syncthreads_or(done ? 0 : 1);
+    if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
+        if (!stopped) {
+            __threadfence();
+            atomicAdd(task_slot, 1);
+        } else {
+            preempt_stamp_leave();
+        }
     }
 }
 
@@ -606,6 +630,61 @@ __global__ void k_delay(unsigned long long ns) {
     }
 }
 
+// ---- preemption stamps: host side ---------------------------------------------------------------------------
+static unsigned long long* g_stamps_dev[16] = {nullptr};
+
+unsigned long long* preempt_stamps_ptr() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+    return g_stamps_dev[dev];
+}
+
+static int stamps_reset(unsigned long long* d) {
+    const unsigned long long init[2] = {~0ull, 0ull};
+    if (cudaMemcpy(d, init, sizeof(init), cudaMemcpyHostToDevice) != cudaSuccess) {
+        set_error("preemption stamps: cannot reset the device words");
+        return REEF_FAIL;
+    }
+    return REEF_SUCC;
+}
+
+int preempt_stamps_arm(int on) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return REEF_FAIL;
+    unsigned long long* d = g_stamps_dev[dev];
+    if (on && d == nullptr) {
+        if (cudaMalloc(&d, 16) != cudaSuccess) {
+            set_error("preemption stamps: cannot allocate the device words");
+            return REEF_FAIL;
+        }
+        if (stamps_reset(d) != REEF_SUCC) return REEF_FAIL;
+        g_stamps_dev[dev] = d;
+    } else if (!on && d != nullptr) {
+        g_stamps_dev[dev] = nullptr;
+        unsigned long long* null = nullptr;
+        cudaMemcpyToSymbol(g_preempt_stamps, &null, sizeof(null));
+        cudaDeviceSynchronize();
+        cudaFree(d);
+        return REEF_SUCC;
+    }
+    unsigned long long* sym = on ? g_stamps_dev[dev] : nullptr;
+    if (cudaMemcpyToSymbol(g_preempt_stamps, &sym, sizeof(sym)) != cudaSuccess) {
+        set_error("preemption stamps: cannot set the device pointer");
+        return REEF_FAIL;
+    }
+    return REEF_SUCC;
+}
+
+int preempt_stamps_read(unsigned long long out[2]) {
+    unsigned long long* d = preempt_stamps_ptr();
+    if (d == nullptr) return REEF_NOT_FOUND;
+    if (cudaMemcpy(out, d, 16, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        set_error("preemption stamps: cannot read the device words");
+        return REEF_FAIL;
+    }
+    return stamps_reset(d);
+}
+
 int launch_delay(cudaStream_t st, unsigned long long ns) {
     k_delay<<<1, 1, 0, st>>>(ns);
     cudaError_t e = cudaGetLastError();
@@ -662,13 +741,17 @@ static void prepare_carveout() {
     g_carveout_set[dev] = true;
 }
 
-// Launch with the programmatic-stream-serialization attribute (REEF_PDL=0 turns it off): the kernel may be
-// scheduled while its predecessor in the stream still runs; all kernels here wait in their prologue.
+// Launch with the programmatic-stream-serialization attribute: the kernel may be scheduled while its predecessor
+// in the stream still runs; all kernels here wait in their prologue.  (Development builds, -DREEF_DEBUG_AIDS, can
+// switch it off with REEF_PDL=0.)
 static cudaError_t launch_pdl(const void* fn, dim3 grid, dim3 block, void** kargs, uint32_t smem, cudaStream_t st) {
     static int use_pdl = -1;
     if (use_pdl < 0) {
+        use_pdl = 1;
+#ifdef REEF_DEBUG_AIDS
         const char* v = getenv("REEF_PDL");
-        use_pdl = (v && v[0] == '0') ? 0 : 1;
+        if (v && v[0] == '0') use_pdl = 0;
+#endif
     }
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));

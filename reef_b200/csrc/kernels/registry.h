@@ -65,8 +65,13 @@ int tc_func_attrs(const TcPlan& pl, cudaFuncAttributes* fa, int* occ);
 int tc_error_word(int** out);
 int tc_error_word_host(volatile int** out);
 int tc_prepare_device();
+#ifdef REEF_DEBUG_AIDS
 int tc_trace_enable(int on);
 int tc_trace_read(long long* out16);
+#endif
+unsigned long long* preempt_stamps_ptr();   // device words {first seen, last leave} of the current device, or null
+int preempt_stamps_arm(int on);
+int preempt_stamps_read(unsigned long long out[2]);
 unsigned long long launch_count();          // kernels launched by this library, all threads
 unsigned long long thread_launch_count();   // ... by the calling thread (a stream capture counts its own launches)
 void add_launches(unsigned long long n);

@@ -207,9 +207,18 @@ __device__ __forceinline__ bool body_gap(const KTask& t, int vb, unsigned char* 
 }
 
 // ---- dense_add[_nn_relu] : GEMV at batch 1 (reference: resource/resnet152/resnet152.cu:2-33) ---
-// args: x[k], W[n][k], out[n], bias[n].  One warp per output row, 8 rows per vblock, float4 loads.
-// HBM-bound: every weight byte is read exactly once.
-constexpr int kDenseRowsPerBlock = 8;
+// args: x[k], W[n][k], out[n], bias[n].  HBM-bound: every weight byte is read exactly once (streaming loads).
+// A warp owns TWO output rows (x is fetched once for both) and keeps 8 independent 128-bit weight loads in flight
+// per lane: with VGG-16's 4096 rows only 1.7 blocks are resident per SM, so the bytes in flight per block, not the
+// number of blocks, are what covers the HBM latency.  16 rows per logical block.
+// Best-effort flavour: every warp polls the preempt flag at the head of every second pass of its main loop (a pass
+// is 16 KB of weights per warp) and leaves; the wrapper counts the block complete only if no warp left.
+constexpr int kDenseRowsPerBlock = 16;
+__device__ __forceinline__ float dense_dot4(float4 a, float4 b, float acc) {
+    acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc);
+    acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+    return acc;
+}
 __device__ __forceinline__ bool body_dense(const KTask& t, int vb, unsigned char*, const int* flag) {
     const DenseP& p = t.p.dense;
     const float* x = (const float*)t.a[0];
@@ -217,30 +226,57 @@ __device__ __forceinline__ bool body_dense(const KTask& t, int vb, unsigned char
     float* out = (float*)t.a[2];
     const float* bias = (const float*)t.a[3];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int row = vb * kDenseRowsPerBlock + warp;
-    if (row >= p.n) return true;
-    const float* wr = w + (size_t)row * p.k;
-    float acc = 0.f;
+    const int row0 = vb * kDenseRowsPerBlock + warp * 2;
+    if (row0 >= p.n) return true;
+    const bool two = row0 + 1 < p.n;
+    const float* wr0 = w + (size_t)row0 * p.k;
+    const float* wr1 = two ? wr0 + p.k : wr0;   // a last odd row is computed twice, stored once
+    float acc0 = 0.f, acc1 = 0.f;
     if ((p.k & 3) == 0) {
-        const float4* w4 = reinterpret_cast<const float4*>(wr);
+        const float4* a4 = reinterpret_cast<const float4*>(wr0);
+        const float4* b4 = reinterpret_cast<const float4*>(wr1);
         const float4* x4 = reinterpret_cast<const float4*>(x);
         const int k4 = p.k >> 2;
-        for (int i = lane; i < k4; i += 32) {
-            float4 a = __ldg(w4 + i);
-            float4 b = x4[i];
-            acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc);
-            acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+        int i = lane, pass = 0;
+        for (; i + 96 < k4; i += 128, pass++) {
+            if (flag != nullptr && (pass & 1) == 1 && ld_flag(flag)) return false;   // loop-head poll
+            float4 wa[4], wb[4], xv[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                wa[u] = __ldcs(a4 + i + 32 * u);
+                wb[u] = __ldcs(b4 + i + 32 * u);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) xv[u] = __ldg(x4 + i + 32 * u);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                acc0 = dense_dot4(wa[u], xv[u], acc0);
+                acc1 = dense_dot4(wb[u], xv[u], acc1);
+            }
+        }
+        for (; i < k4; i += 32) {
+            const float4 xv = __ldg(x4 + i);
+            acc0 = dense_dot4(__ldcs(a4 + i), xv, acc0);
+            acc1 = dense_dot4(__ldcs(b4 + i), xv, acc1);
         }
     } else {
-        for (int i = lane; i < p.k; i += 32) acc = fmaf(wr[i], x[i], acc);
+        for (int i = lane; i < p.k; i += 32) {
+            acc0 = fmaf(wr0[i], x[i], acc0);
+            acc1 = fmaf(wr1[i], x[i], acc1);
+        }
     }
-    acc = warp_sum(acc);
+    acc0 = warp_sum(acc0);
+    acc1 = warp_sum(acc1);
     if (lane == 0) {
-        float v = acc + bias[row];
+        float v = acc0 + bias[row0];
         if (p.relu) v = fmaxf(v, 0.f);
-        out[row] = v;
+        out[row0] = v;
+        if (two) {
+            v = acc1 + bias[row0 + 1];
+            if (p.relu) v = fmaxf(v, 0.f);
+            out[row0 + 1] = v;
+        }
     }
-    (void)flag;
     return true;
 }
 

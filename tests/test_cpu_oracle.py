@@ -10,7 +10,7 @@ import torch.nn.functional as F
 
 from conftest import rel_err, seeded_input
 from oracle import oracle
-from torch_ref import run_graph
+from oracle.torch_ref import run_graph
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -157,3 +157,17 @@ def test_oracle_more_cnn_graphs_vs_torch(gen, model, n):
     o.execute()
     st, names = run_graph(base + ".json", base + ".param", {"data": x})
     assert rel_err(o.get_output(), st[names.index("output")]) < 2e-5
+
+
+def test_oracle_bert_graph_vs_torch_executor(gen):
+    """The schedule interpreter built on PyTorch operators (oracle/torch_ref.py, the second CPU baseline of the bench)
+    agrees with the plain-C oracle on every buffer of a BERT schedule, as it does on the CNN schedules above."""
+    base = gen("bert_tiny")
+    ids = np.random.default_rng(4).integers(0, 1000, 48).astype(np.int64)
+    o = oracle.OracleExecutor(base + ".json", base + ".param")
+    o.set_input("input0", ids)
+    o.execute()
+    st, names = run_graph(base + ".json", base + ".param", {"input0": ids})
+    for i, n in enumerate(names):
+        if n in ("null", "output"):
+            assert rel_err(o.storage[i], st[i]) < 2e-5, f"storage {i}"

@@ -174,11 +174,10 @@ def test_closed_loop_clients_rt_with_be(gen):
     s.close()
 
 
-def test_padding_segments_keep_best_effort_results_exact(gen, monkeypatch):
+def test_padding_segments_keep_best_effort_results_exact(gen):
     """Four best-effort ResNet-152 clients advance only as padding under a back-to-back real-time client
     (padding segments, several pieces per stream, tasks completed inside the window): every client finishes
     requests, most of them entirely by padding, and every output is bit-identical to an unpadded run."""
-    monkeypatch.setenv("REEF_PAD_TARGET", "0.5")      # a generous slowdown budget: pad as much as fits
     base = gen("resnet152")
     x = seeded_input(3 * 224 * 224, seed=21)
     e = capi.HybridExecutor(0)
@@ -189,6 +188,7 @@ def test_padding_segments_keep_best_effort_results_exact(gen, monkeypatch):
     want = e.get_output().copy()
     e.close()
     s = S(S.REEF)
+    s.set_pad_slowdown_target(0.5)      # a generous slowdown budget: pad as much as fits
     s.run()
     rt = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
     s.bind_model_queue(s.create_queue(S.RealTimeQueue), rt)
@@ -208,3 +208,50 @@ def test_padding_segments_keep_best_effort_results_exact(gen, monkeypatch):
     assert st["padded_kernels"] > 1000 and st["be_tasks_padded_to_finish"] > 0
     s.shutdown()
     s.close()
+
+
+def test_failed_launch_and_device_error_end_in_a_failed_task(gen):
+    """A task whose kernel launch returns an error, or during which the device error word was set, ends in Finish
+    with the failed mark and wait_task returns Fail (the reference aborts the process, hip_impl.h:34-41).  Both
+    failures are injected on the host: the launch call is made to return an error before it reaches the device, and
+    the error word is stored from the host; no device-side wait is made to expire."""
+    base = gen("resnet18_64")
+    x = seeded_input(3 * 64 * 64, seed=2)
+    for qtype in (S.RealTimeQueue, S.BestEffortQueue):
+        s = S(S.REEF)
+        s.run()
+        mid = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
+        s.bind_model_queue(s.create_queue(qtype), mid)
+        s.set_input(mid, x)
+        t = s.new_task(mid)
+        s.wait_task(t)
+        good = s.get_output(mid).copy()
+        assert s.get_task(t).failed == 0
+        # 1. the launch call fails (once)
+        s.inject_launch_failures(mid, 1)
+        t = s.new_task(mid)
+        with pytest.raises(capi.ReefError) as ex:
+            s.wait_task(t)
+        assert ex.value.status == capi.FAIL
+        info = s.get_task(t)
+        assert info.state == S.Finish and info.failed == 1
+        # 2. the next task is clean again and right
+        t = s.new_task(mid)
+        s.wait_task(t)
+        assert s.get_task(t).failed == 0 and np.array_equal(s.get_output(mid), good)
+        # 3. the device error word is found set when the task's stream has drained
+        capi.device_error_set(1)
+        t = s.new_task(mid)
+        with pytest.raises(capi.ReefError) as ex:
+            s.wait_task(t)
+        assert ex.value.status == capi.FAIL and s.get_task(t).failed == 1
+        assert capi.device_error() == 0          # the scheduler cleared the word
+        t = s.new_task(mid)
+        s.wait_task(t)
+        assert s.get_task(t).failed == 0 and np.array_equal(s.get_output(mid), good)
+        # a closed-loop client stops at the first failed request and says so
+        s.inject_launch_failures(mid, 1)
+        res = s.run_clients([dict(mid=mid, max_requests=5, warmup=0, input=x)], allow_failed=True)
+        assert res[0]["failed"] and res[0]["completed"] == 0
+        s.shutdown()
+        s.close()
