@@ -133,6 +133,7 @@ typedef struct {
     uint64_t drain_count, drain_ns_sum, drain_ns_max;
     /* the same on the device's clock (set_device_stamps): first best-effort block that saw the flag -> last one that left */
     uint64_t dev_count, dev_ns_sum, dev_ns_max;
+    uint64_t drain_ns_p50, drain_ns_p99;
 } reef_sched_stats_t;
 REEF_HOST_API int reef_sched_stats(reef_scheduler_t s, reef_sched_stats_t* out);
 

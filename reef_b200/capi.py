@@ -41,7 +41,7 @@ class SchedStats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("preempt_count", "preempt_ns_sum", "preempt_ns_max", "rt_tasks", "be_tasks",
                                           "be_tasks_padded_to_finish", "padded_kernels", "padded_blocks",
                                           "drain_count", "drain_ns_sum", "drain_ns_max",
-                                          "dev_count", "dev_ns_sum", "dev_ns_max")]
+                                          "dev_count", "dev_ns_sum", "dev_ns_max", "drain_ns_p50", "drain_ns_p99")]
 
 
 class Client(C.Structure):

@@ -317,6 +317,8 @@ int reef_sched_stats(reef_scheduler_t s, reef_sched_stats_t* out) {
     out->dev_count = st.dev_count;
     out->dev_ns_sum = st.dev_ns_sum;
     out->dev_ns_max = st.dev_ns_max;
+    out->drain_ns_p50 = st.drain_ns_p50;
+    out->drain_ns_p99 = st.drain_ns_p99;
     return Succ;
 }
 

@@ -457,14 +457,19 @@ void REEFScheduler::preempt_reset() {
     auto t_flag = sclock::now();
     write_flag(1);
     uint32_t nq = be_queue_cnt.load();
-    std::vector<std::pair<std::shared_ptr<Task>, TaskQueue*>> hit;   // tasks that had kernels on their stream
+    struct Hit {
+        std::shared_ptr<Task> task;
+        TaskQueue* q;
+        reef_event_t last;   // recorded behind the last kernel handed to the stream
+    };
+    std::vector<Hit> hit;   // tasks that had kernels on their stream
     for (uint32_t i = 0; i < nq; i++) {
         auto& q = *be_queues[i];
         if (q.task_queue.empty()) continue;
         auto task = q.task_queue.front();
         if (task->get_state() == TaskState::Executing && task->all_issued_by_padding) continue;   // nothing to abort
         if (task->get_state() == TaskState::Executing) {
-            hit.push_back({task, &q});
+            hit.push_back(Hit{task, &q, q.inflight.empty() ? nullptr : q.inflight.back().ev});
             // An event that fires after the flag went up may belong to a kernel that left early, so the
             // window is not consulted here: kernel_offset stays at what the last poll saw complete.
             for (auto& f : q.inflight) q.free_events.push_back(f.ev);
@@ -475,35 +480,41 @@ void REEFScheduler::preempt_reset() {
             task->needs_recover = true;
         }
     }
-    if (!mapped_flag_host) reef_stream_sync(preempt_stream);
-    last_flag_ns = ns_since(t_flag);   // flag raised, queued launches dropped, tasks rolled back
-    if (wait_sync) {
-        // Bounded replacement of the reference's reset-until-idle loop (scheduler.cpp:336-345), then the exact
-        // restart point from the completion counters.  Every hit task's counters are copied on the task's OWN
-        // stream, behind its kernels in flight (which leave at their next flag poll), so "copy landed" also means
-        // "stream drained"; the copies of all tasks run side by side and there is one wait per stream.
-        for (auto& h : hit) h.first->model->executor.copy_be_kernel_offset(h.second->stream);
-        for (uint32_t i = 0; i < nq; i++) reef_preempt_wait(be_queues[i]->stream, 200000);
-        for (auto& h : hit) {
-            auto& task = h.first;
-            int k = task->model->executor.get_be_kernel_offset(task->kernel_offset);
-            if (k > task->kernel_offset) {
-                task->kernel_offset = k;
-                task->block_offset = 0;
-            }
-            task->launch_offset = task->kernel_offset;
+    if (!wait_sync) {
+        if (!mapped_flag_host) reef_stream_sync(preempt_stream);
+        last_flag_ns = ns_since(t_flag);   // flag raised, queued launches dropped, tasks rolled back
+        return;
+    }
+    last_flag_ns = ns_since(t_flag);
+    // Bounded replacement of the reference's reset-until-idle loop (scheduler.cpp:336-345): every hit stream is
+    // watched through the event behind its last kernel (those kernels leave at their next flag poll).  The clock
+    // stops when all of them are idle; the completion counters, which give the exact restart kernel, are copied on
+    // each task's own stream afterwards and read when the task is resumed, off the preemption path.
+    bool drained = true;
+    for (auto& h : hit) {
+        if (h.last == nullptr) continue;
+        int pending = 1;
+        while (reef_event_query(h.last, &pending) == REEF_SUCC && pending) {
+            if (ns_since(t_flag) > 200000000ull) { drained = false; break; }
         }
-        const uint64_t ns = ns_since(t_flag);
+    }
+    const uint64_t ns = ns_since(t_flag);
+    if (drained && !hit.empty()) {
         drain_count++;
         drain_ns_sum += ns;
         drain_ns_max = std::max(drain_ns_max, ns);
-        if (device_stamps) {
-            uint64_t first = 0, last = 0;
-            if (reef_preempt_stamps_read(&first, &last) == REEF_SUCC && first != 0 && last >= first) {
-                dev_count++;
-                dev_ns_sum += last - first;
-                dev_ns_max = std::max(dev_ns_max, last - first);
-            }
+        if (drain_samples.size() < (1u << 16)) drain_samples.push_back((uint32_t)std::min<uint64_t>(ns, 0xffffffffu));
+    }
+    for (auto& h : hit) {
+        h.task->model->executor.copy_be_kernel_offset(h.q->stream);
+        h.q->counters_pending = true;
+    }
+    if (device_stamps && !hit.empty()) {
+        uint64_t first = 0, last = 0;
+        if (reef_preempt_stamps_read(&first, &last) == REEF_SUCC && first != 0 && last >= first) {
+            dev_count++;
+            dev_ns_sum += last - first;
+            dev_ns_max = std::max(dev_ns_max, last - first);
         }
     }
 }
@@ -570,13 +581,21 @@ void REEFScheduler::preempt_be_tasks() {
 int64_t REEFScheduler::avg_preempt_latency() const {
     return preempt_count == 0 ? 0 : (int64_t)(preempt_latency_sum / preempt_count / 1000);
 }
+uint64_t REEFScheduler::drain_percentile(double q) const {
+    if (drain_samples.empty()) return 0;
+    std::vector<uint32_t> v(drain_samples);
+    size_t k = std::min(v.size() - 1, (size_t)(q * (double)v.size()));
+    std::nth_element(v.begin(), v.begin() + k, v.end());
+    return v[k];
+}
 int64_t REEFScheduler::avg_kernel_sel_latency() const {
     return kernel_sel_count == 0 ? 0 : (int64_t)(kernel_sel_latency_sum / kernel_sel_count);
 }
 REEFScheduler::Stats REEFScheduler::stats() const {
     return Stats{preempt_count, preempt_latency_sum, preempt_latency_max, n_rt_tasks, n_be_tasks,
                  n_be_padded_finish, n_padded_kernels, n_padded_blocks,
-                 drain_count, drain_ns_sum, drain_ns_max, dev_count, dev_ns_sum, dev_ns_max};
+                 drain_count, drain_ns_sum, drain_ns_max, dev_count, dev_ns_sum, dev_ns_max,
+                 drain_percentile(0.50), drain_percentile(0.99)};
 }
 
 bool REEFScheduler::any_be_waiting() {
@@ -1037,6 +1056,18 @@ void REEFScheduler::execute_be_task(std::shared_ptr<Task>& task, std::shared_ptr
             reset_preempt_flag_async();
             preempted = false;
             reef_stream_sync(preempt_stream);
+        }
+        if (tqueue->counters_pending) {
+            // a preemption with wait_sync left a copy of the completion counters on this stream: the exact restart
+            // kernel is the first one whose counter is short of its block count
+            tqueue->counters_pending = false;
+            reef_stream_sync(tqueue->stream);
+            int k = exe.get_be_kernel_offset(task->kernel_offset);
+            if (k > task->kernel_offset) {
+                task->kernel_offset = k;
+                task->block_offset = 0;
+            }
+            task->launch_offset = task->kernel_offset;
         }
         if (task->needs_recover) {
             // Leftovers of preempted launches and padded pieces may still be on the stream.  Nothing waits for

@@ -151,6 +151,7 @@ public:
         // idle and the counters read; device clock from the first block that saw the flag to the last that left
         uint64_t drain_count, drain_ns_sum, drain_ns_max;
         uint64_t dev_count, dev_ns_sum, dev_ns_max;
+        uint64_t drain_ns_p50, drain_ns_p99;
     };
     Stats stats() const;
     const std::string& error() const { return err_; }
@@ -194,6 +195,7 @@ private:
         std::deque<PadOut> pad_out;
         int pad_quantum_left = 0;
         bool pad_draining = false;
+        bool counters_pending = false;   // a copy of the head task's completion counters is on the stream (wait_sync)
     };
 
     Status create_task_queue(std::shared_ptr<TaskQueue>& ret, bool rt);
@@ -271,6 +273,8 @@ private:
     bool device_stamps = false;
     int cpu_first = -1, cpu_count = 0;
     uint64_t last_flag_ns = 0;
+    std::vector<uint32_t> drain_samples;
+    uint64_t drain_percentile(double q) const;
     void write_flag(uint32_t v);
     uint64_t kernel_sel_count, kernel_sel_latency_sum;
     uint64_t n_rt_tasks, n_be_tasks, n_be_padded_finish, n_padded_kernels, n_padded_blocks;

@@ -381,9 +381,12 @@ def test_tf32_schedule_against_the_unrounded_fp32_model(gen, model, inp):
     # the two parameter files hold different weights for the tensor-core layers (rounded / as drawn)
     from reef_b200.resources.graph import read_param_file
     pa, pb = read_param_file(base + ".param"), read_param_file(gen(model, variant="_fp32") + ".param")
-    big_a = max(pa.values(), key=lambda v: v.size)
-    cand = [v for v in pb.values() if v.size == big_a.size]
-    assert cand and not any(np.array_equal(big_a, v) for v in cand), "the default schedule's weights are not rounded copies"
+    rounded = 0
+    for k in pa:      # the two builds draw the same parameters in the same order: names line up
+        if k in pb and pa[k].size == pb[k].size and not np.array_equal(pa[k], pb[k]):
+            assert np.abs(pa[k] - pb[k]).max() <= 2.0 ** -10 * np.abs(pb[k]).max(), k    # a rounded copy, not another tensor
+            rounded += 1
+    assert rounded > 10, "the default schedule's tensor-core weights should be rounded copies of the fp32 model's"
     e = load_executor(base)
     e.set_input(inp, x)
     e.execute()
