@@ -426,6 +426,11 @@ Status HybridExecutor::launch_pad_segment(int seg, GPUStream_t stream) {
 }
 
 Status HybridExecutor::execute_graph(GPUStream_t stream) {
+    if (fail_launches > 0 && graph != nullptr && graph_stream == stream) {   // injected failure of a graph replay
+        fail_launches--;
+        err_ = "injected graph launch failure";
+        return Status::Fail;
+    }
     if (graph == nullptr || graph_stream != stream) {
         if (graph) reef_graph_destroy(graph);
         graph = nullptr;

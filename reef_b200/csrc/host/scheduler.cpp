@@ -455,7 +455,13 @@ void REEFScheduler::reset_preempt_flag_async() { write_flag(0); }
 // no CUDA form — running blocks leave at their next flag poll.
 void REEFScheduler::preempt_reset() {
     auto t_flag = sclock::now();
-    write_flag(1);
+    if (flag_early) {
+        // timeline_padding raised the flag before it launched the real-time graph: the clock runs from there
+        t_flag = t_flag_early;
+        flag_early = false;
+    } else {
+        write_flag(1);
+    }
     uint32_t nq = be_queue_cnt.load();
     struct Hit {
         std::shared_ptr<Task> task;
@@ -731,10 +737,19 @@ bool REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
                                 ? rt_exe.profile()->model_latency * unit : cum[n_rt] * unit;
     const double scale = cum[n_rt] > 0 ? model_ns / cum[n_rt] : 1.0;   // profile units -> ns of the graph replay
 
+    // The preempt flag goes up first (an asynchronous stream write: about two microseconds of host time), then the
+    // graph: the write travels to the device and the best-effort blocks leave while the host is still busy with the
+    // graph launch, instead of the write queueing up behind it.
+    if (!preempted && (mode == REEF || mode == Reset)) {
+        t_flag_early = sclock::now();
+        write_flag(1);
+        flag_early = true;
+    }
     auto t0 = sclock::now();
     if (rt_exe.execute_graph(rt_queue->stream) != Status::Succ) {
         err_ = "real-time graph launch failed: " + rt_exe.error();
         fprintf(stderr, "[reef] %s\n", err_.c_str());
+        if (flag_early) preempt_be_tasks();   // the flag is up: bring the bookkeeping in line with it
         return false;
     }
     pad_trace.calls++;

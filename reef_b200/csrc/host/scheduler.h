@@ -273,6 +273,8 @@ private:
     bool device_stamps = false;
     int cpu_first = -1, cpu_count = 0;
     uint64_t last_flag_ns = 0;
+    bool flag_early = false;   // the flag was raised ahead of preempt_reset (timeline_padding, before its graph launch)
+    std::chrono::steady_clock::time_point t_flag_early;
     std::vector<uint32_t> drain_samples;
     uint64_t drain_percentile(double q) const;
     void write_flag(uint32_t v);
