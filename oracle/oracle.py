@@ -3,9 +3,10 @@ kernel by kernel, calling the plain-C restatements in ``reef_oracle.c``.
 
 TEST INFRASTRUCTURE ONLY — imported by ``tests/``, ``__graft_entry__.smoke()`` and
 ``bench.py``'s CPU-baseline legs; the product package never imports it.
-PARITY UNPINNED for real networks (see the header of ``reef_oracle.c``); pinned
-only by the reference's mocked_kernel known-answer (reference:
-src/reef/test/test.cpp:102-116).
+Pinned per kernel family against the reference's own kernels run on the CPU
+(tests/golden/ref_kernels.npz, see the header of ``reef_oracle.c``) and by the
+mocked_kernel known answer (reference: src/reef/test/test.cpp:102-116); a
+whole-network golden vector of the reference stays unavailable.
 
 The interpretation of a kernel list mirrors what the reference executor does
 with it (reference: src/reef/executor/executor_base.cpp:35-80,196-223): one
@@ -163,7 +164,8 @@ def run_kernel(name: str, bufs: list, acc64: bool = False) -> None:
         L.reef_oracle_matmul_nt(_p(A), _p(B), _p(out), _p(bias), _p(res), i32(a["m"]), i32(a["n"]), i32(a["k"]),
                                 i32(int("_gelu" in tail)), i32(int(acc64)))
     elif op == "reef_attention":
-        mask = bufs[2] if len(bufs) > 2 and a.get("mask", 0) else None
+        # args: qkv, [mask], out (the mask, when the name carries mask1, sits between the two)
+        mask = bufs[1] if len(bufs) > 2 and a.get("mask", 0) else None
         out = bufs[-1]
         L.reef_oracle_attention(_p(bufs[0]), _p(mask), _p(out), i32(a["s"]), i32(a["heads"]), i32(a["d"]))
     else:

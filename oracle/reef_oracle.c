@@ -3,14 +3,22 @@
  * nothing in the product path links, loads or calls this file; it is the
  * checker the GPU kernels are compared against and the timed CPU baseline.
  *
- * PARITY UNPINNED for real networks: the reference's only golden vector for a
- * DNN (reference: src/reef/test/test.cpp:52-53) needs resnet18.param, which the
- * reference tree does not ship, and the reference's arithmetic is generated by
- * a customised Apache TVM fork (version unpinned, not vendored; call sites
- * reference: script/tvm_generate_model.py:34-62) that cannot be built here.
- * The one pinned known-answer is the mocked_kernel model (all outputs 18.0,
- * reference: src/reef/test/test.cpp:102-116), reproduced by
- * reef_oracle_mocked_add / reef_oracle_mocked_multiply below.
+ * HOW IT IS PINNED.  Per kernel family, by the reference's OWN kernels: the generated
+ * sources resource/resnet152/resnet152.cu, resource/bert/bert.cu and
+ * resource/inception/inception.cu are compiled unchanged for the CPU and run by a fiber
+ * emulator (oracle/refkernels, `make ref`); their outputs on seeded inputs are committed
+ * as tests/golden/ref_kernels.npz, and tests/test_cpu_ref_kernels.py holds every function
+ * below against them (convolution with every epilogue, pooling, bias add / ReLU, global
+ * average pool, GEMV, softmax, LayerNorm, GELU, X W^T, masked attention, embedding): 1e-5
+ * of the largest output, bit-exact where no sum is involved.  Plus the mocked_kernel
+ * known answer (all outputs 18.0, reference: src/reef/test/test.cpp:102-116).
+ * WHAT STAYS UNPINNED: a whole-network result.  The reference's only golden vector for a
+ * DNN (reference: src/reef/test/test.cpp:52-53) needs resnet18.param, which the reference
+ * tree does not ship, and the networks themselves are produced by a customised Apache TVM
+ * fork (version unpinned, not vendored; reference: script/tvm_generate_model.py:34-62)
+ * that cannot be built here.  The order of the kernels in a network is therefore this
+ * repository's own reading of the reference's schedules, cross-checked against an
+ * independent PyTorch interpretation (oracle/torch_ref.py).
  *
  * Each function restates, in plain fp32 C, the per-element math of one fused
  * kernel family of the reference's generated device code.  Activations are
