@@ -12,6 +12,7 @@
 #include <map>
 #include <string>
 
+#include "attention_tc.cuh"
 #include "bert.cuh"
 #include "conv_simt.cuh"
 #include "conv_tc_params.h"
@@ -30,9 +31,12 @@ static inline void count_launch() {
 
 struct TcCache {
     TcParams params;
+    AttParams att;
     void* ptrs[kMaxArgs];
     bool valid = false;
 };
+
+static inline bool is_tc_family(int f) { return f == F_CONV_TC || f == F_ATTENTION_TC; }
 
 static thread_local std::string g_err;
 void set_error(const std::string& s) { g_err = s; }
@@ -217,12 +221,25 @@ static int build_spec(const std::string& name, KernelSpec* s) {
         int sN, heads, d;
         if (!a.need("s", &sN) || !a.need("heads", &heads) || !a.need("d", &d) || d != kAttD) goto bad;
         t.p.raw[0] = sN; t.p.raw[1] = heads; t.p.raw[2] = d; t.p.raw[3] = (int)a.get("mask", 0);
-        t.family = F_ATTENTION;
-        t.nblocks = heads * ceil_div(sN, kAttRows);
-        s->dyn_smem = kAttSmem;
         s->nargs = t.p.raw[3] ? 3 : 2;
         s->flops = 4.0 * heads * (double)sN * sN * d;
         s->bytes = 4.0 * 4.0 * sN * heads * d;
+        if ((int)a.get("v", 0) == 1) {
+            // tensor-core variant: one CTA per head, both products on tcgen05 (attention_tc.cuh)
+            if (!att_supported(sN, heads, d)) {
+                set_error("shape not supported by the tensor-core attention (at most 128 tokens, d = 64): " + name);
+                return REEF_NOT_FOUND;
+            }
+            t.family = F_ATTENTION_TC;
+            t.nblocks = heads;
+            s->dyn_smem = (uint32_t)att_smem_bytes();
+            s->block[0] = ATT_THREADS;
+            s->tensor_core = 1;
+            return REEF_SUCC;
+        }
+        t.family = F_ATTENTION;
+        t.nblocks = heads * ceil_div(sN, kAttRows);
+        s->dyn_smem = kAttSmem;
         return REEF_SUCC;
     }
     if (op.rfind("reef_matmul_nt", 0) == 0) {
@@ -418,7 +435,8 @@ static void fill_arg_bytes(KernelSpec* s) {
             b[i++] = f4(h); b[i++] = f4(h);
             break;
         }
-        case F_ATTENTION: {
+        case F_ATTENTION:
+        case F_ATTENTION_TC: {
             const double sN = t.p.raw[0], H = (double)t.p.raw[1] * t.p.raw[2];
             int i = 0;
             b[i++] = f4(sN * 3 * H);
@@ -791,9 +809,16 @@ static int bind_tc(const KernelSpec& s, void** args) {
     if (!same) {
         void* ptrs[kMaxArgs] = {nullptr};
         for (int i = 0; i < s.nargs; i++) ptrs[i] = *reinterpret_cast<void**>(args[i]);
-        int rc = tc_prepare_device();
-        if (rc != REEF_SUCC) return rc;
-        rc = tc_build_params(s.task.p.conv, s.tc, ptrs, &c.params);
+        int rc;
+        if (s.task.family == F_ATTENTION_TC) {
+            rc = att_prepare_device();
+            if (rc != REEF_SUCC) return rc;
+            rc = att_build_params(s.task.p.raw[0], s.task.p.raw[1], s.task.p.raw[3], ptrs, &c.att);
+        } else {
+            rc = tc_prepare_device();
+            if (rc != REEF_SUCC) return rc;
+            rc = tc_build_params(s.task.p.conv, s.tc, ptrs, &c.params);
+        }
         if (rc != REEF_SUCC) return rc;
         for (int i = 0; i < s.nargs; i++) c.ptrs[i] = ptrs[i];
         c.valid = true;
@@ -803,7 +828,7 @@ static int bind_tc(const KernelSpec& s, void** args) {
 
 int prepare_kernel(const KernelSpec& s, void** args) {
     prepare_carveout();
-    if (s.task.family == F_CONV_TC) return bind_tc(s, args);
+    if (is_tc_family(s.task.family)) return bind_tc(s, args);
     return REEF_SUCC;
 }
 
@@ -813,6 +838,7 @@ static int launch_tc(const KernelSpec& s, cudaStream_t st, void** args, const in
     if (rc != REEF_SUCC) return rc;
     TcCache& c = *s.tc_cache;
     count_launch();
+    if (s.task.family == F_ATTENTION_TC) return att_launch(c.att, st, flag, slot, tile_begin, tile_count);
     return tc_launch(c.params, s.tc, st, flag, slot, tile_begin, tile_count);
 }
 
@@ -821,7 +847,7 @@ int launch_plain(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cud
         set_error("launch_params / shared_memory do not match the kernel plan of " + s.name);
         return REEF_OUT_OF_RANGE;
     }
-    if (s.task.family == F_CONV_TC) return launch_tc(s, st, args, nullptr, nullptr);
+    if (is_tc_family(s.task.family)) return launch_tc(s, st, args, nullptr, nullptr);
     KTask t;
     fill_args(s, args, &t);
     void* kargs[] = {&t};
@@ -837,7 +863,7 @@ int launch_be(const KernelSpec& s, const uint32_t dims[6], uint32_t smem, cudaSt
         set_error("launch_params / shared_memory do not match the kernel plan of " + s.name);
         return REEF_OUT_OF_RANGE;
     }
-    if (s.task.family == F_CONV_TC) return launch_tc(s, st, args, flag, slot);
+    if (is_tc_family(s.task.family)) return launch_tc(s, st, args, flag, slot);
     KTask t;
     fill_args(s, args, &t);
     void* kargs[] = {&t, (void*)&flag, (void*)&slot};
@@ -859,8 +885,8 @@ int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, 
                     int be_num, int sm_partition, int occupancy, int num_sms, int* be_slot, int* ctrl, int* be_ctrl,
                     cudaStream_t st, cudaStream_t be_st) {
     if (be == nullptr) be_num = 0;
-    const bool rt_tc = rt != nullptr && rt->task.family == F_CONV_TC;
-    const bool be_tc = be_num > 0 && be->task.family == F_CONV_TC;
+    const bool rt_tc = rt != nullptr && is_tc_family(rt->task.family);
+    const bool be_tc = be_num > 0 && is_tc_family(be->task.family);
     if (occupancy < 1) occupancy = 1;
     if (be_num > 0 && (be_off < 0 || be_off + be_num > be->task.nblocks)) {
         set_error("best-effort block range outside the kernel");
@@ -914,7 +940,7 @@ int launch_dispatch(const KernelSpec* rt, void** rt_args, const KernelSpec* be, 
     if (be_num > 0) {
         cudaStream_t bs = be_st != nullptr ? be_st : st;
         if (be_tc) {
-            const int sp = be->tc.splits;
+            const int sp = be->task.family == F_CONV_TC ? be->tc.splits : 1;
             if (be_off % sp != 0 || be_num % sp != 0) {
                 set_error("best-effort block range of a cluster kernel must be a multiple of its cluster size");
                 return REEF_OUT_OF_RANGE;
@@ -959,7 +985,7 @@ int launch_dispatch_static(const KernelSpec* rt, void** rt_args, const KernelSpe
     }
     if (rt == nullptr && be == nullptr) return REEF_FAIL;
     if (be == nullptr) be_num = 0;
-    if ((rt != nullptr && rt->task.family == F_CONV_TC) || (be_num > 0 && be->task.family == F_CONV_TC)) {
+    if ((rt != nullptr && is_tc_family(rt->task.family)) || (be_num > 0 && is_tc_family(be->task.family))) {
         set_error("reef_dispatch_static hosts logical-block kernels only (a tensor-core cluster kernel was given)");
         return REEF_FAIL;
     }
@@ -1013,6 +1039,9 @@ int kernel_attrs(const KernelSpec& s, reef_kernel_attrs_t* out) {
     int rc;
     if (s.task.family == F_CONV_TC) {
         rc = tc_func_attrs(s.tc, &fa, &occ);
+        if (rc != REEF_SUCC) return rc;
+    } else if (s.task.family == F_ATTENTION_TC) {
+        rc = att_func_attrs(&fa, &occ);
         if (rc != REEF_SUCC) return rc;
     } else {
         const void* fn = plain_fn(s.task.family);

@@ -23,6 +23,7 @@ struct TcPlan {
 };
 
 struct TcCache;   // tensor maps of one kernel call, rebuilt when its pointers change
+struct AttParams;
 
 struct KernelSpec {
     std::string name;
@@ -55,6 +56,14 @@ int kernel_attrs(const KernelSpec& s, reef_kernel_attrs_t* out);
 int prepare_kernel(const KernelSpec& s, void** args);
 int dispatch_occupancy(uint32_t smem, int* occ);
 int launch_delay(cudaStream_t st, unsigned long long ns);
+
+// attention_tc.cu
+int att_smem_bytes();
+int att_supported(int s, int heads, int d);
+int att_build_params(int s, int heads, int has_mask, void* const* args, AttParams* P);
+int att_prepare_device();
+int att_launch(const AttParams& P, cudaStream_t st, const int* flag, int* slot, int head_begin = 0, int head_count = -1);
+int att_func_attrs(cudaFuncAttributes* fa, int* occ);
 
 // conv_tc.cu
 int tc_plan(const ConvP& p, TcPlan* pl);

@@ -35,7 +35,8 @@ enum Family : int {
     F_NCHW_TO_NHWC4,
     F_COUNT,
     // families with their own __global__ kernel (not hosted by the 256-thread logical-block wrappers)
-    F_CONV_TC = 100
+    F_CONV_TC = 100,
+    F_ATTENTION_TC = 101
 };
 
 // epilogue / option bits

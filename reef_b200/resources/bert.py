@@ -36,7 +36,7 @@ class _B:
     def normal(self, *shape, std=0.02):
         return self.rng().normal(0.0, std, shape).astype(np.float32)
 
-    def matmul(self, x, m, n, k, *, gelu=False, residual=None, out=None):
+    def matmul(self, x, m, n, k, *, gelu=False, residual=None, out=None, round_out=False):
         from .. import capi
         op = "reef_matmul_nt_bias" + ("_gelu" if gelu else "") + ("_residual" if residual is not None else "")
         w = self.normal(n, k)
@@ -47,6 +47,8 @@ class _B:
                 attrs["v"] = 1
                 attrs.update(tuned_plan(kname(op, **attrs)))
                 w = round_tf32(w)
+                if round_out:
+                    attrs["rt"] = 1   # the consumer is a tensor-core kernel: store the nearest TF32 value, not fp32 it would truncate
             except capi.ReefError:
                 pass
         out = self.g.temp(m * n) if out is None else out
@@ -66,6 +68,7 @@ class _B:
 def build_bert(*, name: str = "bert_base", layers: int = 12, hidden: int = 768, heads: int = 12, ffn: int = 3072,
                vocab: int = 30522, seq: int = 128, seed: int = 5000, conv_impl: str = "auto") -> _B:
     assert hidden == heads * 64, "the attention kernel is written for head dimension 64"
+    from .. import capi
     b = _B(name, seed, conv_impl)
     g = b.g
     ids = g.input("input0", seq, "int64")
@@ -75,9 +78,18 @@ def build_bert(*, name: str = "bert_base", layers: int = 12, hidden: int = 768, 
     g.kernel(kname("reef_embedding", s=seq, h=hidden, vocab=vocab), [emb, word, ids, pos])
     x = b.layernorm(emb, seq, hidden)
     for li in range(layers):
-        qkv = b.matmul(x, seq, 3 * hidden, hidden)
+        att_attrs = dict(s=seq, heads=heads, d=hidden // heads)
+        att_tc = False
+        if conv_impl != "simt":
+            try:   # both attention products on the tensor cores where the registry has the shape (<= 128 tokens)
+                capi.kernel_plan(kname("reef_attention", **att_attrs, v=1))
+                att_attrs["v"] = 1
+                att_tc = True
+            except capi.ReefError:
+                pass
+        qkv = b.matmul(x, seq, 3 * hidden, hidden, round_out=att_tc)
         ctx = g.temp(seq * hidden)
-        g.kernel(kname("reef_attention", s=seq, heads=heads, d=hidden // heads), [qkv, ctx])
+        g.kernel(kname("reef_attention", **att_attrs), [qkv, ctx])
         att = b.matmul(ctx, seq, hidden, hidden, residual=x)
         x1 = b.layernorm(att, seq, hidden)
         h1 = b.matmul(x1, seq, ffn, hidden, gelu=True)

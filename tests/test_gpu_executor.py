@@ -449,3 +449,37 @@ def test_best_effort_kernel_leaves_mid_kernel(tmp_path, case):
     # a launch reaches the SMs within a few microseconds: an attempt preempted at `started_by` or later was stopped
     # while its blocks were running, and its counter short of the block count says they left before their end
     assert any(d >= started_by and 0 <= c < nblocks for d, c in seen), "the kernel never left in the middle"
+
+
+@pytest.mark.parametrize("s,heads,mask", [(128, 12, 0), (48, 2, 0), (100, 3, 1), (128, 4, 1), (1, 1, 0)])
+def test_attention_tensor_core_parity(tmp_path, s, heads, mask):
+    """reef_attention _v1: QK^T and PV on tcgen05 (one CTA per head, up to 128 tokens), softmax in registers, against the
+    oracle; ragged sequence lengths (rows and keys beyond the sequence), a key mask, every launch flavour bit-identical;
+    and against the CUDA-core variant of the same kernel."""
+    H = heads * 64
+    name = f"reef_attention__s{s}_heads{heads}_d64" + ("_mask1" if mask else "")
+    specs = [("in", s * 3 * H)] + ([("in", s)] if mask else []) + [("out", s * H)]
+    outs = {}
+    for variant in ("_v1", ""):
+        base, inputs = single_kernel_model(tmp_path / ("m" + variant), "one", name + variant, specs, seed=s + heads)
+        if mask:
+            m = (np.random.default_rng(5).random(s) > 0.3).astype(np.float32)
+            m[0] = 1.0
+            inputs["in1"] = m
+        e = load_executor(base)
+        o = oracle.OracleExecutor(base + ".json", base + ".param")
+        for k, v in inputs.items():
+            e.set_input(k, v)
+            o.set_input(k, v)
+        e.execute()
+        o.execute()
+        got = e.get_output()
+        err = rel_err(got, o.get_output())
+        print(name + variant, "rel err", err)
+        assert capi.device_error() == 0
+        assert not np.isnan(got).any() and err < (TF32_TOL if variant else FP32_TOL)
+        for f in ("execute_preemptable", "execute_dispatch", "execute_graph"):
+            getattr(e, f)()
+            assert np.array_equal(e.get_output(), got), f
+        outs[variant] = got
+    assert rel_err(outs["_v1"], outs[""]) < TF32_TOL
