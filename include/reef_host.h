@@ -67,6 +67,10 @@ REEF_HOST_API int reef_executor_time(reef_executor_t e, int mode, int warmup, in
  * order (CUDA events around `iters` replays after `warmup`); *launches = kernels in that graph.  NotFound when
  * the schedule has none.  No reference counterpart (measurement aid for the roofline of the dominant kernel). */
 REEF_HOST_API int reef_executor_time_tensor_core(reef_executor_t e, int warmup, int iters, float* avg_ms, int* launches);
+/* Microseconds per launch of kernel idx timed alone: a CUDA graph of `reps` back-to-back launches of that kernel,
+ * replayed `iters` times between two CUDA events after `warmup` replays (its operands stay warm in L2 where they fit:
+ * the figure is the kernel's own speed, not its place in the model).  No reference counterpart (roofline bookkeeping). */
+REEF_HOST_API int reef_executor_time_kernel(reef_executor_t e, int idx, int reps, int warmup, int iters, float* us_per_launch);
 /* Per-kernel device time in microseconds (CUDA events around each launch), n = num_kernels entries;
  * also returns algorithmic flops/bytes and the tensor-core marker per kernel when the arrays are given. */
 REEF_HOST_API int reef_executor_profile_kernels(reef_executor_t e, int iters, float* us, double* flops, double* bytes,

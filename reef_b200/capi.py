@@ -239,6 +239,13 @@ class HybridExecutor:
                "time_tensor_core", self._err())
         return float(ms.value), int(n.value)
 
+    def time_kernel(self, idx: int, reps: int = 20, warmup: int = 3, iters: int = 20) -> float:
+        """Microseconds per launch of kernel ``idx`` alone (a CUDA graph of ``reps`` launches, CUDA events)."""
+        us = C.c_float()
+        _check(self._lib.reef_executor_time_kernel(self._h, C.c_int(idx), C.c_int(reps), C.c_int(warmup), C.c_int(iters),
+                                                   C.byref(us)), "time_kernel", self._err())
+        return float(us.value)
+
     def profile_kernels(self, iters: int = 20):
         n = self.num_kernels()
         us = (C.c_float * n)()

@@ -203,6 +203,36 @@ int reef_executor_time_tensor_core(reef_executor_t e, int warmup, int iters, flo
     reef_graph_destroy(g);
     return rc == REEF_SUCC ? Succ : Fail;
 }
+int reef_executor_time_kernel(reef_executor_t e, int idx, int reps, int warmup, int iters, float* us_per_launch) {
+    // a CUDA graph of `reps` back-to-back launches of kernel idx alone (its inputs are whatever the buffers hold),
+    // replayed `iters` times between two events after `warmup` replays
+    auto& exe = e->exe;
+    if (idx < 0 || (size_t)idx >= exe.num_kernels() || reps < 1 || iters < 1) return OutOfRange;
+    reef_graph_t g = nullptr;
+    if (reef_graph_begin(exe.stream()) != REEF_SUCC) return Fail;
+    Status st = Succ;
+    for (int r = 0; r < reps && st == Succ; r++) st = (Status)exe.execute_kernel_async(idx);
+    int rc = reef_graph_end(exe.stream(), &g);
+    if (st != Succ || rc != REEF_SUCC) {
+        if (g) reef_graph_destroy(g);
+        return Fail;
+    }
+    reef_event_t a, b;
+    if (reef_event_create(&a) != REEF_SUCC || reef_event_create(&b) != REEF_SUCC) return Fail;
+    for (int i = 0; i < warmup && rc == REEF_SUCC; i++) rc = reef_graph_launch(g, exe.stream());
+    reef_stream_sync(exe.stream());
+    reef_event_record(a, exe.stream());
+    for (int i = 0; i < iters && rc == REEF_SUCC; i++) rc = reef_graph_launch(g, exe.stream());
+    reef_event_record(b, exe.stream());
+    reef_event_sync(b);
+    float ms = 0;
+    reef_event_elapsed_ms(a, b, &ms);
+    *us_per_launch = ms * 1000.f / (float)(iters * reps);
+    reef_event_destroy(a);
+    reef_event_destroy(b);
+    reef_graph_destroy(g);
+    return rc == REEF_SUCC ? Succ : Fail;
+}
 int reef_executor_profile_kernels(reef_executor_t e, int iters, float* us, double* flops, double* bytes,
                                   int* tensor_core, int* blocks, int* max_blocks_per_sm, size_t n) {
     if (n < e->exe.num_kernels()) return OutOfRange;

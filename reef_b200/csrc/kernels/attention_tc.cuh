@@ -107,18 +107,27 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) reef_attention_tc_kernel(const
             s_bias[tid] = dead ? -__int_as_float(0x7f800000) : 0.f;
         }
         // V -> Vt[d][key], K-major with the 128-byte swizzle: element (d, key) lives in key block key / 32, row d,
-        // 16-byte chunk ((key % 32) / 4) ^ (d % 8), word key % 4
-        float* vts = reinterpret_cast<float*>(smem + ATT_QK_BYTES);
-        for (int i = tid; i < 128 * (ATT_D / 4); i += ATT_THREADS) {
-            const int key = i >> 4, d0 = (i & 15) << 2;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (key < S) v = *reinterpret_cast<const float4*>(P.qkv + (size_t)key * 3 * H + 2 * H + head * ATT_D + d0);
-            const int kb = key >> 5, chunk = (key & 31) >> 2, w = key & 3;
-            const float e[4] = {v.x, v.y, v.z, v.w};
+        // 16-byte chunk ((key % 32) / 4) ^ (d % 8), word key % 4.  A lane stands for a key, a warp for two groups of
+        // four dimensions: all eight 128-bit loads of a thread are in flight at once, and for a fixed d the 32
+        // lanes store to 32 different banks.
+        {
+            float* vts = reinterpret_cast<float*>(smem + ATT_QK_BYTES);
+            float4 v[8];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int d = d0 + j;
-                vts[kb * (64 * 32) + d * 32 + ((chunk ^ (d & 7)) << 2) + w] = e[j];
+            for (int u = 0; u < 8; u++) {
+                const int key = (u >> 1) * 32 + lane, d0 = (warp * 2 + (u & 1)) * 4;
+                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (key < S) v[u] = *reinterpret_cast<const float4*>(P.qkv + (size_t)key * 3 * H + 2 * H + head * ATT_D + d0);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int kb = u >> 1, d0 = (warp * 2 + (u & 1)) * 4;
+                const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int d = d0 + j;
+                    vts[kb * (64 * 32) + d * 32 + (((lane >> 2) ^ (d & 7)) << 2) + (lane & 3)] = e[j];
+                }
             }
         }
         // ---- scores = Q K^T ----

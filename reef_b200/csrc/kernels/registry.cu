@@ -180,7 +180,8 @@ static int build_spec(const std::string& name, KernelSpec* s) {
         if (!a.need("k", &p.k) || !a.need("n", &p.n)) goto bad;
         p.relu = op == "fused_nn_dense_add_nn_relu";
         t.family = F_DENSE;
-        t.nblocks = ceil_div(p.n, kDenseRowsPerBlock);
+        t.nblocks = dense_num_blocks(p.n);
+        s->dyn_smem = kDenseSmem;
         s->nargs = 4;
         s->flops = 2.0 * p.k * p.n;
         s->bytes = 4.0 * ((double)p.k * p.n + p.k + 2.0 * p.n);
@@ -755,6 +756,12 @@ static void prepare_carveout() {
         cudaFuncSetAttribute(be_fn(f), cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     }
     cudaFuncSetAttribute((const void*)k_dispatch, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    // the GEMV's copy ring takes more than the 48 KB a kernel gets without asking (also when the dispatcher hosts it)
+    cudaFuncSetAttribute(plain_fn(F_DENSE), cudaFuncAttributeMaxDynamicSharedMemorySize, kDenseSmem);
+    cudaFuncSetAttribute(be_fn(F_DENSE), cudaFuncAttributeMaxDynamicSharedMemorySize, kDenseSmem);
+    cudaFuncSetAttribute((const void*)k_dispatch, cudaFuncAttributeMaxDynamicSharedMemorySize, kDenseSmem);
+    int* w = nullptr;
+    tc_error_word(&w);   // the device error word exists before any launch can be part of a stream capture
     cudaGetLastError();
     g_carveout_set[dev] = true;
 }
@@ -794,6 +801,8 @@ static int check_cuda(cudaError_t e, const char* what) {
 static void fill_args(const KernelSpec& s, void** args, KTask* t) {
     *t = s.task;
     for (int i = 0; i < s.nargs; i++) t->a[i] = *reinterpret_cast<void**>(args[i]);
+    t->err = nullptr;
+    if (s.task.family == F_DENSE) tc_error_word(&t->err);   // created by prepare_kernel, looked up here
 }
 
 static bool dims_match(const KernelSpec& s, const uint32_t dims[6], uint32_t smem) {

@@ -207,76 +207,227 @@ __device__ __forceinline__ bool body_gap(const KTask& t, int vb, unsigned char* 
 }
 
 // ---- dense_add[_nn_relu] : GEMV at batch 1 (reference: resource/resnet152/resnet152.cu:2-33) ---
-// args: x[k], W[n][k], out[n], bias[n].  HBM-bound: every weight byte is read exactly once (streaming loads).
-// A warp owns TWO output rows (x is fetched once for both) and keeps 8 independent 128-bit weight loads in flight
-// per lane: with VGG-16's 4096 rows only 1.7 blocks are resident per SM, so the bytes in flight per block, not the
-// number of blocks, are what covers the HBM latency.  16 rows per logical block.
-// Best-effort flavour: every warp polls the preempt flag at the head of every second pass of its main loop (a pass
-// is 16 KB of weights per warp) and leaves; the wrapper counts the block complete only if no warp left.
-constexpr int kDenseRowsPerBlock = 16;
-__device__ __forceinline__ float dense_dot4(float4 a, float4 b, float acc) {
-    acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc);
-    acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
-    return acc;
+// args: x[k], W[n][k], out[n], bias[n].  HBM-bound: every weight byte is read exactly once, and what decides the
+// speed is how the reads look to the DRAM: thousands of short interleaved row streams (a warp or a block hopping
+// between many weight rows) reach 0.55-0.6 of the HBM rate whether they are issued as plain loads or by the copy
+// engine; a few hundred long sequential streams reach it.  So:
+//  * the rows are dealt out in equal shares to 296 logical blocks (two per SM on B200): block b owns the contiguous
+//    rows [b*n/B, (b+1)*n/B), at most 16, and walks them four at a time from end to end, i.e. each block reads four
+//    sequential streams in 8 KB pieces;
+//  * the pieces are fetched by the copy engine (cp.async.bulk, no tensor map: a row is contiguous) into a ring of
+//    three 32 KB shared-memory stages, completion on mbarriers, so that ~96 KB per block are in flight without
+//    tying up registers;
+//  * thread t owns eight K positions of every stage: two 128-bit loads of x, two 128-bit shared-memory reads per
+//    row, 32 FMAs.  The partial sums of the 8 warps meet in shared memory in a fixed order.
+// Best-effort flavour: thread 0 polls the preempt flag before it refills a stage (once per 32 KB of weights); it
+// then stops issuing copies and publishes how far it got; every thread waits out what is in flight (its barriers
+// must have completed before the block may leave) and the block exits uncounted.  Waits are bounded.
+constexpr int kDenseBlocks = 296;
+constexpr int kDenseMaxRows = 16;
+// Measured on VGG-16's 411 MB layer (rows together, bytes per piece, stages -> fraction of the measured HBM copy rate):
+// 4 x 4 KB x 6: 0.68 | 2 x 8 KB x 6: 0.92 | 4 x 8 KB x 3: 0.91 | 2 x 4 KB x 12: 0.56 | 1 x 16 KB x 6: 0.86.
+// The piece size decides; 4 rows x 8 KB x 3 stages is also the fastest on the small layers.
+#ifndef REEF_DENSE_RG
+#define REEF_DENSE_RG 4
+#define REEF_DENSE_KC 2048
+#define REEF_DENSE_NS 3
+#endif
+constexpr int kDenseRG = REEF_DENSE_RG;         // rows walked together
+constexpr int kDenseKC = REEF_DENSE_KC;         // K positions per stage and row (8 KB pieces)
+constexpr int kDenseStages = REEF_DENSE_NS;
+constexpr int kDenseVec = kDenseKC / 1024;      // 128-bit slices of a stage row per thread
+constexpr int kDenseStageFloats = kDenseRG * kDenseKC;
+// ring + partial sums [4 groups][8 warps][4 rows] + alignment slack, barriers, control words
+constexpr int kDenseSmem = kDenseStages * kDenseStageFloats * 4 + (kDenseMaxRows / kDenseRG) * 8 * kDenseRG * 4 + 512;
+__host__ __device__ inline int dense_num_blocks(int n) {
+    int b = n < kDenseBlocks ? n : kDenseBlocks;
+    while ((n + b - 1) / b > kDenseMaxRows) b++;     // never more than kDenseMaxRows rows in a block
+    return b;
 }
-__device__ __forceinline__ bool body_dense(const KTask& t, int vb, unsigned char*, const int* flag) {
+__device__ __forceinline__ bool dense_mbar_wait(uint32_t bar, uint32_t parity) {
+    unsigned long long t0 = 0;
+    for (int i = 0; i < (1 << 26); i++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((i & 255) == 255) {   // give up after one second of wall time
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > 1000000000ull) return false;
+        }
+    }
+    return false;
+}
+__device__ __forceinline__ bool body_dense(const KTask& t, int vb, unsigned char* smem_raw, const int* flag) {
     const DenseP& p = t.p.dense;
     const float* x = (const float*)t.a[0];
     const float* w = (const float*)t.a[1];
     float* out = (float*)t.a[2];
     const float* bias = (const float*)t.a[3];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int row0 = vb * kDenseRowsPerBlock + warp * 2;
-    if (row0 >= p.n) return true;
-    const bool two = row0 + 1 < p.n;
-    const float* wr0 = w + (size_t)row0 * p.k;
-    const float* wr1 = two ? wr0 + p.k : wr0;   // a last odd row is computed twice, stored once
-    float acc0 = 0.f, acc1 = 0.f;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int B = t.nblocks;
+    const int r0 = (int)(((long long)vb * p.n) / B), r1 = (int)(((long long)(vb + 1) * p.n) / B);
+    const int nr = r1 - r0;
+    const int ngroups = (nr + kDenseRG - 1) / kDenseRG;
+    // dynamic shared memory: ring | partial sums | barriers (8-byte aligned) | control words
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t ring_off = ((sbase + 127u) & ~127u) - sbase;
+    float* ring = reinterpret_cast<float*>(smem_raw + ring_off);
+    constexpr int kPartFloats = (kDenseMaxRows / kDenseRG) * 8 * kDenseRG;
+    float* part = ring + kDenseStages * kDenseStageFloats;                 // [group][warp][row in group]
+    const uint32_t bars = sbase + ring_off + (kDenseStages * kDenseStageFloats + kPartFloats) * 4;
+    volatile int* ctl = reinterpret_cast<volatile int*>(smem_raw + ring_off + (kDenseStages * kDenseStageFloats + kPartFloats) * 4 + 16 * kDenseStages);
+    // ctl[0] = stop requested, ctl[1] = stages issued when the producer stopped, ctl[2] = a wait expired
+    int stopped = 0;
     if ((p.k & 3) == 0) {
-        const float4* a4 = reinterpret_cast<const float4*>(wr0);
-        const float4* b4 = reinterpret_cast<const float4*>(wr1);
-        const float4* x4 = reinterpret_cast<const float4*>(x);
-        const int k4 = p.k >> 2;
-        int i = lane, pass = 0;
-        for (; i + 96 < k4; i += 128, pass++) {
-            if (flag != nullptr && (pass & 1) == 1 && ld_flag(flag)) return false;   // loop-head poll
-            float4 wa[4], wb[4], xv[4];
+        const int spg = (p.k + kDenseKC - 1) / kDenseKC;     // stages per row group
+        const int nst = ngroups * spg;                        // stages to stream
+        const uint32_t bar_full = bars, bar_empty = bars + 8 * kDenseStages;
+        if (tid == 0) {
+            for (int s = 0; s < kDenseStages; s++) {
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_full + 8 * s), "r"(1));
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_empty + 8 * s), "r"(8));   // one arrive per warp
+            }
+            ctl[0] = 0; ctl[1] = 0; ctl[2] = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncthreads();
+        // one stage = the next 4 KB of each row of a group: lanes 0..3 of warp 0 copy a row's piece each, lane 0
+        // arms the barrier with the byte count
+        auto issue = [&](int st) {
+            const int s = st % kDenseStages;
+            const int g = st / spg, k0 = (st - g * spg) * kDenseKC;
+            const int kc = min(kDenseKC, p.k - k0);
+            const int rows = min(kDenseRG, nr - g * kDenseRG);
+            if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_full + 8 * s), "r"((uint32_t)(rows * kc * 4)) : "memory");
+            __syncwarp();
+            if (lane < rows) {
+                const uint32_t dst = sbase + ring_off + (uint32_t)((s * kDenseStageFloats + lane * kDenseKC) * 4);
+                const float* src = w + (size_t)(r0 + g * kDenseRG + lane) * p.k + k0;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(dst), "l"(src), "r"((uint32_t)(kc * 4)), "r"(bar_full + 8 * s)
+                             : "memory");
+            }
+        };
+        const int first = nst < kDenseStages ? nst : kDenseStages;
+        if (warp == 0)
+            for (int st = 0; st < first; st++) issue(st);
+        int issued = first;        // meaningful in warp 0 only
+        bool ok = true;
+        float acc[kDenseRG];
+        int st = 0;
+        for (int g = 0; g < ngroups && ok && !stopped; g++) {
+            const int rows = min(kDenseRG, nr - g * kDenseRG);
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                wa[u] = __ldcs(a4 + i + 32 * u);
-                wb[u] = __ldcs(b4 + i + 32 * u);
+            for (int r = 0; r < kDenseRG; r++) acc[r] = 0.f;
+            for (int kq = 0; kq < spg; kq++, st++) {
+                const int s = st % kDenseStages;
+                const uint32_t par = (uint32_t)((st / kDenseStages) & 1);
+                const int k0 = kq * kDenseKC;
+                const int kc = min(kDenseKC, p.k - k0);
+                float4 xv[kDenseVec];
+#pragma unroll
+                for (int j = 0; j < kDenseVec; j++) {       // requested before the wait
+                    xv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if ((tid + j * kThreads) * 4 < kc) xv[j] = __ldg(reinterpret_cast<const float4*>(x + k0) + tid + j * kThreads);
+                }
+                if (flag != nullptr && ctl[0] && st >= ctl[1]) {     // the producer stopped and nothing more is in flight
+                    stopped = 1;
+                    break;
+                }
+                if (!dense_mbar_wait(bar_full + 8 * s, par)) {
+                    ok = false;
+                    break;
+                }
+                if (!(flag != nullptr && ctl[0])) {
+                    const float4* sw = reinterpret_cast<const float4*>(ring + (size_t)s * kDenseStageFloats) + tid;
+#pragma unroll
+                    for (int j = 0; j < kDenseVec; j++) {
+                        if ((tid + j * kThreads) * 4 < kc) {
+#pragma unroll
+                            for (int r = 0; r < kDenseRG; r++) {
+                                if (r < rows) {
+                                    const float4 wv = sw[r * (kDenseKC / 4) + j * kThreads];
+                                    acc[r] = fmaf(wv.x, xv[j].x, acc[r]); acc[r] = fmaf(wv.y, xv[j].y, acc[r]);
+                                    acc[r] = fmaf(wv.z, xv[j].z, acc[r]); acc[r] = fmaf(wv.w, xv[j].w, acc[r]);
+                                }
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_empty + 8 * s) : "memory");
+                // refill this stage with the piece kDenseStages ahead, once every warp has released it
+                if (warp == 0 && st + kDenseStages < nst && !(flag != nullptr && ctl[0])) {
+                    int go = 1;
+                    if (lane == 0) {
+                        if (flag != nullptr && ld_flag(flag)) {              // loop-head poll of the preempt flag
+                            ctl[1] = issued;                                 // first how far the copies got, then the request
+                            __threadfence_block();
+                            ctl[0] = 1;
+                            go = 0;
+                        } else if (!dense_mbar_wait(bar_empty + 8 * s, par)) {
+                            ctl[2] = 1;
+                            go = 0;
+                        }
+                    }
+                    go = __shfl_sync(0xffffffffu, go, 0);
+                    if (go) {
+                        issue(st + kDenseStages);
+                        issued = st + kDenseStages + 1;
+                    }
+                }
             }
 #pragma unroll
-            for (int u = 0; u < 4; u++) xv[u] = __ldg(x4 + i + 32 * u);
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                acc0 = dense_dot4(wa[u], xv[u], acc0);
-                acc1 = dense_dot4(wb[u], xv[u], acc1);
+            for (int r = 0; r < kDenseRG; r++) {
+                const float v = warp_sum(acc[r]);
+                if (lane == 0) part[(g * 8 + warp) * kDenseRG + r] = v;
             }
         }
-        for (; i < k4; i += 32) {
-            const float4 xv = __ldg(x4 + i);
-            acc0 = dense_dot4(__ldcs(a4 + i), xv, acc0);
-            acc1 = dense_dot4(__ldcs(b4 + i), xv, acc1);
+        if (!ok || ctl[2]) {   // a wait expired: nothing is stored, the block is counted incomplete, the error word is raised
+            stopped = 1;
+            if (t.err != nullptr && tid == 0) *reinterpret_cast<volatile int*>(t.err) = 1;
         }
+        if (flag != nullptr && ctl[0]) stopped = 1;
     } else {
-        for (int i = lane; i < p.k; i += 32) {
-            acc0 = fmaf(wr0[i], x[i], acc0);
-            acc1 = fmaf(wr1[i], x[i], acc1);
+        // K not a multiple of 4 (no 16-byte alignment for the copy engine): plain loads
+        for (int g = 0; g < ngroups; g++) {
+            float acc[kDenseRG];
+#pragma unroll
+            for (int r = 0; r < kDenseRG; r++) acc[r] = 0.f;
+            const int rows = min(kDenseRG, nr - g * kDenseRG);
+            for (int i = tid; i < p.k; i += kThreads) {
+                const float xv = x[i];
+#pragma unroll
+                for (int r = 0; r < kDenseRG; r++)
+                    if (r < rows) acc[r] = fmaf(w[(size_t)(r0 + g * kDenseRG + r) * p.k + i], xv, acc[r]);
+            }
+#pragma unroll
+            for (int r = 0; r < kDenseRG; r++) {
+                const float v = warp_sum(acc[r]);
+                if (lane == 0) part[(g * 8 + warp) * kDenseRG + r] = v;
+            }
         }
     }
-    acc0 = warp_sum(acc0);
-    acc1 = warp_sum(acc1);
-    if (lane == 0) {
-        float v = acc0 + bias[row0];
+    if (__syncthreads_or(stopped)) return false;     // every thread of the block takes the same exit
+    if (tid < nr) {
+        const int g = tid / kDenseRG, j = tid - g * kDenseRG;
+        float v = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; q++) v += part[(g * 8 + q) * kDenseRG + j];   // fixed order: deterministic
+        v += bias[r0 + tid];
         if (p.relu) v = fmaxf(v, 0.f);
-        out[row0] = v;
-        if (two) {
-            v = acc1 + bias[row0 + 1];
-            if (p.relu) v = fmaxf(v, 0.f);
-            out[row0 + 1] = v;
-        }
+        out[r0 + tid] = v;
     }
+    __syncthreads();   // shared memory may be reused by the next logical block of a persistent caller
     return true;
 }
 

@@ -82,6 +82,7 @@ struct KTask {
         int raw[32];
     } p;
     void* a[kMaxArgs];       // device pointers, positional like the json "args"
+    int* err;                // device error word (set when a bounded wait expired), may be null
 };
 
 __device__ __forceinline__ int ld_flag(const int* flag) {

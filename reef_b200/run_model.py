@@ -38,7 +38,10 @@ def main():
         except capi.ReefError:
             continue
         rng = np.random.default_rng(2001)
-        e.set_input(name, rng.normal(0, 1, n // 4).astype(np.float32))
+        if name == "input0":      # token ids
+            e.set_input(name, rng.integers(0, 30522, n // 8).astype(np.int64))
+        else:
+            e.set_input(name, rng.normal(0, 1, n // 4).astype(np.float32))
     run = {"raw": e.execute, "graph": e.execute_graph, "be": e.execute_preemptable, "dispatch": e.execute_dispatch}[a.mode]
     t0 = time.perf_counter()
     for _ in range(a.iters):
