@@ -136,6 +136,7 @@ typedef struct {
     int tensor_core;       /* 1 when the kernel's contraction runs on tcgen05               */
     int cluster;           /* thread blocks per cluster (1 = no cluster); block ranges handed to
                               reef_dispatch for this kernel must be multiples of it           */
+    int chainable;         /* 1: a tensor-core convolution / matmul that reef_chain_create accepts */
 } reef_kernel_attrs_t;
 REEF_API reef_status reef_kernel_attrs(reef_kernel_t k, reef_kernel_attrs_t* out);
 
@@ -201,6 +202,21 @@ REEF_API reef_status reef_dispatch_static(reef_kernel_t rt, void** rt_args,
                                           int be_block_offset, int be_block_num,
                                           int sm_partition, int occupancy,
                                           reef_dptr_t be_task_slot, int lane, reef_stream_t s);
+
+/* A run of consecutive tensor-core layers as ONE persistent kernel (no reference counterpart: the reference launches
+ * one kernel per layer, executor_base.cpp:196-223; its persistent proxies host one layer each, trans_executor.cpp:132-173).
+ * reef_chain_create binds `n` kernels (all with attrs.chainable) to their argument lists (args[i] as in reef_launch)
+ * and builds the layer table and the completion counters in device memory — call it at load time, never during a
+ * stream capture.  reef_chain_launch clears the counters (stream-ordered) and launches a resident grid of `clusters`
+ * 8-CTA clusters (0 = default 16; never more than can be resident at once) that walks the layers in order; results are
+ * bit-identical to launching the kernels one by one.  One chain object serves one stream at a time (its counters are
+ * shared by its launches).  Every device-side wait is bounded; an expired wait raises the device error word. */
+typedef struct reef_chain_s* reef_chain_t;
+REEF_API reef_status reef_chain_create(reef_kernel_t* kernels, void*** args, int n, int clusters, reef_chain_t* chain);
+REEF_API reef_status reef_chain_launch(reef_chain_t chain, reef_stream_t s);
+REEF_API reef_status reef_chain_destroy(reef_chain_t chain);
+/* layers in the chain, clusters of its grid, and the most clusters the device can hold at once */
+REEF_API reef_status reef_chain_info(reef_chain_t chain, int* layers, int* clusters, int* max_clusters);
 
 /* GPUClearHostQueue / GPUResetCU (reference: hip_impl.h:21-22) have no CUDA equivalent: queued
  * launches are dropped by the host scheduler before they reach the stream and running blocks leave

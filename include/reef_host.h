@@ -53,6 +53,14 @@ REEF_HOST_API int reef_executor_execute_kernel(reef_executor_t e, int idx);
 REEF_HOST_API int reef_executor_execute_preemptable(reef_executor_t e);     /* best-effort flavour           */
 REEF_HOST_API int reef_executor_execute_graph(reef_executor_t e);           /* CUDA-graph replay, then sync  */
 REEF_HOST_API int reef_executor_execute_dispatch(reef_executor_t e);        /* every kernel through the dispatcher, unpadded */
+/* Persistent chains (HybridExecutor::build_chains): every run of >= 2 consecutive tensor-core convolution / matmul
+ * kernels becomes one persistent kernel of `clusters` 8-CTA clusters (0 = default); *num_chains (may be NULL) = runs
+ * found.  execute_graph then replays the schedule with the chains; execute_chained launches it the same way without a
+ * graph, then syncs.  Bit-identical to the per-kernel launches. */
+REEF_HOST_API int reef_executor_build_chains(reef_executor_t e, int clusters, size_t* num_chains);
+REEF_HOST_API int reef_executor_execute_chained(reef_executor_t e);
+/* chain idx covers kernels [*begin, *end) of the schedule and runs on *clusters clusters of the *max_clusters the GPU holds at once */
+REEF_HOST_API int reef_executor_chain_info(reef_executor_t e, size_t idx, int* begin, int* end, int* clusters, int* max_clusters);
 /* Best-effort run with the preempt flag raised `delay_us` after the first launch (host timer), then
  * resumed from the first kernel whose completion counter is short until the model is done.
  * *restarts = number of resume rounds, *first_incomplete = restart kernel of the first round,
@@ -124,6 +132,9 @@ REEF_HOST_API int reef_sched_set_pad_slowdown_target(reef_scheduler_t s, double 
  * clients on the rest of [first_cpu, first_cpu + n_cpus); n_cpus < 3 pins nothing.  Call before reef_sched_run. */
 REEF_HOST_API int reef_sched_set_cpu_slice(reef_scheduler_t s, int first_cpu, int n_cpus);
 REEF_HOST_API int reef_sched_set_rt_graph(reef_scheduler_t s, int value);
+/* Real-time models loaded AFTER this call run their tensor-core layers as persistent chains of `clusters` clusters
+ * (0 = default size, -1 = off). */
+REEF_HOST_API int reef_sched_set_rt_chains(reef_scheduler_t s, int clusters);
 REEF_HOST_API int reef_sched_run(reef_scheduler_t s);
 REEF_HOST_API int reef_sched_shutdown(reef_scheduler_t s);
 REEF_HOST_API int64_t reef_sched_avg_preempt_latency(reef_scheduler_t s);

@@ -29,7 +29,7 @@ class KernelAttrs(C.Structure):
     _fields_ = [("num_blocks", C.c_int), ("threads", C.c_int), ("regs_per_thread", C.c_int),
                 ("static_smem", C.c_int), ("dyn_smem", C.c_int), ("local_mem", C.c_int),
                 ("max_blocks_per_sm", C.c_int), ("flops", C.c_double), ("bytes", C.c_double),
-                ("tensor_core", C.c_int), ("cluster", C.c_int)]
+                ("tensor_core", C.c_int), ("cluster", C.c_int), ("chainable", C.c_int)]
 
 
 class TaskInfo(C.Structure):
@@ -209,6 +209,22 @@ class HybridExecutor:
     def execute_dispatch(self):
         _check(self._lib.reef_executor_execute_dispatch(self._h), "execute_dispatch", self._err())
 
+    def build_chains(self, clusters: int = 0) -> int:
+        """Runs of consecutive tensor-core layers become persistent kernels; returns the number of runs."""
+        n = C.c_size_t()
+        _check(self._lib.reef_executor_build_chains(self._h, C.c_int(clusters), C.byref(n)), "build_chains", self._err())
+        return int(n.value)
+
+    def chain_info(self, idx: int = 0):
+        """(first kernel, end kernel, clusters of the grid, most clusters the GPU holds at once) of chain ``idx``."""
+        b, e, c, m = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+        _check(self._lib.reef_executor_chain_info(self._h, C.c_size_t(idx), C.byref(b), C.byref(e), C.byref(c), C.byref(m)),
+               "chain_info", self._err())
+        return b.value, e.value, c.value, m.value
+
+    def execute_chained(self):
+        _check(self._lib.reef_executor_execute_chained(self._h), "execute_chained", self._err())
+
     def execute_preempt_resume(self, delay_us: int, with_count: bool = False):
         """Best-effort run, flag raised ``delay_us`` after the first launch, resumed until done.  Returns (restarts,
         first incomplete kernel) and, with ``with_count``, that kernel's completion counter when it was found short."""
@@ -371,6 +387,9 @@ class REEFScheduler:
 
     def set_be_stream_cap(self, v: int):
         self._lib.reef_sched_set_be_stream_cap(self._h, C.c_int(v))
+
+    def set_rt_chains(self, clusters: int):
+        self._lib.reef_sched_set_rt_chains(self._h, C.c_int(clusters))
 
     def set_rt_graph(self, v: bool):
         self._lib.reef_sched_set_rt_graph(self._h, C.c_int(int(v)))

@@ -355,6 +355,47 @@ reef_status reef_dispatch_static(reef_kernel_t rt, void** rt_args, reef_kernel_t
                                   sm_partition, occupancy, sms, (int*)be_slot, lane, (cudaStream_t)s);
 }
 
+struct reef_chain_s {
+    TcChain* chain;
+};
+reef_status reef_chain_create(reef_kernel_t* kernels, void*** args, int n, int clusters, reef_chain_t* chain) {
+    if (!kernels || !args || n < 1 || !chain) return REEF_FAIL;
+    std::vector<const KernelSpec*> specs;
+    for (int i = 0; i < n; i++) {
+        if (!kernels[i]) return REEF_FAIL;
+        specs.push_back(&kernels[i]->spec);
+    }
+    TcChain* c = nullptr;
+    int rc = make_chain(specs.data(), args, n, clusters, &c);
+    if (rc != REEF_SUCC) return rc;
+    *chain = new (std::nothrow) reef_chain_s{c};
+    if (!*chain) {
+        chain_destroy(c);
+        return REEF_FAIL;
+    }
+    return REEF_SUCC;
+}
+reef_status reef_chain_launch(reef_chain_t chain, reef_stream_t s) {
+    if (!chain) return REEF_FAIL;
+    int rc = chain_launch(chain->chain, (cudaStream_t)s);
+    if (rc == REEF_SUCC) add_launches(1);
+    return rc;
+}
+reef_status reef_chain_destroy(reef_chain_t chain) {
+    if (chain) {
+        chain_destroy(chain->chain);
+        delete chain;
+    }
+    return REEF_SUCC;
+}
+reef_status reef_chain_info(reef_chain_t chain, int* layers, int* clusters, int* max_clusters) {
+    if (!chain) return REEF_FAIL;
+    if (layers) *layers = chain_num_layers(chain->chain);
+    if (clusters) *clusters = chain_clusters(chain->chain);
+    if (max_clusters) *max_clusters = chain_max_clusters(chain->chain);
+    return REEF_SUCC;
+}
+
 reef_status reef_preempt_wait(reef_stream_t s, uint64_t timeout_us) {
     auto t0 = std::chrono::steady_clock::now();
     for (;;) {

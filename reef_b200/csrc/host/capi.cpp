@@ -128,6 +128,16 @@ int reef_executor_execute_graph(reef_executor_t e) {
     return reef_stream_sync(e->exe.stream());
 }
 int reef_executor_execute_dispatch(reef_executor_t e) { return e->exe.execute_dispatch(); }
+int reef_executor_build_chains(reef_executor_t e, int clusters, size_t* num_chains) {
+    reef_gpu_init(e->device);
+    Status st = e->exe.build_chains(clusters);
+    if (num_chains) *num_chains = e->exe.num_chains();
+    return st;
+}
+int reef_executor_execute_chained(reef_executor_t e) { return e->exe.execute_chained(); }
+int reef_executor_chain_info(reef_executor_t e, size_t idx, int* begin, int* end, int* clusters, int* max_clusters) {
+    return e->exe.chain_info(idx, begin, end, clusters, max_clusters);
+}
 int reef_executor_execute_preempt_resume(reef_executor_t e, int delay_us, int* restarts, int* first_incomplete,
                                          int* first_count) {
     return e->exe.execute_preempt_resume(delay_us, restarts, first_incomplete, first_count);
@@ -327,6 +337,7 @@ int reef_sched_set_device_stamps(reef_scheduler_t s, int on) { return s->sched->
 int reef_sched_set_pad_slowdown_target(reef_scheduler_t s, double v) { s->sched->set_pad_slowdown_target(v); return Succ; }
 int reef_sched_set_cpu_slice(reef_scheduler_t s, int first_cpu, int n_cpus) { s->sched->set_cpu_slice(first_cpu, n_cpus); return Succ; }
 int reef_sched_set_rt_graph(reef_scheduler_t s, int v) { s->sched->set_rt_graph(v != 0); return Succ; }
+int reef_sched_set_rt_chains(reef_scheduler_t s, int clusters) { s->sched->set_rt_chains(clusters); return Succ; }
 int reef_sched_run(reef_scheduler_t s) { return s->sched->run(); }
 int reef_sched_shutdown(reef_scheduler_t s) { return s->sched->shutdown(); }
 int64_t reef_sched_avg_preempt_latency(reef_scheduler_t s) { return s->sched->avg_preempt_latency(); }

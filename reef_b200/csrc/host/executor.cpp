@@ -261,6 +261,7 @@ Status ExecutorBase::launch_kernel(int i, GPUStream_t stream) {
 HybridExecutor::HybridExecutor() {}
 
 HybridExecutor::~HybridExecutor() {
+    for (auto& c : chains) reef_chain_destroy(c.handle);
     if (graph) reef_graph_destroy(graph);
     for (auto g : pad_segments) reef_graph_destroy(g);
     if (own_flag && preempt_flag) reef_free(preempt_flag);
@@ -425,6 +426,69 @@ Status HybridExecutor::launch_pad_segment(int seg, GPUStream_t stream) {
     return Status::Succ;
 }
 
+Status HybridExecutor::build_chains(int clusters) {
+    if (!chains.empty()) return Status::Succ;
+    const int n = (int)num_kernels();
+    for (int i = 0; i < n;) {
+        if (!trans_args[i].resource.chainable) {
+            i++;
+            continue;
+        }
+        int j = i;
+        while (j < n && trans_args[j].resource.chainable) j++;
+        if (j - i >= 2) {
+            std::vector<reef_kernel_t> ks(kernels.begin() + i, kernels.begin() + j);
+            std::vector<void**> as;
+            for (int k = i; k < j; k++) as.push_back(raw_args[k].data());
+            reef_chain_t h = nullptr;
+            int rc = reef_chain_create(ks.data(), as.data(), j - i, clusters, &h);
+            if (rc != REEF_SUCC) {
+                err_ = reef_last_error();
+                for (auto& c : chains) reef_chain_destroy(c.handle);
+                chains.clear();
+                RETURN_STATUS((Status)rc);
+            }
+            chains.push_back(Chain{i, j, h});
+        }
+        i = j;
+    }
+    // a graph captured earlier holds the per-kernel launches: it is rebuilt on next use
+    if (graph) {
+        reef_graph_destroy(graph);
+        graph = nullptr;
+        graph_stream = nullptr;
+    }
+    return Status::Succ;
+}
+
+// the schedule in order: a chain launch for every run that has one, a plain launch for every other kernel
+Status HybridExecutor::launch_schedule(GPUStream_t stream, bool use_chains) {
+    size_t ci = 0;
+    for (size_t i = 0; i < num_kernels();) {
+        if (use_chains && ci < chains.size() && chains[ci].begin == (int)i) {
+            int rc = reef_chain_launch(chains[ci].handle, stream);
+            if (rc != REEF_SUCC) {
+                err_ = reef_last_error();
+                return (Status)rc;
+            }
+            i = (size_t)chains[ci].end;
+            ci++;
+            continue;
+        }
+        Status st = ExecutorBase::launch_kernel((int)i, stream);
+        if (st != Status::Succ) return st;
+        i++;
+    }
+    return Status::Succ;
+}
+
+Status HybridExecutor::execute_chained(GPUStream_t stream) {
+    if (stream == nullptr) stream = s;
+    RETURN_STATUS(launch_schedule(stream, true));
+    GPU_RETURN_STATUS(reef_stream_sync(stream));
+    return Status::Succ;
+}
+
 Status HybridExecutor::execute_graph(GPUStream_t stream) {
     if (fail_launches > 0 && graph != nullptr && graph_stream == stream) {   // injected failure of a graph replay
         fail_launches--;
@@ -435,8 +499,7 @@ Status HybridExecutor::execute_graph(GPUStream_t stream) {
         if (graph) reef_graph_destroy(graph);
         graph = nullptr;
         GPU_RETURN_STATUS(reef_graph_begin(stream));
-        Status st = Status::Succ;
-        for (size_t i = 0; i < num_kernels() && st == Status::Succ; i++) st = ExecutorBase::launch_kernel((int)i, stream);
+        Status st = launch_schedule(stream, true);
         int rc = reef_graph_end(stream, &graph);
         if (st != Status::Succ || rc != REEF_SUCC) {
             // a launch failed while capturing: what was captured is a partial graph and must never be replayed

@@ -130,6 +130,22 @@ public:
     bool has_pad_segments() const { return !pad_segments.empty(); }
     Status launch_pad_segment(int seg, GPUStream_t stream);
     bool has_tensor_core_kernels() const { return has_tc; }
+    // Persistent chains: every run of two or more consecutive tensor-core convolution / matmul kernels of the
+    // schedule becomes ONE persistent kernel (reef_chain_create) with `clusters` 8-CTA clusters (0 = the library's
+    // default).  Built here, once; execute_graph and execute_chained then launch a run through its chain.  Results
+    // are bit-identical to the per-kernel launches.  Call before the first execute_graph on a stream.
+    Status build_chains(int clusters = 0);
+    size_t num_chains() const { return chains.size(); }
+    Status chain_info(size_t idx, int* begin, int* end, int* clusters, int* max_clusters) const {
+        if (idx >= chains.size()) return Status::OutOfRange;
+        int layers = 0;
+        if (begin) *begin = chains[idx].begin;
+        if (end) *end = chains[idx].end;
+        GPU_RETURN_STATUS(reef_chain_info(chains[idx].handle, &layers, clusters, max_clusters));
+        return Status::Succ;
+    }
+    // the whole schedule with chains where they exist and plain launches elsewhere, then sync
+    Status execute_chained(GPUStream_t stream = nullptr);
     // CUDA graph of the whole kernel list on `stream` (captured lazily on first use)
     Status execute_graph(GPUStream_t stream);
     // every kernel through the dispatcher without a best-effort partner, then sync
@@ -164,6 +180,12 @@ protected:
     reef_graph_t graph = nullptr;
     std::vector<reef_graph_t> pad_segments;
     GPUStream_t graph_stream = nullptr;
+    struct Chain {
+        int begin, end;          // kernels [begin, end) of the schedule
+        reef_chain_t handle;
+    };
+    std::vector<Chain> chains;
+    Status launch_schedule(GPUStream_t stream, bool use_chains);
 };
 
 }  // namespace executor

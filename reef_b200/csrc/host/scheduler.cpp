@@ -201,6 +201,13 @@ Status REEFScheduler::bind_model_queue(const QueueID& qid, const ModelID& mid) {
     if (model_pool_size.load() <= mid) return Status::OutOfRange;
     if (be_queue_cnt.load() <= qid && qid != rt_queue_id) return Status::OutOfRange;
     model_pool[mid]->qid = qid;
+    if (qid == rt_queue_id && rt_chain_clusters >= 0) {
+        reef_gpu_init(device);
+        if (model_pool[mid]->executor.build_chains(rt_chain_clusters) != Status::Succ) {
+            err_ = "persistent chains: " + model_pool[mid]->executor.error();
+            return Status::Fail;
+        }
+    }
     if (mode == ScheduleMode::REEF && qid != rt_queue_id) {
         // best-effort model under dynamic kernel padding: capture its padding segments now, not inside a
         // real-time window
@@ -740,7 +747,12 @@ bool REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
     // The preempt flag goes up first (an asynchronous stream write: about two microseconds of host time), then the
     // graph: the write travels to the device and the best-effort blocks leave while the host is still busy with the
     // graph launch, instead of the write queueing up behind it.
-    if (!preempted && (mode == REEF || mode == Reset)) {
+    // With wait_sync the whole switch — flag, queued launches dropped, best-effort streams drained — completes
+    // before the real-time task is launched, as in the reference (scheduler.cpp:262-303: preempt_be_tasks, then the
+    // task), and its duration is what the drain statistics hold.
+    if (wait_sync) {
+        preempt_be_tasks();
+    } else if (!preempted && (mode == REEF || mode == Reset)) {
         t_flag_early = sclock::now();
         write_flag(1);
         flag_early = true;

@@ -114,6 +114,9 @@ public:
     void set_be_stream_cap(int value) { be_stream_device_queue_cap = value < 1 ? 1 : value; }
     // real-time tasks that find no best-effort work replay a CUDA graph of the model (default on)
     void set_rt_graph(bool value) { rt_graph = value; }
+    // models bound to the real-time queue run their tensor-core layers as persistent chains (executor.h) of this
+    // many clusters; 0 = the library's default size, -1 = off (one launch per layer)
+    void set_rt_chains(int clusters) { rt_chain_clusters = clusters; }
     // Timeline padding (tensor-core models).  Unit = one SM slot: an SM holds two tensor-core CTAs.
     //  window      real-time kernels ahead of the estimated position whose footprint bounds the padding
     //  depth       padded pieces queued per best-effort stream (hides the launch-to-completion latency)
@@ -238,6 +241,7 @@ private:
     std::condition_variable task_cnt_cv;
     bool wait_sync;
     bool rt_graph;
+    int rt_chain_clusters = -1;
 
     std::unique_ptr<std::thread> scheduler;
     executor::GPUStream_t preempt_stream = nullptr;

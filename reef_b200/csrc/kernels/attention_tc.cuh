@@ -255,10 +255,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) reef_attention_tc_kernel(const
             atomicMin(&P.stamps[0], t);
             atomicMax(&P.stamps[1], t);
         }
-        if (P.task_slot != nullptr && ok && !stop) {
-            __threadfence();
-            atomicAdd(P.task_slot, 1);
-        }
+        if (P.task_slot != nullptr && ok && !stop) red_release_gpu_add(P.task_slot, 1);
     }
 }
 

@@ -37,7 +37,7 @@ enum : int { TC_EP_RES = 1, TC_EP_BIAS = 2, TC_EP_GB = 4, TC_EP_RELU = 8, TC_EP_
 // exact-erf GELU (reference: resource/bert/bert.cu:167-173).  Not inlined on purpose: inlined, the compiler turned
 // the uniform `if (gelu)` of the epilogue into straight-line code and every layer paid for erff on each element
 // (0.5 us per launch on the row-finishing loop).
-__device__ __noinline__ float tc_gelu(float v) { return v * (0.5f * erff(v * 0.70710678118654752440f) + 0.5f); }
+static __device__ __noinline__ float tc_gelu(float v) { return v * (0.5f * erff(v * 0.70710678118654752440f) + 0.5f); }
 
 __device__ __forceinline__ float tc_epilogue(float v, float r, float sc, float sh, float lo, bool rnd, bool gelu = false) {
     if (gelu) {
@@ -104,7 +104,9 @@ __device__ __forceinline__ void tc_stamp(const TcParams&, int) {}
 // rank order (a fixed order: bit-reproducible), applies the epilogue and stores 512-byte rows.  RB rows per warp
 // are in flight at a time, RB * SMAX 128-bit loads per lane (16: the kernel is built for two CTAs per SM, so
 // a thread has 128 registers).
-template <int RB, int SMAX>
+// CG: the residual was written earlier in the SAME launch (persistent chain kernel): it is read at L2 (ld.global.cg),
+// never through the non-coherent path, and there is no early prefetch.
+template <int RB, int SMAX, bool CG = false>
 __device__ __forceinline__ void tc_finish_split(const TcParams& P, const float* stage, const float* recv, int S, int split,
                                                 int jb, int je, int warp, int cbase, int co, int pix0, float4 sc, float4 sh,
                                                 float lo, bool rnd, bool gelu, bool has_res, float4 b2, const float4* rpre) {
@@ -123,7 +125,11 @@ __device__ __forceinline__ void tc_finish_split(const TcParams& P, const float* 
 #pragma unroll
                 for (int q = 0; q < SMAX; q++)
                     if (q < S) part[u][q] = *reinterpret_cast<const float4*>(src[q] + (size_t)jr * TC_BM);
-                if (has_res) rv[u] = (u < 2 && jbase == warp) ? rpre[u & 1] : __ldg(reinterpret_cast<const float4*>(P.res + (size_t)(pix0 + jb + jr) * P.co + co));
+                if (has_res) {
+                    const float4* rp = reinterpret_cast<const float4*>(P.res + (size_t)(pix0 + jb + jr) * P.co + co);
+                    if (CG) rv[u] = __ldcg(rp);
+                    else rv[u] = (u < 2 && jbase == warp) ? rpre[u & 1] : __ldg(rp);
+                }
             }
         }
 #pragma unroll
@@ -163,9 +169,13 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
     const uint32_t bar_red = bar_acc + 8;
     volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + P.region_bytes + 16 * TC_MAX_STAGES + 16);
     volatile uint32_t* s_flags = s_tmem + 1;    // [0] abort (preempt flag seen by this CTA), [1] wait expired,
-                                                //  [2] K blocks whose loads were issued when the producer stopped
+                                                //  [2] K blocks whose loads were issued when the producer stopped,
+                                                //  [3] some rank of the cluster stopped (written by that rank)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // best-effort flavour: the poll at block entry is issued first, so that its latency hides behind the set-up
+    int flag0 = 0;
+    if (BE && tid == 0) flag0 = *reinterpret_cast<const volatile int*>(P.preempt_flag);
     if (tid == 0) tc_stamp(P, 0);
     // grid = (K splits = cluster, tiles of this launch); a launch may cover a sub-range of the tiles
     const int split = blockIdx.x;
@@ -183,9 +193,10 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         }
         mbar_init(bar_acc, 1);
         mbar_init(bar_red, 1);
-        s_flags[0] = BE ? (uint32_t)(*reinterpret_cast<const volatile int*>(P.preempt_flag) != 0) : 0u;   // poll at block entry
+        s_flags[0] = (uint32_t)(flag0 != 0);
         s_flags[1] = 0;
         s_flags[2] = 0;
+        s_flags[3] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&P.tm_w) : "memory");
@@ -391,11 +402,17 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         // cluster barrier #1 (arrive here, wait after staging): every rank has finished its main loop, so its
         // stage ring is free to receive exchange data
         // (best-effort flavour: with release semantics, the peers read this CTA's abort word behind the barrier)
-        if (S > 1) {
-            if (BE) cluster_arrive();
-            else cluster_arrive_relaxed();
-        }
         const bool my_abort = BE && s_flags[0] != 0;   // final: producer and MMA thread are past their loops
+        if (S > 1) {
+            if (BE) {
+                // a rank that stopped tells every rank of its cluster (itself included) with a remote store ahead of
+                // the barrier: behind the barrier each rank reads only its own shared memory
+                if (my_abort && tid < S) st_dsmem_u32(mapa_shared(smem_u32((const void*)&s_flags[3]), (uint32_t)tid), 1u);
+                cluster_arrive();
+            } else {
+                cluster_arrive_relaxed();
+            }
+        }
         if (!ok || s_flags[1]) {
             ok = false;
             if (tid == 0 && P.error_word) *reinterpret_cast<volatile int*>(P.error_word) = 1;
@@ -444,14 +461,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             if (warp == 1) tmem_free(tmem, (uint32_t)P.tmem_cols);
             cluster_wait();       // barrier #1: all peers are past their main loops (and their barriers are armed)
             if (tid == 0) tc_stamp(P, 3);
-            if (BE) {
-                // every rank learns whether ANY rank of the cluster stopped for the preempt flag: one thread per rank
-                // reads that rank's abort word through distributed shared memory; all ranks compute the same OR
-                uint32_t f = 0;
-                if (tid < S)
-                    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(f) : "r"(mapa_shared(smem_u32((const void*)&s_flags[0]), (uint32_t)tid)) : "memory");
-                abort_all = __syncthreads_or((int)f) != 0;
-            }
+            // (the word was written, if at all, before its writer arrived at the barrier: all ranks read the same)
+            if (BE) abort_all = s_flags[3] != 0;
             if (!abort_all) {
                 if (tid < S && tid != split) {   // one thread per peer: the copies are issued side by side
                     const int q = tid;
@@ -527,10 +538,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         }
         if (P.task_slot != nullptr && ok && !abort_all) {
             __syncthreads();
-            if (tid == 0) {
-                __threadfence();
-                atomicAdd(P.task_slot, 1);
-            }
+            if (tid == 0) red_release_gpu_add(P.task_slot, 1);
         }
     }
 

@@ -574,8 +574,7 @@ __global__ void __launch_bounds__(kThreads) k_be(const __grid_constant__ KTask t
     const int stopped = __syncthreads_or(done ? 0 : 1);
     if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
         if (!stopped) {
-            __threadfence();
-            atomicAdd(task_slot, 1);
+            red_release_gpu_add(task_slot, 1);
         } else {
             preempt_stamp_leave();
         }
@@ -617,10 +616,7 @@ __global__ void __launch_bounds__(kThreads) k_dispatch(const __grid_constant__ K
                 if (v >= be_num) break;
                 run_any(be, be_off + v, reef_dyn_smem, nullptr);
                 __syncthreads();
-                if (threadIdx.x == 0) {
-                    __threadfence();
-                    atomicAdd(be_slot, 1);
-                }
+                if (threadIdx.x == 0) red_release_gpu_add(be_slot, 1);
             }
         }
     }
@@ -833,6 +829,22 @@ static int bind_tc(const KernelSpec& s, void** args) {
         c.valid = true;
     }
     return REEF_SUCC;
+}
+
+int make_chain(const KernelSpec* const* specs, void*** args, int n, int clusters, TcChain** out) {
+    std::vector<const TcParams*> params;
+    std::vector<TcPlan> plans;
+    for (int i = 0; i < n; i++) {
+        if (specs[i]->task.family != F_CONV_TC) {
+            set_error("a chain holds tensor-core convolution / matmul kernels only: " + specs[i]->name);
+            return REEF_FAIL;
+        }
+        int rc = bind_tc(*specs[i], args[i]);
+        if (rc != REEF_SUCC) return rc;
+        params.push_back(&specs[i]->tc_cache->params);
+        plans.push_back(specs[i]->tc);
+    }
+    return chain_create(params, plans, clusters, out);
 }
 
 int prepare_kernel(const KernelSpec& s, void** args) {
@@ -1071,6 +1083,7 @@ int kernel_attrs(const KernelSpec& s, reef_kernel_attrs_t* out) {
     out->bytes = s.bytes;
     out->tensor_core = s.tensor_core;
     out->cluster = s.task.family == F_CONV_TC ? s.tc.splits : 1;
+    out->chainable = s.task.family == F_CONV_TC ? 1 : 0;
     return REEF_SUCC;
 }
 

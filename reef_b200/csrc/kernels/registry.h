@@ -5,6 +5,7 @@
 
 #include <memory>
 #include <string>
+#include <vector>
 
 #include "../../../include/reef_cuda.h"
 #include "task.cuh"
@@ -64,6 +65,17 @@ int att_build_params(int s, int heads, int has_mask, void* const* args, AttParam
 int att_prepare_device();
 int att_launch(const AttParams& P, cudaStream_t st, const int* flag, int* slot, int head_begin = 0, int head_count = -1);
 int att_func_attrs(cudaFuncAttributes* fa, int* occ);
+
+// conv_tc_chain.cu: a run of tensor-core convolution layers as one persistent kernel
+struct TcChain;
+int chain_create(const std::vector<const TcParams*>& params, const std::vector<TcPlan>& plans, int clusters, TcChain** out);
+void chain_destroy(TcChain* c);
+int chain_launch(TcChain* c, cudaStream_t st);
+int chain_num_layers(const TcChain* c);
+int chain_clusters(const TcChain* c);
+int chain_max_clusters(const TcChain* c);
+// registry.cu: the chain of kernel specs [0, n) bound to their argument lists (all must be tensor-core convolutions)
+int make_chain(const KernelSpec* const* specs, void*** args, int n, int clusters, TcChain** out);
 
 // conv_tc.cu
 int tc_plan(const ConvP& p, TcPlan* pl);

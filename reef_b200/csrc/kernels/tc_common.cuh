@@ -10,6 +10,12 @@ namespace reef {
 
 constexpr int TC_UMMA_M = 128;   // rows of every UMMA tile here = the 128 lanes of tensor memory
 
+// Completion counters: a reduction with release semantics at GPU scope.  Issued by one thread behind a CTA barrier, it
+// orders every store of the CTA before the increment and, unlike fence + atomicAdd, waits for no value to come back.
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

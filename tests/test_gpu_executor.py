@@ -483,3 +483,37 @@ def test_attention_tensor_core_parity(tmp_path, s, heads, mask):
             assert np.array_equal(e.get_output(), got), f
         outs[variant] = got
     assert rel_err(outs["_v1"], outs[""]) < TF32_TOL
+
+
+@pytest.mark.parametrize("model,clusters", [("resnet18_64", 0), ("resnet50_64", 4), ("resnet152", 0), ("resnet152", 9), ("bert_base", 0),
+                                            ("inception_v3_139", 0), ("vgg16_32", 0), ("densenet121_64", 0)])
+def test_persistent_chain_is_bit_identical(gen, model, clusters):
+    """Runs of consecutive tensor-core layers as ONE persistent kernel (8-CTA clusters walking the layer list, layers
+    ordered by completion counters): every buffer bit-identical to the per-kernel launches, directly and as a CUDA
+    graph, for every K split the plans use and for several grid sizes (the tile -> CTA mapping changes with the
+    number of clusters, the arithmetic must not)."""
+    base = gen(model)
+    j = json.load(open(base + ".json"))
+    st = j["storage"][0]
+    x = seeded_input(st["size"], seed=17) if st["stype"] == "float32" else np.random.default_rng(17).integers(0, 1000, st["size"]).astype(np.int64)
+    ref = load_executor(base)
+    ref.set_input(st["name"], x)
+    ref.execute()
+    want = all_storage(ref, j)
+    e = load_executor(base)
+    n = e.build_chains(clusters)
+    assert n >= 1
+    e.set_input(st["name"], x)
+    for rep in range(3):
+        e.execute_chained()
+        got = all_storage(e, j)
+        for i, (a, b) in enumerate(zip(got, want)):
+            assert np.array_equal(a, b), f"{model}: storage {i} differs (chained run {rep})"
+    assert capi.device_error() == 0
+    e.execute_graph()
+    e.execute_graph()
+    got = all_storage(e, j)
+    for i, (a, b) in enumerate(zip(got, want)):
+        assert np.array_equal(a, b), f"{model}: storage {i} differs (graph with chains)"
+    assert capi.device_error() == 0
+    print(model, "chains", n, "clusters asked", clusters, "chain 0 (begin, end, clusters, max)", e.chain_info(0), "graph ms plain", ref.time(1, 3, 20), "with chains", e.time(1, 3, 20))
