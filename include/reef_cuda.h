@@ -207,14 +207,25 @@ REEF_API reef_status reef_dispatch_static(reef_kernel_t rt, void** rt_args,
  * one kernel per layer, executor_base.cpp:196-223; its persistent proxies host one layer each, trans_executor.cpp:132-173).
  * reef_chain_create binds `n` kernels (all with attrs.chainable) to their argument lists (args[i] as in reef_launch)
  * and builds the layer table and the completion counters in device memory — call it at load time, never during a
- * stream capture.  reef_chain_launch clears the counters (stream-ordered) and launches a resident grid of `clusters`
- * 8-CTA clusters (0 = default 16; never more than can be resident at once) that walks the layers in order; results are
- * bit-identical to launching the kernels one by one.  One chain object serves one stream at a time (its counters are
+ * stream capture.  reef_chain_launch sets the counters (stream-ordered) and launches a grid of `clusters` 8-CTA clusters
+ * (0 = default 32, two CTAs per SM) that walks the layers in order; results are bit-identical to launching the kernels
+ * one by one.  One chain object serves one stream at a time (its counters are
  * shared by its launches).  Every device-side wait is bounded; an expired wait raises the device error word. */
 typedef struct reef_chain_s* reef_chain_t;
 REEF_API reef_status reef_chain_create(reef_kernel_t* kernels, void*** args, int n, int clusters, reef_chain_t* chain);
 REEF_API reef_status reef_chain_launch(reef_chain_t chain, reef_stream_t s);
 REEF_API reef_status reef_chain_destroy(reef_chain_t chain);
+/* Best-effort use of a chain (the BE wrapper contract of script/best_effort_kernel.py:22-33 for a whole run of layers):
+ * the grid starts at `first_layer` (layers before it count as complete), runs on `clusters` clusters (0 = the chain's
+ * default) and polls *preempt_flag whenever a cluster takes its next tile: once the flag is up every cluster leaves at
+ * its next tile boundary.  The completion counters then say how far each layer got: reef_chain_copy_progress copies
+ * them (stream-ordered, to pinned memory) and, after the caller has synchronised `s`, reef_chain_first_incomplete
+ * returns the first layer that is not complete (the number of layers when all are): restart there, layers are
+ * idempotent.  Tiles are taken by ticket and in order, so a chain makes progress with however few of its clusters the
+ * hardware has made resident beside kernels of greater priority. */
+REEF_API reef_status reef_chain_launch_be(reef_chain_t chain, reef_stream_t s, int first_layer, reef_dptr_t preempt_flag, int clusters);
+REEF_API reef_status reef_chain_copy_progress(reef_chain_t chain, reef_stream_t s);
+REEF_API reef_status reef_chain_first_incomplete(reef_chain_t chain, int* layer);
 /* layers in the chain, clusters of its grid, and the most clusters the device can hold at once */
 REEF_API reef_status reef_chain_info(reef_chain_t chain, int* layers, int* clusters, int* max_clusters);
 

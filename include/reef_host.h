@@ -59,7 +59,14 @@ REEF_HOST_API int reef_executor_execute_dispatch(reef_executor_t e);        /* e
  * graph, then syncs.  Bit-identical to the per-kernel launches. */
 REEF_HOST_API int reef_executor_build_chains(reef_executor_t e, int clusters, size_t* num_chains);
 REEF_HOST_API int reef_executor_execute_chained(reef_executor_t e);
+/* As reef_executor_execute_preempt_resume, with every chain launched in its best-effort form on `clusters` clusters
+ * (0 = default): the flag stops a chain at a tile boundary and it is restarted at its first incomplete layer. */
+REEF_HOST_API int reef_executor_execute_preempt_resume_chained(reef_executor_t e, int delay_us, int clusters, int* restarts, int* first_incomplete);
 /* chain idx covers kernels [*begin, *end) of the schedule and runs on *clusters clusters of the *max_clusters the GPU holds at once */
+/* the best-effort flavour of the whole schedule with its chains on `clusters` clusters, then sync */
+REEF_HOST_API int reef_executor_execute_preemptable_chained(reef_executor_t e, int clusters);
+/* gives the executor a stream of its own with the greatest (high != 0) or the least CUDA stream priority */
+REEF_HOST_API int reef_executor_set_stream_priority(reef_executor_t e, int high);
 REEF_HOST_API int reef_executor_chain_info(reef_executor_t e, size_t idx, int* begin, int* end, int* clusters, int* max_clusters);
 /* Best-effort run with the preempt flag raised `delay_us` after the first launch (host timer), then
  * resumed from the first kernel whose completion counter is short until the model is done.

@@ -222,6 +222,19 @@ class HybridExecutor:
                "chain_info", self._err())
         return b.value, e.value, c.value, m.value
 
+    def execute_preempt_resume_chained(self, delay_us: int, clusters: int = 0):
+        restarts, first = C.c_int(), C.c_int()
+        _check(self._lib.reef_executor_execute_preempt_resume_chained(self._h, C.c_int(delay_us), C.c_int(clusters),
+                                                                      C.byref(restarts), C.byref(first)),
+               "execute_preempt_resume_chained", self._err())
+        return restarts.value, first.value
+
+    def execute_preemptable_chained(self, clusters: int = 0):
+        _check(self._lib.reef_executor_execute_preemptable_chained(self._h, C.c_int(clusters)), "execute_preemptable_chained", self._err())
+
+    def set_stream_priority(self, high: bool):
+        _check(self._lib.reef_executor_set_stream_priority(self._h, C.c_int(int(high))), "set_stream_priority", self._err())
+
     def execute_chained(self):
         _check(self._lib.reef_executor_execute_chained(self._h), "execute_chained", self._err())
 

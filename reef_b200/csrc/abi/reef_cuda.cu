@@ -381,6 +381,21 @@ reef_status reef_chain_launch(reef_chain_t chain, reef_stream_t s) {
     if (rc == REEF_SUCC) add_launches(1);
     return rc;
 }
+reef_status reef_chain_launch_be(reef_chain_t chain, reef_stream_t s, int first_layer, reef_dptr_t preempt_flag, int clusters) {
+    if (!chain || !preempt_flag) return REEF_FAIL;
+    int rc = chain_launch(chain->chain, (cudaStream_t)s, first_layer, (const int*)preempt_flag, clusters);
+    if (rc == REEF_SUCC) add_launches(1);
+    return rc;
+}
+reef_status reef_chain_copy_progress(reef_chain_t chain, reef_stream_t s) {
+    if (!chain) return REEF_FAIL;
+    return chain_copy_progress(chain->chain, (cudaStream_t)s);
+}
+reef_status reef_chain_first_incomplete(reef_chain_t chain, int* layer) {
+    if (!chain || !layer) return REEF_FAIL;
+    *layer = chain_first_incomplete(chain->chain);
+    return REEF_SUCC;
+}
 reef_status reef_chain_destroy(reef_chain_t chain) {
     if (chain) {
         chain_destroy(chain->chain);

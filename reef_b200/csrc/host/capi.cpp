@@ -135,6 +135,18 @@ int reef_executor_build_chains(reef_executor_t e, int clusters, size_t* num_chai
     return st;
 }
 int reef_executor_execute_chained(reef_executor_t e) { return e->exe.execute_chained(); }
+int reef_executor_execute_preempt_resume_chained(reef_executor_t e, int delay_us, int clusters, int* restarts, int* first_incomplete) {
+    return e->exe.execute_preempt_resume_chained(delay_us, clusters, restarts, first_incomplete);
+}
+int reef_executor_execute_preemptable_chained(reef_executor_t e, int clusters) { return e->exe.execute_preemptable_chained(clusters); }
+int reef_executor_set_stream_priority(reef_executor_t e, int high) {
+    reef_gpu_init(e->device);
+    reef_stream_t st = nullptr;
+    int rc = reef_stream_create(&st, high);
+    if (rc != REEF_SUCC) return rc;
+    e->exe.set_stream(st);    // the executor keeps the new stream for its lifetime (the old one stays allocated)
+    return Succ;
+}
 int reef_executor_chain_info(reef_executor_t e, size_t idx, int* begin, int* end, int* clusters, int* max_clusters) {
     return e->exe.chain_info(idx, begin, end, clusters, max_clusters);
 }

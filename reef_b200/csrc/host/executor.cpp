@@ -482,6 +482,111 @@ Status HybridExecutor::launch_schedule(GPUStream_t stream, bool use_chains) {
     return Status::Succ;
 }
 
+Status HybridExecutor::launch_preempt_chain(int k, int clusters, GPUStream_t stream, int* next) {
+    const int ci = chain_of(k);
+    if (ci < 0) RETURN_STATUS(Status::OutOfRange);
+    int rc = reef_chain_launch_be(chains[ci].handle, stream, k - chains[ci].begin, preempt_flag, clusters);
+    if (rc != REEF_SUCC) {
+        err_ = reef_last_error();
+        RETURN_STATUS((Status)rc);
+    }
+    if (next) *next = chains[ci].end;
+    return Status::Succ;
+}
+
+Status HybridExecutor::execute_preemptable_chained(int clusters, GPUStream_t stream) {
+    if (stream == nullptr) stream = s;
+    const int n = (int)num_kernels();
+    for (int i = 0; i < n;) {
+        if (chain_of(i) >= 0) {
+            int next = i;
+            RETURN_STATUS(launch_preempt_chain(i, clusters, stream, &next));
+            i = next;
+        } else {
+            RETURN_STATUS(launch_preempt_kernel(i, stream));
+            i++;
+        }
+    }
+    GPU_RETURN_STATUS(reef_stream_sync(stream));
+    return Status::Succ;
+}
+
+void HybridExecutor::copy_chain_progress(GPUStream_t stream) {
+    for (auto& c : chains) reef_chain_copy_progress(c.handle, stream);
+}
+
+int HybridExecutor::chain_kernel_offset(int from) {
+    // `from` inside a chain: the chain's counters say which of its layers are complete
+    const int ci = chain_of(from);
+    if (ci < 0) return from;
+    int layer = 0;
+    if (reef_chain_first_incomplete(chains[ci].handle, &layer) != REEF_SUCC) return from;
+    return std::max(from, chains[ci].begin + layer);
+}
+
+Status HybridExecutor::execute_preempt_resume_chained(int delay_us, int clusters, int* restarts, int* first_incomplete) {
+    GPUStream_t flag_stream;
+    GPU_RETURN_STATUS(reef_stream_create(&flag_stream, 1));
+    const int n = (int)num_kernels();
+    int from = 0, rounds = 0;
+    if (first_incomplete) *first_incomplete = -1;
+    GPU_RETURN_STATUS(reef_write32_async(flag_stream, preempt_flag, 0));
+    GPU_RETURN_STATUS(reef_stream_sync(flag_stream));
+    reset_task_slots(s, 0);
+    Status st = Status::Succ;
+    while (from < n) {
+        for (int i = from; i < n && st == Status::Succ;) {
+            if (chain_of(i) >= 0) {
+                int next = i;
+                st = launch_preempt_chain(i, clusters, s, &next);
+                i = next;
+            } else {
+                st = launch_preempt_kernel(i, s);
+                i++;
+            }
+        }
+        if (st != Status::Succ) break;
+        const bool preempt = rounds < 8;
+        if (preempt) {
+            auto t0 = std::chrono::steady_clock::now();
+            const int us = delay_us << std::min(rounds, 6);
+            while (std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count() < us) {
+            }
+            reef_write32_async(flag_stream, preempt_flag, 1);
+            reef_stream_sync(flag_stream);
+        }
+        if (reef_preempt_wait(s, 5000000) != REEF_SUCC) { st = Status::Timeout; break; }
+        copy_be_kernel_offset(s);
+        copy_chain_progress(s);
+        GPU_RETURN_STATUS(reef_stream_sync(s));
+        // first kernel not complete: plain kernels by their task slots, kernels inside a chain by its counters
+        int k = from;
+        while (k < n) {
+            const int ci = chain_of(k);
+            if (ci >= 0) {
+                const int kk = chain_kernel_offset(k);
+                if (kk < chains[ci].end) { k = kk; break; }
+                k = chains[ci].end;
+            } else {
+                if (task_slots_host[k] < trans_args[k].block_num) break;
+                k++;
+            }
+        }
+        if (preempt) {
+            reef_write32_async(flag_stream, preempt_flag, 0);
+            reef_stream_sync(flag_stream);
+        }
+        if (k >= n) break;
+        if (rounds == 0 && first_incomplete) *first_incomplete = k;
+        reset_task_slots(s, k);
+        from = k;
+        rounds++;
+    }
+    if (restarts) *restarts = rounds;
+    reef_stream_destroy(flag_stream);
+    return st;
+}
+
 Status HybridExecutor::execute_chained(GPUStream_t stream) {
     if (stream == nullptr) stream = s;
     RETURN_STATUS(launch_schedule(stream, true));

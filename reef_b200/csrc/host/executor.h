@@ -146,6 +146,24 @@ public:
     }
     // the whole schedule with chains where they exist and plain launches elsewhere, then sync
     Status execute_chained(GPUStream_t stream = nullptr);
+    // Best-effort flavour with chains: kernel `k` must be the first kernel of a chain or inside one; the chain is
+    // launched from that layer on `clusters` clusters (0 = default) with the preempt flag polled at every tile.
+    // Returns the chain's end (first kernel behind it) in *next.
+    Status launch_preempt_chain(int k, int clusters, GPUStream_t stream, int* next);
+    // chain index whose run contains kernel k, or -1
+    int chain_of(int k) const {
+        for (size_t i = 0; i < chains.size(); i++)
+            if (k >= chains[i].begin && k < chains[i].end) return (int)i;
+        return -1;
+    }
+    // after a preemption: copy every chain's counters on `stream` (async); once the stream is synchronised,
+    // chain_kernel_offset(from) = the first kernel at or behind `from` that is not known complete
+    void copy_chain_progress(GPUStream_t stream);
+    int chain_kernel_offset(int from);
+    // best-effort flavour of the whole schedule, chains on `clusters` clusters, then sync (the flag is not touched)
+    Status execute_preemptable_chained(int clusters, GPUStream_t stream = nullptr);
+    // best-effort run of the whole schedule with chains, flag raised after delay_us, resumed until done
+    Status execute_preempt_resume_chained(int delay_us, int clusters, int* restarts, int* first_incomplete);
     // CUDA graph of the whole kernel list on `stream` (captured lazily on first use)
     Status execute_graph(GPUStream_t stream);
     // every kernel through the dispatcher without a best-effort partner, then sync

@@ -12,7 +12,11 @@ namespace reef {
 struct TcChain {
     TcParams* layers = nullptr;   // device
     int* need = nullptr;          // device
-    int* done = nullptr;          // device, n + 2 words
+    int* done = nullptr;          // device, n + 3 words: counters, "gave up", ticket
+    int* init0 = nullptr;         // pinned host image of `done` for a launch from layer 0 (constant: usable in a graph)
+    int* progress = nullptr;      // pinned host copy of `done` (reef_chain_copy_progress)
+    std::vector<int> need_h;      // host copies of need[] and of the group prefix
+    std::vector<int> goff_h;
     int n = 0;
     int ctrl_offset = 0;
     int smem = 0;
@@ -99,23 +103,32 @@ int chain_create(const std::vector<const TcParams*>& params, const std::vector<T
         delete c;
         return REEF_FAIL;
     }
+    // Tile groups are taken by ticket, in order, so any number of clusters is safe: those the hardware has not made
+    // resident simply take no tickets.  The default asks for two CTAs per SM.
     c->clusters = clusters > 0 ? clusters : 32;
-    if (c->clusters > c->max_clusters) c->clusters = c->max_clusters;
+    c->need_h.assign(need.begin(), need.begin() + n + 1);
+    c->goff_h.assign(need.begin() + n + 1, need.end());
     if (cudaMalloc(&c->layers, sizeof(TcParams) * n) != cudaSuccess || cudaMalloc(&c->need, 4 * (2 * n + 2)) != cudaSuccess ||
-        cudaMalloc(&c->done, 4 * (n + 2)) != cudaSuccess ||
+        cudaMalloc(&c->done, 4 * (n + 3)) != cudaSuccess ||
+        cudaHostAlloc((void**)&c->init0, 4 * (n + 3), cudaHostAllocDefault) != cudaSuccess ||
+        cudaHostAlloc((void**)&c->progress, 4 * (n + 3), cudaHostAllocDefault) != cudaSuccess ||
         cudaMemcpy(c->layers, host.data(), sizeof(TcParams) * n, cudaMemcpyHostToDevice) != cudaSuccess ||
         cudaMemcpy(c->need, need.data(), 4 * (2 * n + 2), cudaMemcpyHostToDevice) != cudaSuccess ||
-        cudaMemset(c->done, 0, 4 * (n + 2)) != cudaSuccess || cudaStreamSynchronize(cudaStreamLegacy) != cudaSuccess) {
+        cudaMemset(c->done, 0, 4 * (n + 3)) != cudaSuccess || cudaStreamSynchronize(cudaStreamLegacy) != cudaSuccess) {
         set_error("chain: cannot allocate or fill the layer table");
         chain_destroy(c);
         return REEF_FAIL;
     }
+    memset(c->init0, 0, 4 * (n + 3));
+    memset(c->progress, 0, 4 * (n + 3));
     *out = c;
     return REEF_SUCC;
 }
 
 void chain_destroy(TcChain* c) {
     if (!c) return;
+    if (c->init0) cudaFreeHost(c->init0);
+    if (c->progress) cudaFreeHost(c->progress);
     if (c->layers) cudaFree(c->layers);
     if (c->need) cudaFree(c->need);
     if (c->done) cudaFree(c->done);
@@ -126,8 +139,15 @@ int chain_num_layers(const TcChain* c) { return c->n; }
 int chain_clusters(const TcChain* c) { return c->clusters; }
 int chain_max_clusters(const TcChain* c) { return c->max_clusters; }
 
-int chain_launch(TcChain* c, cudaStream_t st) {
+int chain_launch(TcChain* c, cudaStream_t st, int first_layer, const int* flag, int clusters) {
+    if (first_layer < 0 || first_layer >= c->n) {
+        set_error("chain: first layer outside the chain");
+        return REEF_OUT_OF_RANGE;
+    }
     ChainParams P;
+    P.preempt_flag = flag;
+    P.first_group = c->goff_h[first_layer];
+    P.total_groups = c->goff_h[c->n];
     P.layers = c->layers;
     P.need = c->need;
     P.done = c->done;
@@ -135,13 +155,25 @@ int chain_launch(TcChain* c, cudaStream_t st) {
     P.ctrl_offset = c->ctrl_offset;
     int rc = tc_error_word(&P.error_word);
     if (rc != REEF_SUCC) return rc;
-    if (cudaMemsetAsync(c->done, 0, 4 * (c->n + 2), st) != cudaSuccess) {
-        set_error("chain: cannot clear the completion counters");
+    // counters: the layers before first_layer count as complete, the ticket counter starts at its first group
+    cudaError_t e;
+    if (first_layer == 0) {
+        e = cudaMemcpyAsync(c->done, c->init0, 4 * (c->n + 3), cudaMemcpyHostToDevice, st);   // constant pinned image
+    } else {
+        std::vector<int> img(c->n + 3, 0);
+        for (int l = 0; l <= first_layer; l++) img[l] = c->need_h[l];
+        img[c->n + 2] = c->goff_h[first_layer];
+        // pageable source: the bytes are staged before the call returns (a restart is never part of a stream capture)
+        e = cudaMemcpyAsync(c->done, img.data(), 4 * (c->n + 3), cudaMemcpyHostToDevice, st);
+    }
+    if (e != cudaSuccess) {
+        set_error(std::string("chain: cannot set the completion counters: ") + cudaGetErrorString(e));
         return REEF_FAIL;
     }
+    const int nc = clusters > 0 ? clusters : c->clusters;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(TC_CHAIN_CLUSTER, c->clusters, 1);
+    cfg.gridDim = dim3(TC_CHAIN_CLUSTER, nc, 1);
     cfg.blockDim = dim3(TC_THREADS);
     cfg.dynamicSmemBytes = c->smem;
     cfg.stream = st;
@@ -152,12 +184,27 @@ int chain_launch(TcChain* c, cudaStream_t st) {
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, reef_conv_tc_chain_kernel, P);
+    e = cudaLaunchKernelEx(&cfg, reef_conv_tc_chain_kernel, P);
     if (e != cudaSuccess) {
         set_error(std::string("cudaLaunchKernelEx(conv_tc_chain): ") + cudaGetErrorString(e));
         return REEF_FAIL;
     }
     return REEF_SUCC;
+}
+
+// progress of a (possibly preempted) launch: stream-ordered copy of the counters to pinned memory, then, once the
+// caller has synchronised, the first layer whose counter is short (n = every layer complete)
+int chain_copy_progress(TcChain* c, cudaStream_t st) {
+    if (cudaMemcpyAsync(c->progress, c->done, 4 * (c->n + 3), cudaMemcpyDeviceToHost, st) != cudaSuccess) {
+        set_error("chain: cannot copy the completion counters");
+        return REEF_FAIL;
+    }
+    return REEF_SUCC;
+}
+int chain_first_incomplete(const TcChain* c) {
+    for (int l = 0; l < c->n; l++)
+        if (c->progress[l + 1] < c->need_h[l + 1]) return l;
+    return c->n;
 }
 
 }  // namespace reef

@@ -5,8 +5,11 @@
 // best-effort grids that launch and retire beside a real-time chain cost it time.  Here a resident grid of
 // 8-CTA clusters walks the layer list itself:
 //   * tensor memory is allocated and the mbarriers are initialised once; their phases are carried from tile to tile;
-//   * layer l's tiles are dealt out to the clusters in a fixed order (group g of a layer goes to cluster g mod NC): no
-//     tickets, no atomics on the way in, and the same CTA computes the same tile in every run (bit-reproducible);
+//   * the tile groups of all layers form one ordered list; a cluster takes the next group with a ticket (one atomic
+//     by rank 0, handed to the other ranks through distributed shared memory).  Groups are taken in order, so the
+//     layers a group depends on are always held by clusters that are running: the walk cannot deadlock however few
+//     clusters the hardware has made resident (a best-effort chain shares the GPU with real-time kernels of greater
+//     priority).  Which cluster computes a tile does not matter for the result: the arithmetic of a tile is fixed;
 //   * a cluster of 8 serves every K split of the per-layer plans: with S splits it works on 8/S tiles at once, the
 //     K-split exchange staying inside each group of S ranks;
 //   * layers are ordered by completion counters in global memory: every CTA that has stored its rows adds one
@@ -16,7 +19,10 @@
 //     layer before l+1 is complete, so residual inputs need no counter of their own.
 // The tile body is the per-layer kernel's: TMA ring -> tcgen05.mma (TF32, fp32 accumulate in TMEM) -> staging ->
 // K-split exchange over distributed shared memory in fixed rank order -> fused epilogue; results are bit-identical
-// to the per-layer launches.  Real-time flavour only (no preempt flag: a real-time task is never preempted).
+// to the per-layer launches.
+// Best-effort use (preempt_flag != nullptr): rank 0 reads the flag whenever it takes a ticket and hands out "stop"
+// instead: every cluster leaves at its next tile boundary (a tile is a few microseconds).  The completion counters
+// say how far each layer got; the host restarts the chain at the first incomplete layer (layers are idempotent).
 #pragma once
 #include <cstddef>
 
@@ -27,11 +33,14 @@ namespace reef {
 constexpr int TC_CHAIN_CLUSTER = 8;
 
 struct ChainParams {
+    const int* preempt_flag;  // best-effort use: polled at every ticket; nullptr for a real-time chain
+    int first_group;          // (informative) the ticket counter starts here: a restart skips the complete layers
+    int total_groups;
     const TcParams* layers;   // device array, one entry per layer (tensor maps included: 64-byte aligned entries)
     const int* need;          // need[l] = CTAs of layer l-1 that must have finished before layer l may read (need[0] = 0);
                               // need[n_layers + 1 + l] = tile groups of all layers before l (deals the groups out in turn)
     int* done;                // done[l] = CTAs of layer l-1 that have finished; done[n_layers + 1] = "a CTA gave up";
-                              // zeroed before every launch
+                              // done[n_layers + 2] = the ticket counter.  Initialised by the host before every launch
     int* error_word;
     int n_layers;
     int ctrl_offset;          // offset of the control words in dynamic shared memory = largest data region of any layer
@@ -53,11 +62,10 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_chain_kernel(const
     const uint32_t bar_red = bar_acc + 8;
     volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + C.ctrl_offset + 16 * TC_MAX_STAGES + 16);
     volatile uint32_t* s_flags = s_tmem + 1;    // [0] some CTA of the grid gave up (read once per tile), [1] a wait of
-                                                //  this CTA expired; both sticky for the rest of the launch
+                                                //  this CTA expired; both sticky for the rest of the launch.  [4],[5]: tickets
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rank = (int)cluster_ctarank();      // 0..7
-    const int cid = blockIdx.y, NC = gridDim.y;
     constexpr uint32_t TMEM_COLS = 256;
 
     if (tid == 0) {
@@ -102,31 +110,46 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_chain_kernel(const
     static_assert((sizeof(TcParams) - kMapBytes) % 8 == 0, "copied in 8-byte words");
     TcParams* Ps = reinterpret_cast<TcParams*>(smem + C.ctrl_offset + 256 - kMapBytes);
 
+    const int* goff = C.need + C.n_layers + 1;          // goff[l] = tile groups of all layers before l
+    volatile int* s_ticket = reinterpret_cast<volatile int*>(s_flags + 4);   // [2]: alternating, a rank lags at most one turn
+    int L = 0, cur_L = -1, turn = 0;
+
 #pragma unroll 1
-    for (int L = 0; L < C.n_layers; L++) {
+    for (;; turn ^= 1) {
+        // ---- the next tile group: rank 0 takes a ticket and hands it to every rank of the cluster ----
+        if (rank == 0 && tid == 0) {
+            int G = -1;
+            const bool stop = (C.preempt_flag != nullptr && *reinterpret_cast<const volatile int*>(C.preempt_flag) != 0) || s_flags[0] != 0 || s_flags[1] != 0;
+            if (!stop) {
+                G = atomicAdd(&C.done[C.n_layers + 2], 1);
+                if (G >= C.total_groups) G = -1;
+            }
+            for (uint32_t q = 0; q < (uint32_t)TC_CHAIN_CLUSTER; q++)
+                st_dsmem_u32(mapa_shared(smem_u32((const void*)&s_ticket[turn]), q), (uint32_t)G);
+        }
+        cluster_sync_all();      // the ticket is in every rank's shared memory
+        const int G = s_ticket[turn];
+        if (G < 0) break;
+        while (G >= goff[L + 1]) L++;
         const TcParams& Pg = C.layers[L];
-        {
+        if (L != cur_L) {
+            __syncthreads();     // every thread is done with the previous layer's parameters
             const unsigned long long* src = reinterpret_cast<const unsigned long long*>(reinterpret_cast<const unsigned char*>(&Pg) + kMapBytes);
             unsigned long long* dst = reinterpret_cast<unsigned long long*>(smem + C.ctrl_offset + 256);
             for (int i = tid; i < (int)((sizeof(TcParams) - kMapBytes) / 8); i += TC_THREADS) dst[i] = __ldg(src + i);
             __syncthreads();
+            cur_L = L;
         }
         const TcParams& P = *Ps;
         const int S = P.splits;
         const int per = TC_CHAIN_CLUSTER / S;                       // tiles a cluster works on at once
         const int tiles = P.n_tiles * ((P.co + TC_BM - 1) / TC_BM);
-        const int groups = (tiles + per - 1) / per;
         const int NS = P.stages;
         const uint32_t stage_bytes = TC_A_BYTES + (uint32_t)P.n_mma * 128u;
         const int split = rank % S, sub = rank / S;                 // K-split rank and tile slot inside the cluster
         const uint32_t grp_base = (uint32_t)(sub * S);              // cluster rank of this group's split 0
-        // The tile groups of ALL layers are dealt out to the clusters in turn (group g of layer l goes to cluster
-        // (groups before l + g) mod NC): with more clusters than a layer has groups, the clusters that are idle
-        // during layer l hold the tiles of layer l+1, have requested their weights and wait at the dependency — the
-        // overlap a chain of separate launches gets from the early launch of the next grid.
-        const int g0 = (cid - C.need[C.n_layers + 1 + L] % NC + NC) % NC;
-#pragma unroll 1
-        for (int g = g0; g < groups; g += NC) {
+        const int g = G - goff[L];
+        {
             const int tile = g * per + sub;
             // after a failure anywhere in the grid the CTAs only keep their cluster barriers going (every wait is
             // bounded, and nothing new is started, so the launch ends within a few seconds at worst)
@@ -359,7 +382,6 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_chain_kernel(const
             }
             __syncthreads();
         }
-        __syncthreads();    // every thread is done with this layer's parameters before the next layer's overwrite them
     }
     if (!ok && tid == 0 && C.error_word) *reinterpret_cast<volatile int*>(C.error_word) = 1;
     // the kernels behind the chain may start their prologues

@@ -70,7 +70,9 @@ int att_func_attrs(cudaFuncAttributes* fa, int* occ);
 struct TcChain;
 int chain_create(const std::vector<const TcParams*>& params, const std::vector<TcPlan>& plans, int clusters, TcChain** out);
 void chain_destroy(TcChain* c);
-int chain_launch(TcChain* c, cudaStream_t st);
+int chain_launch(TcChain* c, cudaStream_t st, int first_layer = 0, const int* flag = nullptr, int clusters = 0);
+int chain_copy_progress(TcChain* c, cudaStream_t st);
+int chain_first_incomplete(const TcChain* c);
 int chain_num_layers(const TcChain* c);
 int chain_clusters(const TcChain* c);
 int chain_max_clusters(const TcChain* c);

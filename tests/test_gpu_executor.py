@@ -517,3 +517,34 @@ def test_persistent_chain_is_bit_identical(gen, model, clusters):
         assert np.array_equal(a, b), f"{model}: storage {i} differs (graph with chains)"
     assert capi.device_error() == 0
     print(model, "chains", n, "clusters asked", clusters, "chain 0 (begin, end, clusters, max)", e.chain_info(0), "graph ms plain", ref.time(1, 3, 20), "with chains", e.time(1, 3, 20))
+
+
+@pytest.mark.parametrize("model,clusters,delays", [("resnet50_64", 2, [30, 80, 200]), ("resnet152", 4, [200, 700, 2500]),
+                                                   ("resnet152", 0, [100, 400, 1200])])
+def test_best_effort_chain_preempted_and_resumed_is_bit_identical(gen, model, clusters, delays):
+    """The best-effort form of a persistent chain: the preempt flag goes up while the chain walks its layers, every
+    cluster leaves at its next tile boundary, the completion counters give the first incomplete layer and the chain is
+    restarted there.  Every buffer ends bit-identical to an uninterrupted per-kernel run, for a chain that runs on a
+    few clusters (the padding configuration) as well as on the default grid."""
+    base = gen(model)
+    j = json.load(open(base + ".json"))
+    x = seeded_input(j["storage"][0]["size"], seed=23)
+    ref = load_executor(base)
+    ref.set_input("data", x)
+    ref.execute()
+    want = all_storage(ref, j)
+    e = load_executor(base)
+    assert e.build_chains(0) >= 1
+    e.set_input("data", x)
+    hit = []
+    for d in delays:
+        restarts, first = e.execute_preempt_resume_chained(d, clusters)
+        hit.append((d, restarts, first))
+        got = all_storage(e, j)
+        for i, (a, b) in enumerate(zip(got, want)):
+            assert np.array_equal(a, b), f"{model} delay {d}us: storage {i} differs after {restarts} restarts (first {first})"
+    print(model, "clusters", clusters, "(delay us, restarts, first incomplete kernel):", hit)
+    assert capi.device_error() == 0
+    assert any(r > 0 for _, r, _ in hit), "no delay landed inside the run"
+    b, en, _, _ = e.chain_info(0)
+    assert any(b < f < en for _, r, f in hit if r > 0), "no preemption stopped the chain in the middle of its layers"
