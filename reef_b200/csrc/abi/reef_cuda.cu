@@ -171,6 +171,7 @@ reef_status reef_write32_async(reef_stream_t s, reef_dptr_t ptr, uint32_t value)
         }
     }
     if (g_write32_state == 1) {
+        // (the no-memory-barrier form of the write is refused by this driver with CUDA_ERROR_INVALID_VALUE)
         int rc = g_write32((cudaStream_t)s, (unsigned long long)ptr, value, 0);
         if (rc != 0) {
             set_error("cuStreamWriteValue32 failed with CUresult " + std::to_string(rc));
