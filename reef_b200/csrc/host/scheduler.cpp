@@ -445,7 +445,16 @@ void REEFScheduler::loop_body() {
 void REEFScheduler::retire(TaskQueue& q, Task& t) {
     while (!q.inflight.empty()) {
         int pending = 1;
-        if (reef_event_query(q.inflight.front().ev, &pending) != REEF_SUCC || pending) break;
+        if (reef_event_query(q.inflight.front().ev, &pending) != REEF_SUCC) {
+            // the device reports an error (it stays set for the life of the context): nothing in flight will ever
+            // complete.  The window is emptied and the task marked failed, so that it ends instead of waiting forever.
+            if (!t.failed) fprintf(stderr, "[reef] best-effort task %u: the device reports an error, the task is failed\n", t.id);
+            t.failed = true;
+            for (auto& f : q.inflight) q.free_events.push_back(f.ev);
+            q.inflight.clear();
+            break;
+        }
+        if (pending) break;
         t.kernel_offset = std::max(t.kernel_offset, q.inflight.front().kernel + 1);
         t.block_offset = 0;
         q.free_events.push_back(q.inflight.front().ev);
@@ -786,7 +795,13 @@ bool REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
             auto& q = *be_queues[i];
             while (!q.pad_out.empty()) {
                 int pending = 1;
-                if (reef_event_query(q.pad_out.front().ev, &pending) != REEF_SUCC || pending) break;
+                if (reef_event_query(q.pad_out.front().ev, &pending) != REEF_SUCC) {
+                    // device error: the pieces out will never complete; forget them (their tasks fail in retire())
+                    for (auto& po : q.pad_out) q.free_events.push_back(po.ev);
+                    q.pad_out.clear();
+                    break;
+                }
+                if (pending) break;
                 pad_trace.retired++;
                 pad_trace.turnaround_ns += abs_ns() - q.pad_out.front().t_launch;
                 q.free_events.push_back(q.pad_out.front().ev);

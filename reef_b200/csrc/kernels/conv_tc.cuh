@@ -169,8 +169,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
     const uint32_t bar_red = bar_acc + 8;
     volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(smem + P.region_bytes + 16 * TC_MAX_STAGES + 16);
     volatile uint32_t* s_flags = s_tmem + 1;    // [0] abort (preempt flag seen by this CTA), [1] wait expired,
-                                                //  [2] K blocks whose loads were issued when the producer stopped,
-                                                //  [3] some rank of the cluster stopped (written by that rank)
+                                                //  [2] K blocks whose loads were issued when the producer stopped
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // best-effort flavour: the poll at block entry is issued first, so that its latency hides behind the set-up
@@ -196,7 +195,6 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         s_flags[0] = (uint32_t)(flag0 != 0);
         s_flags[1] = 0;
         s_flags[2] = 0;
-        s_flags[3] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&P.tm_w) : "memory");
@@ -404,14 +402,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
         // (best-effort flavour: with release semantics, the peers read this CTA's abort word behind the barrier)
         const bool my_abort = BE && s_flags[0] != 0;   // final: producer and MMA thread are past their loops
         if (S > 1) {
-            if (BE) {
-                // a rank that stopped tells every rank of its cluster (itself included) with a remote store ahead of
-                // the barrier: behind the barrier each rank reads only its own shared memory
-                if (my_abort && tid < S) st_dsmem_u32(mapa_shared(smem_u32((const void*)&s_flags[3]), (uint32_t)tid), 1u);
-                cluster_arrive();
-            } else {
-                cluster_arrive_relaxed();
-            }
+            // (best-effort flavour: with release semantics, the peers read this CTA's abort word behind the barrier.
+            // Nothing may be written into a peer's shared memory before this barrier: only behind it is every CTA
+            // of the cluster known to have started.)
+            if (BE) cluster_arrive();
+            else cluster_arrive_relaxed();
         }
         if (!ok || s_flags[1]) {
             ok = false;
@@ -461,8 +456,14 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             if (warp == 1) tmem_free(tmem, (uint32_t)P.tmem_cols);
             cluster_wait();       // barrier #1: all peers are past their main loops (and their barriers are armed)
             if (tid == 0) tc_stamp(P, 3);
-            // (the word was written, if at all, before its writer arrived at the barrier: all ranks read the same)
-            if (BE) abort_all = s_flags[3] != 0;
+            if (BE) {
+                // every rank learns whether ANY rank of the cluster stopped for the preempt flag: one thread per rank
+                // reads that rank's abort word through distributed shared memory; all ranks compute the same OR
+                uint32_t f = 0;
+                if (tid < S)
+                    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(f) : "r"(mapa_shared(smem_u32((const void*)&s_flags[0]), (uint32_t)tid)) : "memory");
+                abort_all = __syncthreads_or((int)f) != 0;
+            }
             if (!abort_all) {
                 if (tid < S && tid != split) {   // one thread per peer: the copies are issued side by side
                     const int q = tid;
