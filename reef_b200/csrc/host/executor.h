@@ -52,6 +52,8 @@ public:
     Status execute_kernel(int idx, GPUStream_t stream = nullptr);
     Status execute_kernel_async(int idx) { return launch_kernel(idx, s); }   // no sync
     size_t num_kernels() const;
+    // name of kernel i as the schedule gives it (diagnostics)
+    const char* kernel_name(size_t i) const { return model && i < model->kernels.size() ? model->kernels[i].name.c_str() : "?"; }
 
     void set_stream(GPUStream_t stream);
     GPUStream_t stream() const;

@@ -307,8 +307,33 @@ bool REEFScheduler::device_error_seen(const char* where) {
     return true;
 }
 
+// Diagnostics for the first CUDA error of a run: a device fault is reported by whichever call comes next, not by the
+// kernel that caused it, so the kernels every best-effort stream had in flight at that moment are listed once.
+void REEFScheduler::dump_streams_once(const char* why) {
+    if (streams_dumped) return;
+    streams_dumped = true;
+    fprintf(stderr, "[reef] first error (%s): preempted=%d wait_sync=%d; best-effort streams:\n", why, (int)preempted, (int)wait_sync);
+    const uint32_t nq = be_queue_cnt.load();
+    for (uint32_t i = 0; i < nq; i++) {
+        auto& q = *be_queues[i];
+        if (q.task_queue.empty()) {
+            fprintf(stderr, "[reef]   queue %u: idle, %zu padded pieces out\n", i, q.pad_out.size());
+            continue;
+        }
+        auto t = q.task_queue.front();
+        auto& exe = t->model->executor;
+        fprintf(stderr, "[reef]   queue %u: task %u state %d kernel_offset %d launch_offset %d block_offset %d padded pieces out %zu\n", i,
+                t->id, (int)t->get_state(), t->kernel_offset, t->launch_offset, t->block_offset, q.pad_out.size());
+        for (auto& f : q.inflight) fprintf(stderr, "[reef]     in flight (best-effort flavour): %d %s\n", f.kernel, exe.kernel_name(f.kernel));
+        for (int k : q.preempted_kernels) fprintf(stderr, "[reef]     in flight at the last preemption: %d %s\n", k, exe.kernel_name(k));
+        if (q.inflight.empty() && t->kernel_offset < (int)exe.num_kernels())
+            fprintf(stderr, "[reef]     next kernel: %d %s\n", t->kernel_offset, exe.kernel_name(t->kernel_offset));
+    }
+}
+
 // a best-effort task whose launch failed: ended as failed, off its queue, nothing left in the window
 void REEFScheduler::fail_be_task(TaskQueue& q, std::shared_ptr<Task>& t, const std::string& why) {
+    dump_streams_once(why.c_str());
     err_ = why;
     fprintf(stderr, "[reef] best-effort task %u failed: %s\n", t->id, why.c_str());
     for (auto& f : q.inflight) q.free_events.push_back(f.ev);
@@ -494,7 +519,11 @@ void REEFScheduler::preempt_reset() {
             hit.push_back(Hit{task, &q, q.inflight.empty() ? nullptr : q.inflight.back().ev});
             // An event that fires after the flag went up may belong to a kernel that left early, so the
             // window is not consulted here: kernel_offset stays at what the last poll saw complete.
-            for (auto& f : q.inflight) q.free_events.push_back(f.ev);
+            q.preempted_kernels.clear();
+            for (auto& f : q.inflight) {
+                q.preempted_kernels.push_back(f.kernel);
+                q.free_events.push_back(f.ev);
+            }
             q.inflight.clear();
             task->launch_offset = task->kernel_offset;
             task->state.store(TaskState::Waiting);
@@ -769,6 +798,7 @@ bool REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
     auto t0 = sclock::now();
     if (rt_exe.execute_graph(rt_queue->stream) != Status::Succ) {
         err_ = "real-time graph launch failed: " + rt_exe.error();
+        dump_streams_once(err_.c_str());
         fprintf(stderr, "[reef] %s\n", err_.c_str());
         if (flag_early) preempt_be_tasks();   // the flag is up: bring the bookkeeping in line with it
         return false;
@@ -1150,6 +1180,7 @@ void REEFScheduler::execute_be_task(std::shared_ptr<Task>& task, std::shared_ptr
         if (exe.launch_preempt_kernel(k, tqueue->stream) != Status::Succ) {
             // fail the task rather than spin on it: Finish with the failed mark (wait_task returns Fail)
             err_ = "best-effort launch failed: " + exe.error();
+            dump_streams_once(err_.c_str());
             fprintf(stderr, "[reef] %s\n", err_.c_str());
             for (auto& f : tqueue->inflight) tqueue->free_events.push_back(f.ev);
             tqueue->inflight.clear();

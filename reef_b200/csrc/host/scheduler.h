@@ -199,6 +199,7 @@ private:
         int pad_quantum_left = 0;
         bool pad_draining = false;
         bool counters_pending = false;   // a copy of the head task's completion counters is on the stream (wait_sync)
+        std::vector<int> preempted_kernels;   // kernels that were in flight at the last preemption (diagnostics)
     };
 
     Status create_task_queue(std::shared_ptr<TaskQueue>& ret, bool rt);
@@ -212,6 +213,8 @@ private:
     bool dynamic_kernel_padding(std::shared_ptr<Task>& rt_task);
     bool timeline_padding(std::shared_ptr<Task>& rt_task);
     bool device_error_seen(const char* where);
+    void dump_streams_once(const char* why);   // what every best-effort stream had in flight (printed once)
+    bool streams_dumped = false;
     void fail_be_task(TaskQueue& q, std::shared_ptr<Task>& t, const std::string& why);
     bool side_padding_needed(executor::HybridExecutor& rt_exe);
     void advance_padded(Task* be_task, TaskQueue* q, int blocks, bool side_launch,

@@ -564,8 +564,11 @@ template <int F>
 __global__ void __launch_bounds__(kThreads) k_be(const __grid_constant__ KTask t, const int* __restrict__ flag,
                                                  int* __restrict__ task_slot) {
     pdl_prologue();
-    if (ld_flag(flag)) {
-        preempt_stamp_leave();
+    // ONE thread reads the flag and the block takes one decision: were every thread to read it for itself, a flag
+    // that goes up between the reads of two warps would let part of a block leave and the rest run the body with
+    // threads missing (wrong partial sums counted as a complete block, barriers short of arrivals).
+    if (__syncthreads_or(threadIdx.x == 0 ? ld_flag(flag) : 0)) {
+        if (threadIdx.x == 0) preempt_stamp_leave();
         return;
     }
     const bool done = run_body<F>(t, blockIdx.x, reef_dyn_smem, flag);
@@ -1021,7 +1024,9 @@ int launch_dispatch_static(const KernelSpec* rt, void** rt_args, const KernelSpe
         return REEF_OUT_OF_RANGE;
     }
     if (g_static_ctrl_ptr[dev] == nullptr) {
-        // set-up, once per device, with that device current
+        // set-up, once per device, with that device current.  The cache is filled without a lock: two threads that
+        // both find it empty ask the runtime for the same symbol of the same device and store the same address, so
+        // whichever store lands last changes nothing (a pointer-sized aligned store is not torn on the host).
         void* p = nullptr;
         int rc = check_cuda(cudaGetSymbolAddress(&p, g_static_dispatch_ctrl), "cudaGetSymbolAddress(static dispatch lanes)");
         if (rc != REEF_SUCC) return rc;

@@ -265,6 +265,32 @@ __device__ __forceinline__ bool dense_mbar_wait(uint32_t bar, uint32_t parity) {
     }
     return false;
 }
+// The consumers' wait in the best-effort flavour: 0 = the stage landed, 1 = the wait expired, 2 = the producer stopped
+// before it issued this stage (ctl[0] set and st >= ctl[1]).  A warp that runs ahead of the producer can already be
+// waiting for a stage when the producer sees the preempt flag and decides never to issue it: the stop has to be looked
+// at inside the wait, or that warp sits out the whole time limit.
+__device__ __forceinline__ int dense_mbar_wait_abortable(uint32_t bar, uint32_t parity, const volatile int* ctl, int st) {
+    unsigned long long t0 = 0;
+    for (int i = 0; i < (1 << 26); i++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return 0;
+        if (ctl[0] && st >= ctl[1]) return 2;
+        if ((i & 255) == 255) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > 1000000000ull) return 1;
+        }
+    }
+    return 1;
+}
 __device__ __forceinline__ bool body_dense(const KTask& t, int vb, unsigned char* smem_raw, const int* flag) {
     const DenseP& p = t.p.dense;
     const float* x = (const float*)t.a[0];
@@ -339,11 +365,17 @@ __device__ __forceinline__ bool body_dense(const KTask& t, int vb, unsigned char
                     xv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                     if ((tid + j * kThreads) * 4 < kc) xv[j] = __ldg(reinterpret_cast<const float4*>(x + k0) + tid + j * kThreads);
                 }
-                if (flag != nullptr && ctl[0] && st >= ctl[1]) {     // the producer stopped and nothing more is in flight
-                    stopped = 1;
-                    break;
-                }
-                if (!dense_mbar_wait(bar_full + 8 * s, par)) {
+                if (flag != nullptr) {
+                    const int w = dense_mbar_wait_abortable(bar_full + 8 * s, par, ctl, st);
+                    if (w == 2) {          // the producer stopped before this stage: nothing of it is in flight
+                        stopped = 1;
+                        break;
+                    }
+                    if (w == 1) {
+                        ok = false;
+                        break;
+                    }
+                } else if (!dense_mbar_wait(bar_full + 8 * s, par)) {
                     ok = false;
                     break;
                 }
