@@ -271,6 +271,14 @@ REEF_API reef_status reef_flag_alloc_mapped(uint32_t** host_ptr, reef_dptr_t* de
 REEF_API reef_status reef_flag_free_mapped(uint32_t* host_ptr);
 REEF_API reef_status reef_flag_set(uint32_t* host_ptr, uint32_t value);
 
+/* Measurement helper: what the host sees of the device through a stream.  `iters` times (spaced 200 us apart, after
+ * iters/10 untimed rounds) it (a) issues reef_write32_async on an idle high-priority stream, (b) records an event
+ * behind it and spins on reef_event_query until it completes, (c) records a bare event and spins again.  Medians in
+ * microseconds: the cost of the write call, write + completion as seen from the host, a bare event's round trip.
+ * These are the floor of any host-clocked figure that ends with "the stream is idle" (the preemption drain). */
+REEF_API reef_status reef_probe_stream_latency(int iters, double* write_call_us, double* write_complete_us,
+                                               double* event_round_trip_us);
+
 /* Number of kernels this library launched since load (its own kernels only; graph replays count
  * the kernels inside the graph). */
 REEF_API uint64_t reef_launch_count(void);

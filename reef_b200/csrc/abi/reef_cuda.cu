@@ -3,6 +3,7 @@
 #include <cstring>
 #include <new>
 #include <string>
+#include <algorithm>
 #include <thread>
 #include <vector>
 
@@ -184,6 +185,50 @@ reef_status reef_write32_async(reef_stream_t s, reef_dptr_t ptr, uint32_t value)
         return REEF_OUT_OF_RANGE;
     }
     CK(cudaMemcpyAsync((void*)ptr, &g_flag_consts[value], 4, cudaMemcpyHostToDevice, (cudaStream_t)s));
+    return REEF_SUCC;
+}
+
+reef_status reef_probe_stream_latency(int iters, double* write_call_us, double* write_complete_us,
+                                      double* event_round_trip_us) {
+    using clk = std::chrono::steady_clock;
+    auto us = [](clk::time_point a, clk::time_point b) { return std::chrono::duration<double, std::micro>(b - a).count(); };
+    if (iters < 10) iters = 10;
+    cudaStream_t st;
+    int lo = 0, hi = 0;
+    CK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    CK(cudaStreamCreateWithPriority(&st, cudaStreamNonBlocking, hi));
+    void* flag = nullptr;
+    cudaEvent_t ev;
+    CK(cudaMalloc(&flag, 256));
+    CK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    std::vector<double> a, b, c;
+    reef_status rc = REEF_SUCC;
+    for (int i = 0; i < iters + iters / 10 && rc == REEF_SUCC; i++) {
+        auto t0 = clk::now();
+        rc = reef_write32_async((reef_stream_t)st, (reef_dptr_t)flag, (uint32_t)(i & 1));
+        auto t1 = clk::now();
+        cudaEventRecord(ev, st);
+        while (cudaEventQuery(ev) == cudaErrorNotReady) {}
+        auto t2 = clk::now();
+        cudaEventRecord(ev, st);
+        while (cudaEventQuery(ev) == cudaErrorNotReady) {}
+        auto t3 = clk::now();
+        if (i >= iters / 10) {
+            a.push_back(us(t0, t1));
+            b.push_back(us(t0, t2));
+            c.push_back(us(t2, t3));
+        }
+        while (us(t3, clk::now()) < 200.0) {}
+    }
+    cudaEventDestroy(ev);
+    cudaFree(flag);
+    cudaStreamDestroy(st);
+    if (rc != REEF_SUCC) return rc;
+    CK(cudaGetLastError());
+    auto med = [](std::vector<double>& v) { std::sort(v.begin(), v.end()); return v[v.size() / 2]; };
+    if (write_call_us) *write_call_us = med(a);
+    if (write_complete_us) *write_complete_us = med(b);
+    if (event_round_trip_us) *event_round_trip_us = med(c);
     return REEF_SUCC;
 }
 

@@ -84,11 +84,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) reef_attention_tc_kernel(const
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *s_tmem;
-    bool stop = BE && s_flags[0] != 0;
 
     // the QKV projection is the previous kernel of the stream: nothing of it may be read before this wait
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // best-effort flavour: the flag is looked at again behind the wait (a kernel queued behind a running one is
+    // resident early and made its entry poll before its predecessor finished, possibly before the flag went up)
+    bool stop = false;
+    if (BE) {
+        if (tid == 0 && *reinterpret_cast<const volatile int*>(P.preempt_flag) != 0) s_flags[0] = 1;
+        __syncthreads();
+        stop = s_flags[0] != 0;
+    }
 
     bool ok = true;
     if (!stop) {

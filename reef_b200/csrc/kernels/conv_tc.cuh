@@ -312,6 +312,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) reef_conv_tc_kernel(const __gri
             uint32_t par = 0;                      // parity of the "empty" phase awaited: ((i / NS) - 1) & 1
             int issued = abort0 ? 0 : first;       // K blocks whose loads are out
             bool stop = abort0;
+            // A second look at the preempt flag, behind the dependency wait: a best-effort kernel queued behind a
+            // running one is resident early (programmatic dependent launch) and made its entry poll long before its
+            // predecessor finished, possibly before the flag went up.  Its first loads are out (their barriers were
+            // armed for both operands, so the activation loads had to follow the weight loads); it issues no more, and
+            // the MMA thread only waits for those to land.
+            if (BE && !stop && *reinterpret_cast<const volatile int*>(P.preempt_flag) != 0) stop = true;
             for (int i = first; i < nkb && ok && !stop; i++) {
                 // loop-head poll of the preempt flag (every 4th K block): the load is issued before the wait for a
                 // free stage and looked at after it, so its latency hides behind the wait
