@@ -178,6 +178,9 @@ def main():
     ap.add_argument("--pad-target", type=float, default=None,
                     help="slowdown the padding controller may cost a real-time task (default: the scheduler's 0.06)")
     ap.add_argument("--mapped-flag", action="store_true", help="also measure preemption with the flag in mapped host memory")
+    ap.add_argument("--be-sms", type=int, default=int(os.environ.get("REEF_BE_SMS", "0")),
+                    help="SMs set aside for the best-effort streams (spatial partition; 0 = none, all streams share the GPU)")
+    ap.add_argument("--partition-flags", type=int, default=0, help="flags of reef_partition_create")
     ap.add_argument("--no-pin", action="store_true", help="do not pin the scheduler and client threads to CPU cores")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--profile-out", default="")
@@ -250,8 +253,12 @@ def main():
         s.set_input(mid, inputs[m][1], inputs[m][0])
         return mid
 
-    def make_sched(n_be_clients, rt=True, mapped_flag=False, stamps=False):
+    extra_cfg = {}
+
+    def make_sched(n_be_clients, rt=True, mapped_flag=False, stamps=False, partition=True):
         s = S(S.REEF, local_rank)
+        if partition and args.be_sms > 0:
+            extra_cfg["sm_partition_rt_be"] = list(s.set_sm_partition(args.be_sms, args.partition_flags))
         s.set_be_stream_cap(args.be_cap)
         if args.pad_target is not None:
             s.set_pad_slowdown_target(args.pad_target)
@@ -270,17 +277,23 @@ def main():
         return s, ids
 
     extra = {}
-    # ---- phase A: RT alone (closed loop, inputs resident) -------------------------------------
-    s, ids = make_sched(0)
+    # ---- phase A: RT alone (on the whole GPU: with a spatial partition the baselines of both kinds stay unpartitioned) (closed loop, inputs resident) -------------------------------------
+    s, ids = make_sched(0, partition=False)
     r = s.run_clients([dict(mid=ids["rt"], max_requests=n_req, warmup=n_warm, want_output=False)])[0]
     extra["rt_alone_p50_ms"] = pct(r["latencies_ms"], 50)
     extra["rt_alone_p99_ms"] = pct(r["latencies_ms"], 99)
     extra["rt_alone_inf_s"] = r["completed"] / r["elapsed_s"]
     s.shutdown(); s.close()
+    if args.be_sms > 0:
+        s, ids = make_sched(0)
+        r = s.run_clients([dict(mid=ids["rt"], max_requests=max(200, n_req // 4), warmup=n_warm, want_output=False)])[0]
+        extra["rt_alone_on_its_partition_p50_ms"] = pct(r["latencies_ms"], 50)
+        extra["rt_alone_on_its_partition_p99_ms"] = pct(r["latencies_ms"], 99)
+        s.shutdown(); s.close()
 
     # ---- phase B: BE alone ---------------------------------------------------------------------
     if n_be:
-        s, ids = make_sched(n_be, rt=False)
+        s, ids = make_sched(n_be, rt=False, partition=False)
         be_req = max(20, n_req // 8)
         rs = s.run_clients([dict(mid=m, max_requests=be_req, warmup=max(3, n_warm // 8), want_output=False)
                             for m in ids["be"]])
@@ -482,6 +495,7 @@ def main():
                            "clients": "1 RT + %d BE per GPU" % n_be,
                            "step": "%d back-to-back RT requests (%d timed after %d warm-up)" % (REQS_PER_STEP, n_req, n_warm),
                            "cpu_slice": list(cpu_slice) if cpu_slice else None,
+                           **extra_cfg,
                            "l2": "every client owns a weight replica; the replicas streamed per pass exceed the 126 MB L2"},
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes},
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,

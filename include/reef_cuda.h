@@ -271,6 +271,21 @@ REEF_API reef_status reef_flag_alloc_mapped(uint32_t** host_ptr, reef_dptr_t* de
 REEF_API reef_status reef_flag_free_mapped(uint32_t* host_ptr);
 REEF_API reef_status reef_flag_set(uint32_t* host_ptr, uint32_t value);
 
+/* Spatial partition of the current device's SMs (CUDA green contexts): `be_sms` SMs are set aside for best-effort
+ * streams and the rest for real-time streams, so that best-effort blocks never share an SM with real-time blocks
+ * (the reference's dynamic kernel padding partitions compute units inside one grid, `cu_partition`,
+ * resource/mocked_kernel/mocked_kernel.trans.cu:112-186; here the hardware block scheduler keeps the two apart).
+ * The driver rounds SM counts to its granularity (8 on this architecture): reef_partition_info reports what was
+ * provisioned.  flags: bit 0 = the clean group goes to the real-time side (best-effort gets the remainder) instead
+ * of the other way round; bit 1 = ask for groups that keep the largest cluster size schedulable.  (The scheduler
+ * knows a third bit, 4: only the best-effort side is confined and the real-time stream keeps every SM.)
+ * Streams of a partition are ordinary streams in every other respect (kernels, graphs, events, copies). */
+typedef struct reef_partition_s* reef_partition_t;
+REEF_API reef_status reef_partition_create(int be_sms, int flags, reef_partition_t* p);
+REEF_API reef_status reef_partition_info(reef_partition_t p, int* rt_sms, int* be_sms);
+REEF_API reef_status reef_partition_stream_create(reef_partition_t p, int best_effort, int high_priority, reef_stream_t* s);
+REEF_API reef_status reef_partition_destroy(reef_partition_t p);
+
 /* Measurement helper: what the host sees of the device through a stream.  `iters` times (spaced 200 us apart, after
  * iters/10 untimed rounds) it (a) issues reef_write32_async on an idle high-priority stream, (b) records an event
  * behind it and spins on reef_event_query until it completes, (c) records a bare event and spins again.  Medians in

@@ -131,6 +131,9 @@ REEF_HOST_API int reef_sched_set_wait_sync(reef_scheduler_t s, int value);
 REEF_HOST_API int reef_sched_set_be_stream_cap(reef_scheduler_t s, int value);
 /* Preempt flag in pinned host memory raised by a host store instead of a stream write (before the first load_model). */
 REEF_HOST_API int reef_sched_use_mapped_flag(reef_scheduler_t s);
+/* Spatial partition of the SMs between the real-time stream and the best-effort streams (before any queue is
+ * created): see reef_partition_create in reef_cuda.h. */
+REEF_HOST_API int reef_sched_set_sm_partition(reef_scheduler_t s, int be_sms, int flags, int* rt_sms, int* be_sms_out);
 /* Device-clock preemption stamps on/off (implies wait_sync). */
 REEF_HOST_API int reef_sched_set_device_stamps(reef_scheduler_t s, int on);
 /* Dynamic-kernel-padding controller: padded real-time tasks may take (1 + value) x their latency alone; 0 = no limit. */

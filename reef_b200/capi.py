@@ -398,6 +398,14 @@ class REEFScheduler:
     def use_mapped_flag(self):
         _check(self._lib.reef_sched_use_mapped_flag(self._h), "use_mapped_flag", self._err())
 
+    def set_sm_partition(self, be_sms: int, flags: int = 0):
+        """Best-effort streams get ``be_sms`` SMs of their own, the real-time stream the rest (before any queue is
+        created).  Returns (real-time SMs, best-effort SMs) as provisioned by the driver."""
+        a, b = C.c_int(), C.c_int()
+        _check(self._lib.reef_sched_set_sm_partition(self._h, C.c_int(be_sms), C.c_int(flags), C.byref(a), C.byref(b)),
+               "set_sm_partition", self._err())
+        return a.value, b.value
+
     def set_device_stamps(self, on: bool):
         _check(self._lib.reef_sched_set_device_stamps(self._h, C.c_int(int(on))), "set_device_stamps", self._err())
 

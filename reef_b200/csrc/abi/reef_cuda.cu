@@ -1,4 +1,5 @@
 // C-ABI device layer (see include/reef_cuda.h for the reference symbols each entry point replaces).
+#include <cuda.h>
 #include <chrono>
 #include <cstring>
 #include <new>
@@ -185,6 +186,140 @@ reef_status reef_write32_async(reef_stream_t s, reef_dptr_t ptr, uint32_t value)
         return REEF_OUT_OF_RANGE;
     }
     CK(cudaMemcpyAsync((void*)ptr, &g_flag_consts[value], 4, cudaMemcpyHostToDevice, (cudaStream_t)s));
+    return REEF_SUCC;
+}
+
+// ---- SM partition (green contexts) ------------------------------------------------------------------------------
+// The driver entry points are looked up at run time (the library links the runtime only).
+struct reef_partition_s {
+    CUgreenCtx ctx[2] = {nullptr, nullptr};   // [0] real-time side, [1] best-effort side
+    int sms[2] = {0, 0};
+};
+namespace {
+typedef CUresult (*fn_get_dev_resource)(CUdevice, CUdevResource*, CUdevResourceType);
+typedef CUresult (*fn_split_by_count)(CUdevResource*, unsigned int*, const CUdevResource*, CUdevResource*, unsigned int, unsigned int);
+typedef CUresult (*fn_generate_desc)(CUdevResourceDesc*, CUdevResource*, unsigned int);
+typedef CUresult (*fn_green_create)(CUgreenCtx*, CUdevResourceDesc, CUdevice, unsigned int);
+typedef CUresult (*fn_green_destroy)(CUgreenCtx);
+typedef CUresult (*fn_green_stream)(CUstream*, CUgreenCtx, unsigned int, int);
+typedef CUresult (*fn_device_get)(CUdevice*, int);
+void* driver_fn(const char* name) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    return fn;
+}
+reef_status cu_fail(const char* what, CUresult r) {
+    set_error(std::string(what) + " failed with CUresult " + std::to_string((int)r));
+    return REEF_FAIL;
+}
+}  // namespace
+
+reef_status reef_partition_create(int be_sms, int flags, reef_partition_t* out) {
+    auto get_res = (fn_get_dev_resource)driver_fn("cuDeviceGetDevResource");
+    auto split = (fn_split_by_count)driver_fn("cuDevSmResourceSplitByCount");
+    auto gen = (fn_generate_desc)driver_fn("cuDevResourceGenerateDesc");
+    auto create = (fn_green_create)driver_fn("cuGreenCtxCreate");
+    auto dev_get = (fn_device_get)driver_fn("cuDeviceGet");
+    if (!get_res || !split || !gen || !create || !dev_get) {
+        set_error("reef_partition_create: this driver has no green contexts");
+        return REEF_FAIL;
+    }
+    int ordinal = 0;
+    CK(cudaGetDevice(&ordinal));
+    CK(cudaFree(0));
+    CUdevice dev;
+    CUresult r = dev_get(&dev, ordinal);
+    if (r != CUDA_SUCCESS) return cu_fail("cuDeviceGet", r);
+    CUdevResource all;
+    r = get_res(dev, &all, CU_DEV_RESOURCE_TYPE_SM);
+    if (r != CUDA_SUCCESS) return cu_fail("cuDeviceGetDevResource", r);
+    const int total = (int)all.sm.smCount;
+    if (be_sms < 1 || be_sms >= total) {
+        set_error("reef_partition_create: best-effort SM count outside 1.." + std::to_string(total - 1));
+        return REEF_OUT_OF_RANGE;
+    }
+    if (flags & 8) {
+        // both sides are made of whole groups of 8 SMs (the driver's granularity here): the best-effort side takes the
+        // first ceil(be_sms / 8) groups, the real-time side all the others; the remainder of the split is left unused
+        CUdevResource groups[32], rest8;
+        unsigned int ng = 32;
+        r = split(groups, &ng, &all, &rest8, (flags & 2) ? CU_DEV_SM_RESOURCE_SPLIT_MAX_POTENTIAL_CLUSTER_SIZE : 0u, 8u);
+        if (r != CUDA_SUCCESS) return cu_fail("cuDevSmResourceSplitByCount(8)", r);
+        const unsigned int nbe = (unsigned int)((be_sms + 7) / 8);
+        if (nbe >= ng) {
+            set_error("reef_partition_create: no group left for the real-time side");
+            return REEF_OUT_OF_RANGE;
+        }
+        reef_partition_s* p8 = new (std::nothrow) reef_partition_s();
+        if (!p8) return REEF_FAIL;
+        CUdevResource* first[2] = {groups + nbe, groups};
+        const unsigned int cnt[2] = {ng - nbe, nbe};
+        for (int i = 0; i < 2; i++) {
+            CUdevResourceDesc desc;
+            r = gen(&desc, first[i], cnt[i]);
+            if (r == CUDA_SUCCESS) r = create(&p8->ctx[i], desc, dev, CU_GREEN_CTX_DEFAULT_STREAM);
+            if (r != CUDA_SUCCESS) {
+                reef_partition_destroy(p8);
+                return cu_fail("cuGreenCtxCreate (groups of 8)", r);
+            }
+            for (unsigned int g = 0; g < cnt[i]; g++) p8->sms[i] += (int)first[i][g].sm.smCount;
+        }
+        *out = p8;
+        return REEF_SUCC;
+    }
+    const bool group_is_rt = (flags & 1) != 0;
+    const unsigned int use = (flags & 2) ? CU_DEV_SM_RESOURCE_SPLIT_MAX_POTENTIAL_CLUSTER_SIZE : 0u;
+    CUdevResource group, rest;
+    unsigned int n = 1;
+    r = split(&group, &n, &all, &rest, use, (unsigned int)(group_is_rt ? total - be_sms : be_sms));
+    if (r != CUDA_SUCCESS || n != 1) return cu_fail("cuDevSmResourceSplitByCount", r);
+    if (rest.sm.smCount == 0) {
+        set_error("reef_partition_create: the split left no SMs for the other side");
+        return REEF_OUT_OF_RANGE;
+    }
+    reef_partition_s* p = new (std::nothrow) reef_partition_s();
+    if (!p) return REEF_FAIL;
+    CUdevResource* side[2] = {group_is_rt ? &group : &rest, group_is_rt ? &rest : &group};
+    for (int i = 0; i < 2; i++) {
+        CUdevResourceDesc desc;
+        r = gen(&desc, side[i], 1);
+        if (r == CUDA_SUCCESS) r = create(&p->ctx[i], desc, dev, CU_GREEN_CTX_DEFAULT_STREAM);
+        if (r != CUDA_SUCCESS) {
+            reef_partition_destroy(p);
+            return cu_fail("cuGreenCtxCreate", r);
+        }
+        p->sms[i] = (int)side[i]->sm.smCount;
+    }
+    *out = p;
+    return REEF_SUCC;
+}
+reef_status reef_partition_info(reef_partition_t p, int* rt_sms, int* be_sms) {
+    if (!p) return REEF_FAIL;
+    if (rt_sms) *rt_sms = p->sms[0];
+    if (be_sms) *be_sms = p->sms[1];
+    return REEF_SUCC;
+}
+reef_status reef_partition_stream_create(reef_partition_t p, int best_effort, int high_priority, reef_stream_t* s) {
+    auto mk = (fn_green_stream)driver_fn("cuGreenCtxStreamCreate");
+    if (!p || !mk) return REEF_FAIL;
+    int lo = 0, hi = 0;
+    CK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    CUstream st = nullptr;
+    CUresult r = mk(&st, p->ctx[best_effort ? 1 : 0], CU_STREAM_NON_BLOCKING, high_priority ? hi : lo);
+    if (r != CUDA_SUCCESS) return cu_fail("cuGreenCtxStreamCreate", r);
+    *s = (reef_stream_t)st;
+    return REEF_SUCC;
+}
+reef_status reef_partition_destroy(reef_partition_t p) {
+    if (!p) return REEF_SUCC;
+    auto destroy = (fn_green_destroy)driver_fn("cuGreenCtxDestroy");
+    for (int i = 0; i < 2; i++)
+        if (p->ctx[i] && destroy) destroy(p->ctx[i]);
+    delete p;
     return REEF_SUCC;
 }
 

@@ -345,6 +345,9 @@ int reef_sched_inject_launch_failures(reef_scheduler_t s, uint32_t mid, int n) {
 int reef_sched_set_wait_sync(reef_scheduler_t s, int v) { s->sched->set_wait_sync(v != 0); return Succ; }
 int reef_sched_set_be_stream_cap(reef_scheduler_t s, int v) { s->sched->set_be_stream_cap(v); return Succ; }
 int reef_sched_use_mapped_flag(reef_scheduler_t s) { return s->sched->use_mapped_flag(); }
+int reef_sched_set_sm_partition(reef_scheduler_t s, int be_sms, int flags, int* rt_sms, int* be_sms_out) {
+    return s->sched->set_sm_partition(be_sms, flags, rt_sms, be_sms_out);
+}
 int reef_sched_set_device_stamps(reef_scheduler_t s, int on) { return s->sched->set_device_stamps(on != 0); }
 int reef_sched_set_pad_slowdown_target(reef_scheduler_t s, double v) { s->sched->set_pad_slowdown_target(v); return Succ; }
 int reef_sched_set_cpu_slice(reef_scheduler_t s, int first_cpu, int n_cpus) { s->sched->set_cpu_slice(first_cpu, n_cpus); return Succ; }

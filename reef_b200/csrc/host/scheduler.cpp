@@ -96,6 +96,7 @@ REEFScheduler::~REEFScheduler() {
     if (rt_queue && rt_queue->stream) reef_stream_destroy(rt_queue->stream);
     if (preempt_stream) reef_stream_destroy(preempt_stream);
     if (device_stamps) reef_preempt_stamps_arm(0);
+    if (partition) reef_partition_destroy(partition);
     if (mapped_flag_host) reef_flag_free_mapped(mapped_flag_host);
     else if (preempt_flag) reef_free(preempt_flag);
 }
@@ -109,6 +110,19 @@ Status REEFScheduler::use_mapped_flag() {
     if (preempt_flag) reef_free(preempt_flag);
     mapped_flag_host = h;
     preempt_flag = d;
+    return Status::Succ;
+}
+
+Status REEFScheduler::set_sm_partition(int be_sms, int flags, int* rt_sms_out, int* be_sms_out) {
+    if (partition != nullptr || rt_queue.get() != nullptr || be_queue_cnt.load() != 0) return Status::Fail;   // streams exist already
+    GPU_RETURN_STATUS(reef_gpu_init(device));
+    if (reef_partition_create(be_sms, flags, &partition) != REEF_SUCC) {
+        err_ = reef_last_error();
+        partition = nullptr;
+        return Status::Fail;
+    }
+    reef_partition_info(partition, rt_sms_out, be_sms_out);
+    partition_rt_whole_gpu = (flags & 4) != 0;
     return Status::Succ;
 }
 
@@ -129,7 +143,11 @@ void REEFScheduler::write_flag(uint32_t v) {
 Status REEFScheduler::create_task_queue(std::shared_ptr<TaskQueue>& ret, bool rt) {
     executor::GPUStream_t stream;
     GPU_RETURN_STATUS(reef_gpu_init(device));
-    GPU_RETURN_STATUS(reef_stream_create(&stream, rt ? 1 : 0));
+    if (partition && !(rt && partition_rt_whole_gpu)) {
+        GPU_RETURN_STATUS(reef_partition_stream_create(partition, rt ? 0 : 1, rt ? 1 : 0, &stream));
+    } else {
+        GPU_RETURN_STATUS(reef_stream_create(&stream, rt ? 1 : 0));
+    }
     ret = std::make_shared<TaskQueue>();
     ret->stream = stream;
     return Status::Succ;

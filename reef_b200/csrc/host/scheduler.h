@@ -102,6 +102,9 @@ public:
     // reference: hip_impl.h:20).  With the mapped flag it lives in pinned host memory instead and is raised by a plain
     // host store; every device-side poll then crosses PCIe.  Call before the first load_model.
     Status use_mapped_flag();
+    // Spatial partition (before any queue exists): best-effort streams get `be_sms` SMs of their own, the real-time
+    // stream the rest; flags as reef_partition_create.  rt_sms / be_sms report what the driver provisioned.
+    Status set_sm_partition(int be_sms, int flags, int* rt_sms_out, int* be_sms_out);
     // Records, on the device's own clock, when the flag was first seen by a best-effort block and when the last one
     // left (measurement; read once per preemption after the drain, so it implies wait_sync).
     Status set_device_stamps(bool on);
@@ -276,6 +279,8 @@ private:
     uint64_t preempt_count, preempt_latency_sum, preempt_latency_max;
     uint64_t drain_count = 0, drain_ns_sum = 0, drain_ns_max = 0;
     uint64_t dev_count = 0, dev_ns_sum = 0, dev_ns_max = 0;
+    bool partition_rt_whole_gpu = false;    // flags bit 2: only the best-effort side is confined, the real-time stream keeps every SM
+    reef_partition_t partition = nullptr;   // non-null: queues take their streams from the two sides of an SM partition
     uint32_t* mapped_flag_host = nullptr;   // non-null: the flag is pinned host memory raised by a host store
     bool device_stamps = false;
     int cpu_first = -1, cpu_count = 0;

@@ -255,3 +255,27 @@ def test_failed_launch_and_device_error_end_in_a_failed_task(gen):
         assert res[0]["failed"] and res[0]["completed"] == 0
         s.shutdown()
         s.close()
+
+
+def test_scheduler_sm_partition_keeps_results(gen):
+    """Best-effort streams confined to SMs of their own (a green-context partition; the real-time stream keeps the
+    whole GPU with flag 4, or takes the other side of the split with flag 0): outputs are unchanged."""
+    base = gen("resnet18")
+    x = seeded_input(3 * 224 * 224, seed=11)
+    want = _oracle_out(base, x)
+    tol = tol_for(base)
+    for flags in (4, 0):
+        s = S(S.REEF)
+        rt_sms, be_sms = s.set_sm_partition(32, flags)
+        assert be_sms >= 8 and rt_sms >= 8 and rt_sms + be_sms <= 148
+        s.run()
+        rt = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
+        be = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
+        s.bind_model_queue(s.create_queue(S.RealTimeQueue), rt)
+        s.bind_model_queue(s.create_queue(S.BestEffortQueue), be)
+        res = s.run_clients([dict(mid=rt, max_requests=40, warmup=5, input=x), dict(mid=be, max_requests=0, input=x)])
+        assert rel_err(res[0]["output"], want) < tol
+        assert res[1]["completed"] > 0 and rel_err(res[1]["output"], want) < tol
+        assert capi.device_error() == 0
+        s.shutdown()
+        s.close()
