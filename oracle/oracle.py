@@ -68,6 +68,22 @@ def set_threads(n: int) -> None:
     lib().reef_oracle_set_threads(int(n))
 
 
+def im2col_nchw(x, bias, a) -> np.ndarray:
+    """[ho*wo][kp] im2col matrix of the planar tensor x [c][hi][wi] + bias[c] (numpy, fp32; attrs of the kernel name)."""
+    c, hi, wi, kh, kw, sh, sw, ph, pw, kp = (a[k] for k in ("c", "hi", "wi", "kh", "kw", "sh", "sw", "ph", "pw", "kp"))
+    ho, wo = (hi + 2 * ph - kh) // sh + 1, (wi + 2 * pw - kw) // sw + 1
+    planar = np.asarray(x, np.float32).reshape(c, hi, wi) + np.asarray(bias, np.float32).reshape(c, 1, 1)
+    padded = np.zeros((c, hi + 2 * ph, wi + 2 * pw), np.float32)
+    padded[:, ph:ph + hi, pw:pw + wi] = planar
+    out = np.zeros((ho, wo, kp), np.float32)
+    for ky in range(kh):
+        for kx in range(kw):
+            tap = padded[:, ky:ky + (ho - 1) * sh + 1:sh, kx:kx + (wo - 1) * sw + 1:sw]   # [c][ho][wo]
+            k0 = (ky * kw + kx) * c
+            out[:, :, k0:k0 + c] = tap.transpose(1, 2, 0)
+    return out.reshape(ho * wo, kp)
+
+
 def run_kernel(name: str, bufs: list, acc64: bool = False) -> None:
     """Execute one kernel of the schedule on numpy buffers (positional, like the json)."""
     L = lib()
@@ -87,6 +103,11 @@ def run_kernel(name: str, bufs: list, acc64: bool = False) -> None:
         out = bufs[0].reshape(hw, 4)
         out[:] = 0.0
         out[:, :c] = planar.reshape(c, hw).T
+    elif op == "reef_im2col_nchw":
+        # the planar input + per-channel bias (the reference's fused_add), gathered into the im2col matrix of the first
+        # convolution: bufs = out [ho*wo][kp], in [c][hi][wi], bias [c]; k = (ky*kw + kx)*c + channel, zero beyond
+        # kh*kw*c and where a tap falls into the padding
+        bufs[0][:] = im2col_nchw(bufs[1], bufs[2], a).reshape(-1)
     elif op == "fused_add_nn_relu":
         L.reef_oracle_fused_add_nn_relu(_p(bufs[0]), _p(bufs[1]), _p(bufs[2]), i32(a["c"]), i32(a["n"]),
                                         i32(a.get("ics", a["c"])), i32(a.get("ioff", 0)))

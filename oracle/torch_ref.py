@@ -91,6 +91,17 @@ class TorchExecutor:
                 y[:, :a["c"]] = x.T
                 t[args[0]][:] = y.reshape(-1)
             return f
+        if op == "reef_im2col_nchw":
+            def f():
+                c, hi, wi, kh, kw, kp = a["c"], a["hi"], a["wi"], a["kh"], a["kw"], a["kp"]
+                x = t[args[1]].view(1, c, hi, wi) + t[args[2]].view(1, c, 1, 1)
+                cols = F.unfold(x, (kh, kw), padding=(a["ph"], a["pw"]), stride=(a["sh"], a["sw"]))[0]   # [c*kh*kw][P], (c, ky, kx) order
+                P = cols.shape[1]
+                cols = cols.view(c, kh * kw, P).permute(2, 1, 0).reshape(P, kh * kw * c)                   # -> (ky, kx, c) order
+                y = torch.zeros(P, kp, dtype=x.dtype)
+                y[:, :kh * kw * c] = cols
+                t[args[0]][:] = y.reshape(-1)
+            return f
         if op == "fused_add_nn_relu":
             ics, ioff = a.get("ics", a["c"]), a.get("ioff", 0)
 

@@ -128,6 +128,26 @@ static int build_spec(const std::string& name, KernelSpec* s) {
         s->bytes = 4.0 * ((double)p.c * p.n + 4.0 * p.n + p.c);
         return REEF_SUCC;
     }
+    if (op == "reef_im2col_nchw") {
+        ConvP& p = t.p.conv;
+        if (!a.need("c", &p.ci) || !a.need("hi", &p.hi) || !a.need("wi", &p.wi) || !a.need("kh", &p.kh) ||
+            !a.need("kw", &p.kw) || !a.need("sh", &p.sh) || !a.need("sw", &p.sw) || !a.need("ph", &p.ph) ||
+            !a.need("pw", &p.pw) || !a.need("kp", &p.ocs))
+            goto bad;
+        if (p.ci < 1 || p.kh < 1 || p.kw < 1 || p.sh < 1 || p.sw < 1 || p.ph < 0 || p.pw < 0) goto bad;
+        p.ho = (p.hi + 2 * p.ph - p.kh) / p.sh + 1;
+        p.wo = (p.wi + 2 * p.pw - p.kw) / p.sw + 1;
+        p.ktot = p.kh * p.kw * p.ci;
+        p.ptot = p.ho * p.wo;
+        if (p.ho < 1 || p.wo < 1 || (p.ocs & 3) || p.ocs < p.ktot || p.ocs > kIm2colMaxKp || (double)p.ptot * p.ocs > 5e8) goto bad;
+        p.nchw = 1;
+        t.family = F_IM2COL_NCHW;
+        s->dyn_smem = (uint32_t)(p.ocs * 12);
+        t.nblocks = ceil_div(p.ptot * (p.ocs / 4), kIm2colPerBlock);
+        s->nargs = 3;
+        s->bytes = 4.0 * ((double)p.ci * p.hi * p.wi + (double)p.ptot * p.ocs + p.ci);
+        return REEF_SUCC;
+    }
     if (op == "fused_add_nn_relu") {
         EltP& p = t.p.elt;
         if (!a.need("c", &p.c) || !a.need("n", &p.n)) goto bad;
@@ -398,6 +418,11 @@ static void fill_arg_bytes(KernelSpec* s) {
         case F_NCHW_TO_NHWC4:
             b[0] = f4(4.0 * t.p.elt.n); b[1] = f4((double)t.p.elt.c * t.p.elt.n); b[2] = f4(t.p.elt.c);
             break;
+        case F_IM2COL_NCHW:
+            b[0] = f4((double)t.p.conv.ptot * t.p.conv.ocs);
+            b[1] = f4((double)t.p.conv.ci * t.p.conv.hi * t.p.conv.wi);
+            b[2] = f4(t.p.conv.ci);
+            break;
         case F_BIAS_RELU:
             b[0] = f4((double)t.p.elt.c * t.p.elt.n);
             b[1] = f4((double)(t.p.elt.n - 1) * t.p.elt.ics + t.p.elt.ioff + t.p.elt.c);
@@ -489,6 +514,7 @@ __device__ __forceinline__ bool run_body(const KTask& t, int vb, unsigned char* 
     if (F == F_MOCK_MUL) return body_mock<true>(t, vb, smem, flag);
     if (F == F_FUSED_ADD_NCHW) return body_fused_add_nchw(t, vb, smem, flag);
     if (F == F_NCHW_TO_NHWC4) return body_nchw_to_nhwc4(t, vb, smem, flag);
+    if (F == F_IM2COL_NCHW) return body_im2col_nchw(t, vb, smem, flag);
     if (F == F_BIAS_RELU) return body_bias_relu(t, vb, smem, flag);
     if (F == F_CONV_SIMT) return body_conv_simt(t, vb, smem, flag);
     if (F == F_MAX_POOL) return body_pool<true>(t, vb, smem, flag);
@@ -509,6 +535,7 @@ __device__ __forceinline__ bool run_any(const KTask& t, int vb, unsigned char* s
         case F_MOCK_MUL: return run_body<F_MOCK_MUL>(t, vb, smem, flag);
         case F_FUSED_ADD_NCHW: return run_body<F_FUSED_ADD_NCHW>(t, vb, smem, flag);
         case F_NCHW_TO_NHWC4: return run_body<F_NCHW_TO_NHWC4>(t, vb, smem, flag);
+        case F_IM2COL_NCHW: return run_body<F_IM2COL_NCHW>(t, vb, smem, flag);
         case F_BIAS_RELU: return run_body<F_BIAS_RELU>(t, vb, smem, flag);
         case F_CONV_SIMT: return run_body<F_CONV_SIMT>(t, vb, smem, flag);
         case F_MAX_POOL: return run_body<F_MAX_POOL>(t, vb, smem, flag);
@@ -723,7 +750,7 @@ void add_launches(unsigned long long n) { g_launches.fetch_add(n, std::memory_or
 #define FOR_EACH_FAMILY(X)                                                                      \
     X(F_MOCK_ADD) X(F_MOCK_MUL) X(F_FUSED_ADD_NCHW) X(F_BIAS_RELU) X(F_CONV_SIMT) X(F_MAX_POOL) \
     X(F_AVG_POOL) X(F_GLOBAL_AVG_POOL) X(F_COPY) X(F_DENSE) X(F_SOFTMAX) X(F_EMBEDDING) X(F_LAYERNORM) X(F_ATTENTION) \
-    X(F_NCHW_TO_NHWC4)
+    X(F_NCHW_TO_NHWC4) X(F_IM2COL_NCHW)
 
 static const void* plain_fn(int family) {
     switch (family) {

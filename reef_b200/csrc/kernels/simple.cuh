@@ -84,6 +84,69 @@ __device__ __forceinline__ bool body_nchw_to_nhwc4(const KTask& t, int vb, unsig
     return true;
 }
 
+// ---- model input for the first convolution on the tensor cores: planar NCHW (+ per-channel bias) -> the im2col
+// matrix out[pixel][kp], k = (ky * kw + kx) * c + channel for k < kh*kw*c, zero beyond (kp = K rounded up to whole
+// 32-channel K blocks) and zero where the tap falls into the padding (the bias is added to real input values only:
+// the reference adds it with fused_add on the planar tensor, resource/resnet152/resnet152.cu:771-773, and the
+// convolution pads the sum with zeros).  Values are rounded to the nearest TF32.  The first convolution is then a
+// 1x1 convolution (X W^T) over kp "channels" with the weights flattened in the same k order: 7x7x3 = 147 of 160
+// operand columns carry data, where a 4-channel channels-last input left 7/8 of every K block empty.
+// args: out [ho*wo][kp], in [c][hi][wi], bias [c].  A thread writes four consecutive k of a pixel per step.
+constexpr int kIm2colPerBlock = 1024;   // 128-bit items per logical block
+constexpr int kIm2colMaxKp = 512;       // columns of the matrix (the lookup table lives in shared memory)
+__device__ __forceinline__ bool body_im2col_nchw(const KTask& t, int vb, unsigned char* smem_raw, const int*) {
+    const ConvP& p = t.p.conv;
+    float* out = (float*)t.a[0];
+    const float* in = (const float*)t.a[1];
+    const float* bias = (const float*)t.a[2];
+    const int kp = p.ocs, kp4 = kp >> 2;
+    const int total = p.ptot * kp4;
+    // per column k: offset of its tap inside the input plane stack, the tap's (dy, dx), the channel's bias — the
+    // divisions that take k apart are done once per block here, not once per element
+    int* s_off = reinterpret_cast<int*>(smem_raw);            // (ch * hi + ky) * wi + kx, or -1 beyond K
+    int* s_dyx = s_off + kp;                                   // ky << 16 | kx
+    float* s_bias = reinterpret_cast<float*>(s_dyx + kp);
+    __syncthreads();   // a persistent caller may still be reading the previous logical block's table
+    for (int k = threadIdx.x; k < kp; k += kThreads) {
+        int off = -1, dyx = 0;
+        float b = 0.f;
+        if (k < p.ktot) {
+            const int tap = k / p.ci, ch = k - tap * p.ci;
+            const int ky = tap / p.kw, kx = tap - ky * p.kw;
+            off = (ch * p.hi + ky) * p.wi + kx;
+            dyx = (ky << 16) | kx;
+            b = bias[ch];
+        }
+        s_off[k] = off;
+        s_dyx[k] = dyx;
+        s_bias[k] = b;
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (int it = 0; it < kIm2colPerBlock / kThreads; it++) {
+        const int item = vb * kIm2colPerBlock + it * kThreads + (int)threadIdx.x;
+        if (item >= total) break;
+        const int pix = item / kp4, q = item - pix * kp4;
+        const int oy = pix / p.wo, ox = pix - oy * p.wo;
+        const int y0 = oy * p.sh - p.ph, x0 = ox * p.sw - p.pw;
+        const int base = y0 * p.wi + x0;
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int k = q * 4 + e;
+            const int off = s_off[k], dyx = s_dyx[k];
+            const int iy = y0 + (dyx >> 16), ix = x0 + (dyx & 0xffff);
+            float x = 0.f;
+            if (off >= 0 && iy >= 0 && iy < p.hi && ix >= 0 && ix < p.wi) x = __ldg(in + base + off) + s_bias[k];
+            uint32_t u;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+            v[e] = __uint_as_float(u);
+        }
+        *reinterpret_cast<float4*>(out + (size_t)item * 4) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    return true;
+}
+
 // ---- fused_add_nn_relu, channels-last (reference: resource/resnet152/resnet152.cu:4056-4066) ---
 // args: out, in, bias.  out[p][c] = max(in[p*ics+ioff+c] + bias[c], 0); c, ics, ioff multiples of 4.
 __device__ __forceinline__ bool body_bias_relu(const KTask& t, int vb, unsigned char*, const int*) {

@@ -33,6 +33,7 @@ enum Family : int {
     F_LAYERNORM,
     F_ATTENTION,
     F_NCHW_TO_NHWC4,
+    F_IM2COL_NCHW,
     F_COUNT,
     // families with their own __global__ kernel (not hosted by the 256-thread logical-block wrappers)
     F_CONV_TC = 100,

@@ -68,6 +68,8 @@ def generate(model: str, out_root: str | None = None, *, force: bool = False, va
     schedule uses the tcgen05 TF32 convolution wherever the registry supports the shape."""
     if variant == "_fp32":
         kw.setdefault("conv_impl", "simt")
+    elif variant == "_simtstem":
+        kw.setdefault("conv_impl", "simt_stem")   # tensor-core schedule with the first convolution left on CUDA cores
     from .. import capi
     out_root = out_root or DEFAULT_DIR
     name = model + variant

@@ -56,7 +56,11 @@ class Builder:
         # input).  Measured slower than the CUDA-core stem (ResNet-152 replay 1.04 -> 1.09 ms): with 4 real
         # channels per 32-channel K block the operand tiles are 7/8 zero fill, so it is not the default.
         self.tc_stem = conv_impl == "tc_stem"
-        if self.tc_stem:
+        # the first convolution by default: an im2col gather of the planar input (reef_im2col_nchw) followed by a 1x1
+        # tensor-core convolution over the flattened taps; "simt_stem" keeps the reference's planar convolution on CUDA
+        # cores for the first layer only (the schedule this one is measured against)
+        self.im2col_stem = conv_impl in ("auto", "tc")
+        if self.tc_stem or conv_impl == "simt_stem":
             self.conv_impl = "auto"
 
     # ---- randomness ----------------------------------------------------
@@ -122,6 +126,22 @@ class Builder:
             w4[..., :c] = wgt
             x = self.input_nhwc4(data_idx, c, h, w, input_bias)
             return self.conv(x, co, k, stride, pad, weight=w4, real_ci=c, **kw)
+        if self.im2col_stem:
+            ktot = kh * kw_ * c
+            kp = -(-ktot // 32) * 32
+            ho, wo = (h + 2 * ph - kh) // sh + 1, (w + 2 * ph - kw_) // sh + 1
+            attrs1 = dict(ci=kp, hi=ho, wi=wo, co=co, kh=1, kw=1, sh=1, sw=1, ph=0, pw=0, cr=ktot)
+            col = dict(c=c, hi=h, wi=w, kh=kh, kw=kw_, sh=sh, sw=sh, ph=ph, pw=ph, kp=kp)
+            if self.pick_conv_impl(op, attrs1) == 1 and self.has_kernel(kname("reef_im2col_nchw", **col)):
+                in_scale = kw.pop("in_scale", None)
+                if in_scale is not None:
+                    wgt = wgt * np.asarray(in_scale, np.float32)[None, None, None, :]
+                wcol = np.zeros((co, 1, 1, kp), np.float32)
+                wcol[:, 0, 0, :ktot] = wgt.reshape(co, ktot)      # OHWI flattened: k = (ky * kw + kx) * c + channel
+                x = Tensor(self.g.temp(ho * wo * kp), ho, wo, kp)
+                b = self.g.param(np.zeros(c, np.float32) if input_bias is None else np.asarray(input_bias, np.float32))
+                self.g.kernel(kname("reef_im2col_nchw", **col), [x.idx, data_idx, b])
+                return self.conv(x, co, 1, 1, 0, weight=wcol, real_ci=ktot, **kw)
         if input_bias is not None:
             x = self.input_bias_nchw(data_idx, c, h, w, input_bias)
         else:
@@ -201,6 +221,15 @@ class Builder:
         if preact_bias is not None:
             return out, self.bias_relu(out, preact_bias)
         return out
+
+    @staticmethod
+    def has_kernel(name: str) -> bool:
+        from .. import capi
+        try:
+            capi.kernel_plan(name)
+            return True
+        except capi.ReefError:
+            return False
 
     def pick_conv_impl(self, op, attrs) -> int:
         """0 = fp32 implicit GEMM on CUDA cores; 1 = tcgen05 TF32 implicit GEMM (fp32 accumulate).

@@ -152,6 +152,69 @@ def test_tensor_core_stem_variant(tmp_path):
         assert np.array_equal(e.get_output(), raw), f
 
 
+IM2COL_CASES = [  # c, hi, wi, kh, kw, sh, sw, ph, pw, kp
+    (3, 64, 64, 7, 7, 2, 2, 3, 3, 160), (3, 33, 47, 3, 3, 1, 1, 1, 1, 32), (3, 41, 41, 3, 3, 2, 2, 0, 0, 32),
+    (1, 20, 24, 5, 3, 1, 2, 2, 0, 32), (4, 17, 17, 3, 3, 3, 3, 1, 1, 64), (3, 8, 8, 7, 7, 1, 1, 3, 3, 148)]
+
+
+@pytest.mark.parametrize("case", IM2COL_CASES, ids=["c%d_%dx%d_k%dx%d_s%d%d_p%d%d_kp%d" % c for c in IM2COL_CASES])
+def test_im2col_kernel_matches_oracle(tmp_path, case):
+    """reef_im2col_nchw (planar input + bias -> im2col matrix, rounded to TF32): against the oracle's gather, with
+    ragged borders, strides, padding wider than a tap's reach and columns beyond K; all launch flavours bit-identical."""
+    c, hi, wi, kh, kw, sh, sw, ph, pw, kp = case
+    ho, wo = (hi + 2 * ph - kh) // sh + 1, (wi + 2 * pw - kw) // sw + 1
+    name = f"reef_im2col_nchw__c{c}_hi{hi}_wi{wi}_kh{kh}_kw{kw}_sh{sh}_sw{sw}_ph{ph}_pw{pw}_kp{kp}"
+    base, inputs = single_kernel_model(tmp_path, "one", name, [("out", ho * wo * kp), ("in", c * hi * wi), ("param", c)])
+    e = load_executor(base)
+    o = oracle.OracleExecutor(base + ".json", base + ".param")
+    for k, v in inputs.items():
+        e.set_input(k, v)
+        o.set_input(k, v)
+    e.execute()
+    o.execute()
+    got, want = e.get_output(), o.get_output()
+    assert capi.device_error() == 0
+    # TF32 rounding of the stored values: 2^-11 relative; zeros (padding, columns beyond K) are exact
+    assert np.array_equal(got == 0.0, want == 0.0)
+    assert np.all(np.abs(got - want) <= np.abs(want) * 2.0 ** -11 + 1e-30)
+    raw = got.copy()
+    for f in ("execute_preemptable", "execute_dispatch", "execute_graph"):
+        getattr(e, f)()
+        assert np.array_equal(e.get_output(), raw), f
+
+
+def test_im2col_stem_against_the_planar_stem(tmp_path):
+    """The default schedule runs the first convolution as reef_im2col_nchw + a 1x1 tensor-core convolution over the
+    flattened taps; the `_simtstem` variant keeps the planar CUDA-core convolution.  Same seed, same weights: the two
+    networks agree within the TF32 tolerance on the logits and the output, and the default one against the oracle
+    buffer by buffer."""
+    from reef_b200 import resources
+    d1 = resources.generate("resnet18_64", str(tmp_path))
+    d0 = resources.generate("resnet18_64", str(tmp_path), variant="_simtstem")
+    b1, b0 = d1 + "/resnet18_64", d0 + "/resnet18_64_simtstem"
+    j1, j0 = json.load(open(b1 + ".json")), json.load(open(b0 + ".json"))
+    n1, n0 = [k["name"] for k in j1["kernels"]], [k["name"] for k in j0["kernels"]]
+    assert n1[0].startswith("reef_im2col_nchw__c3") and "_ci160_" in n1[1] and "_kh1_kw1_" in n1[1] and "_v1" in n1[1]
+    assert "_nchw1" in n0[1] and not any(n.startswith("reef_im2col") for n in n0)
+    x = seeded_input(3 * 64 * 64, seed=6)
+    outs = []
+    for b in (b1, b0):
+        e = load_executor(b)
+        e.set_input("data", x)
+        e.execute()
+        outs.append(e.get_output().copy())
+        assert capi.device_error() == 0
+    assert rel_err(outs[0], outs[1]) < TF32_TOL
+    e = load_executor(b1)
+    o = oracle.OracleExecutor(b1 + ".json", b1 + ".param")
+    e.set_input("data", x)
+    o.set_input("data", x)
+    e.execute()
+    o.execute()
+    worst = compare_layers(e, o, j1, lambda n: TF32_TOL)
+    print("im2col stem worst layer", worst)
+
+
 @pytest.mark.parametrize("case", CONV_CASES, ids=[c[0][9:] + f"_{c[1]}x{c[4]}k{c[5]}{c[6]}s{c[7]}" for c in CONV_CASES])
 def test_conv_kernel_parity(tmp_path, case):
     _conv_case(tmp_path, case, "", FP32_TOL)
@@ -382,9 +445,18 @@ def test_tf32_schedule_against_the_unrounded_fp32_model(gen, model, inp):
     from reef_b200.resources.graph import read_param_file
     pa, pb = read_param_file(base + ".param"), read_param_file(gen(model, variant="_fp32") + ".param")
     rounded = 0
-    for k in pa:      # the two builds draw the same parameters in the same order: names line up
-        if k in pb and pa[k].size == pb[k].size and not np.array_equal(pa[k], pb[k]):
-            assert np.abs(pa[k] - pb[k]).max() <= 2.0 ** -10 * np.abs(pb[k]).max(), k    # a rounded copy, not another tensor
+    # the two builds draw the same parameters in the same order; the default schedule holds a few arrays the fp32 one
+    # does not (the im2col bias, the first convolution's weights flattened and padded), so the lists are walked side
+    # by side and an array without a partner of its size among the next few is skipped
+    la, lb = list(pa.values()), list(pb.values())
+    i = 0
+    for b in lb:
+        j2 = next((q for q in range(i, min(i + 4, len(la))) if la[q].size == b.size), None)
+        if j2 is None:
+            continue
+        a, i = la[j2], j2 + 1
+        if not np.array_equal(a, b):
+            assert np.abs(a - b).max() <= 2.0 ** -10 * np.abs(b).max()    # a rounded copy, not another tensor
             rounded += 1
     assert rounded > 10, "the default schedule's tensor-core weights should be rounded copies of the fp32 model's"
     e = load_executor(base)
