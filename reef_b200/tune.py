@@ -136,7 +136,8 @@ def tune_models(models, out_path: str = DEFAULT_OUT, variant: str = ""):
         d = resources.generate(m, variant=variant)
         for k in json.load(open(os.path.join(d, m + variant + ".json")))["kernels"]:
             fl, by, tc = capi.kernel_cost(k["name"])
-            if tc and k["name"] not in names:
+            # (the tensor-core attention kernel has one CTA per head: no tile cap or K split to choose)
+            if tc and not k["name"].startswith("reef_attention") and k["name"] not in names:
                 names.append(k["name"])
     del os.environ["REEF_UNTUNED"]
     with tempfile.TemporaryDirectory() as wd:
