@@ -314,7 +314,7 @@ def test_full_size_resnet_logits_and_probs(gen, model, variant):
         assert np.array_equal(e.get_output(), raw), f
 
 
-@pytest.mark.parametrize("model,delays", [("resnet50_64", [20, 60, 150]), ("resnet152", [100, 400, 1500])])
+@pytest.mark.parametrize("model,delays", [("resnet50_64", [10, 20, 40, 60, 100, 150, 250]), ("resnet152", [100, 400, 900, 1500])])
 def test_preempted_and_rerun_is_bit_identical(gen, model, delays):
     """A best-effort run that is preempted (flag raised mid-flight) and resumed from the first kernel whose
     completion counter is short must leave every buffer bit-identical to an uninterrupted GPU run."""
@@ -329,15 +329,18 @@ def test_preempted_and_rerun_is_bit_identical(gen, model, delays):
     slots, blocks = ref.task_slots()
     assert slots == blocks                      # every kernel's counter reached its block count
     hit = 0
-    for d in delays:
-        e = load_executor(base)
-        e.set_input("data", x)
-        restarts, first = e.execute_preempt_resume(d)
-        hit += restarts > 0
-        got = all_storage(e, j)
-        for i, (a, b) in enumerate(zip(got, want)):
-            assert np.array_equal(a, b), f"delay {d}us: storage {i} differs after {restarts} restarts (first {first})"
-        print(model, "delay", d, "us -> restarts", restarts, "first incomplete kernel", first)
+    for rep in range(3):          # where a delay lands depends on the host's launch rate: a second and third round if none did
+        for d in delays:
+            e = load_executor(base)
+            e.set_input("data", x)
+            restarts, first = e.execute_preempt_resume(d)
+            hit += restarts > 0
+            got = all_storage(e, j)
+            for i, (a, b) in enumerate(zip(got, want)):
+                assert np.array_equal(a, b), f"delay {d}us: storage {i} differs after {restarts} restarts (first {first})"
+            print(model, "delay", d, "us -> restarts", restarts, "first incomplete kernel", first)
+        if hit > 0:
+            break
     assert hit > 0, "no delay landed inside the run; preemption was not exercised"
 
 
