@@ -343,9 +343,11 @@ def main():
         # device-side poll then crosses PCIe: measured 20 times slower, hence not the default).
         n_pre = max(200, n_req // 8)
 
-        def preempt_phase(wait_sync, mapped):
+        def preempt_phase(wait_sync, mapped, be_cap=None):
             s, ids = make_sched(n_be, mapped_flag=mapped, stamps=wait_sync)
             s.set_wait_sync(wait_sync)
+            if be_cap is not None:
+                s.set_be_stream_cap(be_cap)
             clients = [dict(mid=ids["rt"], max_requests=n_pre, warmup=5, want_output=False, think_us=2000)] + \
                       [dict(mid=m, max_requests=0, want_output=False) for m in ids["be"]]
             rs = s.run_clients(clients)
@@ -372,6 +374,14 @@ def main():
             if not mapped:
                 extra["rt_after_preempt_p50_ms"] = pct(rs[0]["latencies_ms"], 50)
                 extra["rt_after_preempt_p99_ms"] = pct(rs[0]["latencies_ms"], 99)
+        if args.be_cap != 1:
+            # the in-flight cap trades free-running best-effort throughput against the drain: with one kernel per stream
+            # in flight (the reference's default is 2, scheduler.cpp:29-33) nothing is queued behind the kernel that leaves
+            rs, st = preempt_phase(True, False, be_cap=1)
+            extra["preempt_cap1_drain_avg_us"] = st["drain_ns_sum"] / max(1, st["drain_count"]) / 1e3
+            extra["preempt_cap1_drain_p99_us"] = st["drain_ns_p99"] / 1e3
+            extra["preempt_cap1_drain_max_us"] = st["drain_ns_max"] / 1e3
+            extra["be_inf_s_cap1_rt_every_2ms_with_drain"] = sum(r["completed"] / r["elapsed_s"] for r in rs[1:] if r["elapsed_s"] > 0)
         extra["preempt_target_metric"] = "preempt_drain_avg_us (flag write -> best-effort streams drained, host clock) < 20"
 
     # ---- phase E (e2e): same workload through the request calls with pinned host buffers ---------
