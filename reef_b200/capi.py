@@ -116,12 +116,13 @@ def device_count() -> int:
 
 
 def probe_stream_latency(iters: int = 2000, device: int = 0):
-    """(write call, write + completion as the host sees it, bare event round trip) in microseconds, medians."""
+    """(write call, write + completion as the host sees it, completion-only event round trip, timed event round trip)
+    in microseconds, medians."""
     lib = cuda_lib()
     _check(lib.reef_gpu_init(C.c_int(device)), "reef_gpu_init")
-    a, b, c = C.c_double(), C.c_double(), C.c_double()
-    _check(lib.reef_probe_stream_latency(C.c_int(iters), C.byref(a), C.byref(b), C.byref(c)), "reef_probe_stream_latency")
-    return a.value, b.value, c.value
+    a, b, c, d = C.c_double(), C.c_double(), C.c_double(), C.c_double()
+    _check(lib.reef_probe_stream_latency(C.c_int(iters), C.byref(a), C.byref(b), C.byref(c), C.byref(d)), "reef_probe_stream_latency")
+    return a.value, b.value, c.value, d.value
 
 
 def device_error() -> int:

@@ -324,7 +324,7 @@ reef_status reef_partition_destroy(reef_partition_t p) {
 }
 
 reef_status reef_probe_stream_latency(int iters, double* write_call_us, double* write_complete_us,
-                                      double* event_round_trip_us) {
+                                      double* event_round_trip_us, double* timed_event_round_trip_us) {
     using clk = std::chrono::steady_clock;
     auto us = [](clk::time_point a, clk::time_point b) { return std::chrono::duration<double, std::micro>(b - a).count(); };
     if (iters < 10) iters = 10;
@@ -336,7 +336,9 @@ reef_status reef_probe_stream_latency(int iters, double* write_call_us, double* 
     cudaEvent_t ev;
     CK(cudaMalloc(&flag, 256));
     CK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
-    std::vector<double> a, b, c;
+    cudaEvent_t evt;
+    CK(cudaEventCreate(&evt));
+    std::vector<double> a, b, c, d;
     reef_status rc = REEF_SUCC;
     for (int i = 0; i < iters + iters / 10 && rc == REEF_SUCC; i++) {
         auto t0 = clk::now();
@@ -348,14 +350,19 @@ reef_status reef_probe_stream_latency(int iters, double* write_call_us, double* 
         cudaEventRecord(ev, st);
         while (cudaEventQuery(ev) == cudaErrorNotReady) {}
         auto t3 = clk::now();
+        cudaEventRecord(evt, st);
+        while (cudaEventQuery(evt) == cudaErrorNotReady) {}
+        auto t4 = clk::now();
         if (i >= iters / 10) {
             a.push_back(us(t0, t1));
             b.push_back(us(t0, t2));
             c.push_back(us(t2, t3));
+            d.push_back(us(t3, t4));
         }
-        while (us(t3, clk::now()) < 200.0) {}
+        while (us(t4, clk::now()) < 200.0) {}
     }
     cudaEventDestroy(ev);
+    cudaEventDestroy(evt);
     cudaFree(flag);
     cudaStreamDestroy(st);
     if (rc != REEF_SUCC) return rc;
@@ -364,12 +371,19 @@ reef_status reef_probe_stream_latency(int iters, double* write_call_us, double* 
     if (write_call_us) *write_call_us = med(a);
     if (write_complete_us) *write_complete_us = med(b);
     if (event_round_trip_us) *event_round_trip_us = med(c);
+    if (timed_event_round_trip_us) *timed_event_round_trip_us = med(d);
     return REEF_SUCC;
 }
 
 reef_status reef_event_create(reef_event_t* e) {
     cudaEvent_t ev;
     CK(cudaEventCreate(&ev));
+    *e = (reef_event_t)ev;
+    return REEF_SUCC;
+}
+reef_status reef_event_create_untimed(reef_event_t* e) {
+    cudaEvent_t ev;
+    CK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
     *e = (reef_event_t)ev;
     return REEF_SUCC;
 }

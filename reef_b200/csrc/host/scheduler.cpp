@@ -736,7 +736,7 @@ void REEFScheduler::advance_padded(Task* be_task, TaskQueue* q, int blocks, bool
             ev = q->free_events.back();
             q->free_events.pop_back();
         } else {
-            reef_event_create(&ev);
+            reef_event_create_untimed(&ev);
         }
         reef_event_record(ev, q->stream);
         q->inflight.push_back(InFlight{ev, n_be - 1});
@@ -939,7 +939,7 @@ bool REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
                         ev = q.free_events.back();
                         q.free_events.pop_back();
                     } else {
-                        reef_event_create(&ev);
+                        reef_event_create_untimed(&ev);
                     }
                     reef_event_record(ev, q.stream);
                     if (q.pad_out.empty()) {
@@ -990,7 +990,7 @@ bool REEFScheduler::timeline_padding(std::shared_ptr<Task>& rt_task) {
                 ev = q.free_events.back();
                 q.free_events.pop_back();
             } else {
-                reef_event_create(&ev);
+                reef_event_create_untimed(&ev);
             }
             reef_event_record(ev, q.stream);
             if (q.pad_out.empty()) {
@@ -1214,7 +1214,7 @@ void REEFScheduler::execute_be_task(std::shared_ptr<Task>& task, std::shared_ptr
             ev = tqueue->free_events.back();
             tqueue->free_events.pop_back();
         } else {
-            reef_event_create(&ev);
+            reef_event_create_untimed(&ev);
         }
         reef_event_record(ev, tqueue->stream);
         tqueue->inflight.push_back(InFlight{ev, k});
