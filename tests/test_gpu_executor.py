@@ -623,3 +623,12 @@ def test_best_effort_chain_preempted_and_resumed_is_bit_identical(gen, model, cl
     assert any(r > 0 for _, r, _ in hit), "no delay landed inside the run"
     b, en, _, _ = e.chain_info(0)
     assert any(b < f < en for _, r, f in hit if r > 0), "no preemption stopped the chain in the middle of its layers"
+
+
+def test_stream_latency_probe_and_untimed_events():
+    """reef_probe_stream_latency returns positive medians, and a completion-only event is seen complete by the host no
+    later than a timed one (the reason the scheduler tracks completion with reef_event_create_untimed)."""
+    w, wc, ev, evt = capi.probe_stream_latency(200, 0)
+    print("write call", w, "write+completion", wc, "untimed event", ev, "timed event", evt)
+    assert 0 < w < wc and 0 < ev <= evt * 1.5 and wc < 1000 and evt < 1000
+    assert capi.device_error() == 0
