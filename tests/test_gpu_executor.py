@@ -612,16 +612,19 @@ def test_best_effort_chain_preempted_and_resumed_is_bit_identical(gen, model, cl
     assert e.build_chains(0) >= 1
     e.set_input("data", x)
     hit = []
-    for d in delays:
-        restarts, first = e.execute_preempt_resume_chained(d, clusters)
-        hit.append((d, restarts, first))
-        got = all_storage(e, j)
-        for i, (a, b) in enumerate(zip(got, want)):
-            assert np.array_equal(a, b), f"{model} delay {d}us: storage {i} differs after {restarts} restarts (first {first})"
+    b, en, _, _ = e.chain_info(0)
+    for rep in range(3):      # where a delay lands depends on the host's launch rate: up to three rounds
+        for d in delays:
+            restarts, first = e.execute_preempt_resume_chained(d, clusters)
+            hit.append((d, restarts, first))
+            got = all_storage(e, j)
+            for i, (a, bb) in enumerate(zip(got, want)):
+                assert np.array_equal(a, bb), f"{model} delay {d}us: storage {i} differs after {restarts} restarts (first {first})"
+        if any(b < f < en for _, r, f in hit if r > 0):
+            break
     print(model, "clusters", clusters, "(delay us, restarts, first incomplete kernel):", hit)
     assert capi.device_error() == 0
     assert any(r > 0 for _, r, _ in hit), "no delay landed inside the run"
-    b, en, _, _ = e.chain_info(0)
     assert any(b < f < en for _, r, f in hit if r > 0), "no preemption stopped the chain in the middle of its layers"
 
 
