@@ -176,7 +176,7 @@ def main():
     ap.add_argument("--be-cap", type=int, default=int(os.environ.get("REEF_BE_CAP", "2")),
                     help="kernels a BE task keeps on its stream (reference: 2, scheduler.cpp:32)")
     ap.add_argument("--pad-target", type=float, default=None,
-                    help="slowdown the padding controller may cost a real-time task (default: the scheduler's 0.07)")
+                    help="slowdown the padding controller may cost a real-time task (default: the scheduler's 0.065)")
     ap.add_argument("--mapped-flag", action="store_true", help="also measure preemption with the flag in mapped host memory")
     ap.add_argument("--be-sms", type=int, default=int(os.environ.get("REEF_BE_SMS", "0")),
                     help="SMs set aside for the best-effort streams (spatial partition; 0 = none, all streams share the GPU)")

@@ -267,7 +267,7 @@ private:
     int pad_quantum = 24;
     double pad_piece_bytes = 32e6;      // a padded piece moves at most this many algorithmic bytes (0: no limit)
     int pad_piece_cap = 0;              // > 0: best-effort pieces never claim more slots than this (wide kernels are cut)
-    double pad_target = 0.07;
+    double pad_target = 0.065;
     double pad_ratio_ema = 0.0;
     double pad_rate = 100.0;            // best-effort kernels per real-time window (controller state)
     // loop statistics of timeline_padding, printed at destruction when REEF_PAD_TRACE is set
